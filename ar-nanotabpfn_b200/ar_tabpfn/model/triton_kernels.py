@@ -1,0 +1,176 @@
+"""Functional shared-context attention operators, same names and tensor shapes as
+the reference module ``ar_tabpfn/model/triton_kernels.py`` (347-475, 478-524,
+662-767), executed by the sm_100a kernels of libartab_b200.so.
+
+Shapes follow the reference: q [B,H,Lq,Dh], k_ctx / v_ctx [H,Nc,Dh] shared by the
+whole batch, k_buf / v_buf [B,H,Nb,Dh] private per batch element.  Inputs may be
+non-contiguous views.  float32 inputs use fp32 FMA kernels, bfloat16 inputs the
+tcgen05 tensor-core kernel (head_dim 32) with fp32 accumulation.
+"""
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import torch
+from torch import Tensor
+
+from .. import _lib
+
+
+def triton_available() -> bool:
+    """True when the CUDA library can be used (the name is the reference's)."""
+    try:
+        _lib.lib()
+        return True
+    except Exception:
+        return False
+
+
+def _pad8(n: int) -> int:
+    return (n + 7) // 8 * 8
+
+
+def _rows(q: Tensor) -> Tensor:
+    """[B,H,Lq,Dh] -> token-major [B*Lq,H,Dh], contiguous."""
+    B, H, Lq, Dh = q.shape
+    return q.permute(0, 2, 1, 3).reshape(B * Lq, H, Dh).contiguous()
+
+
+def _unrows(o: Tensor, B: int, Lq: int) -> Tensor:
+    rows, H, Dh = o.shape
+    return o.view(B, Lq, H, Dh).permute(0, 2, 1, 3)
+
+
+def pack_context(k_ctx: Tensor, v_ctx: Tensor) -> Tuple[Tensor, Tensor, int, int]:
+    """Lay [H,Nc,Dh] (or [G,H,Nc,Dh]) context K/V out as the kernels read it:
+    K [G,H,Ncp,Dh]; V the same in fp32, transposed [G,H,Dh,Ncp] in bf16."""
+    if k_ctx.dim() == 3:
+        k_ctx, v_ctx = k_ctx.unsqueeze(0), v_ctx.unsqueeze(0)
+    G, H, Nc, Dh = k_ctx.shape
+    Ncp = _pad8(Nc)
+    k = torch.zeros(G, H, Ncp, Dh, device=k_ctx.device, dtype=k_ctx.dtype)
+    k[:, :, :Nc] = k_ctx
+    if k_ctx.dtype == torch.bfloat16:
+        v = torch.zeros(G, H, Dh, Ncp, device=k_ctx.device, dtype=k_ctx.dtype)
+        v[:, :, :, :Nc] = v_ctx.transpose(-1, -2)
+    else:
+        v = torch.zeros(G, H, Ncp, Dh, device=k_ctx.device, dtype=k_ctx.dtype)
+        v[:, :, :Nc] = v_ctx
+    return k, v, Nc, Ncp
+
+
+def _context_partials(qr: Tensor, k: Tensor, v: Tensor, Nc: int, Ncp: int, rows_per_group: int,
+                      n_splits: int) -> Tuple[Tensor, Tensor]:
+    lib = _lib.lib()
+    rows, H, Dh = qr.shape
+    G = k.shape[0]
+    out = torch.empty(n_splits, rows, H, Dh, device=qr.device, dtype=torch.float32)
+    lse = torch.empty(n_splits, rows, H, device=qr.device, dtype=torch.float32)
+    status = torch.zeros(1, device=qr.device, dtype=torch.int32)
+    _lib.check(lib.artab_context_attention(_lib.dtype_code(qr.dtype), _lib.ptr(qr), _lib.ptr(k), _lib.ptr(v), rows,
+                                           rows_per_group, G, H, Dh, Nc, Ncp, n_splits, _lib.ptr(out),
+                                           _lib.ptr(lse), _lib.ptr(status), _lib.stream_ptr()))
+    return out, lse
+
+
+def _scaled(q: Tensor, scale: Optional[float]) -> Tensor:
+    Dh = q.shape[-1]
+    if scale is None or abs(scale - Dh ** -0.5) < 1e-12:
+        return q
+    return q * (scale * Dh ** 0.5)
+
+
+def triton_context_attention(q: Tensor, k_ctx: Tensor, v_ctx: Tensor,
+                             scale: Optional[float] = None, n_splits: int = 1) -> Tuple[Tensor, Tensor]:
+    """out [B,H,Lq,Dh] (q dtype), lse [B,H,Lq] fp32 (natural log)."""
+    B, H, Lq, Dh = q.shape
+    k, v, Nc, Ncp = pack_context(k_ctx.to(q.dtype), v_ctx.to(q.dtype))
+    qr = _rows(_scaled(q, scale))
+    o, l = _context_partials(qr, k, v, Nc, Ncp, B * Lq, n_splits)
+    if n_splits > 1:
+        zeros = torch.zeros_like(qr)
+        merged = torch.empty(B * Lq, H, Dh, device=q.device, dtype=torch.float32)
+        _lib.check(_lib.lib().artab_buffer_attention_merge(
+            _lib.dtype_code(q.dtype), _lib.ptr(zeros), None, B * Lq, H, Dh, 0, 0, 1, 0, _lib.ptr(o), _lib.ptr(l),
+            n_splits, B * Lq, _lib.ptr(merged), _lib.stream_ptr()))
+        lse = torch.logsumexp(l, dim=0)
+        return _unrows(merged, B, Lq).to(q.dtype), lse.view(B, Lq, H).permute(0, 2, 1)
+    return _unrows(o[0], B, Lq).to(q.dtype), l[0].view(B, Lq, H).permute(0, 2, 1)
+
+
+def triton_context_attention_multiq(q, k_ctx, v_ctx, scale=None):
+    return triton_context_attention(q, k_ctx, v_ctx, scale=scale)
+
+
+def merge_attention_outputs(out_ctx: Tensor, lse_ctx: Tensor, out_buf: Tensor, lse_buf: Tensor) -> Tensor:
+    """Log-sum-exp merge of two partial attentions, [B,H,Lq,Dh] / [B,H,Lq]."""
+    B, H, Lq, Dh = out_ctx.shape
+    o = torch.stack([_rows(out_ctx.float()), _rows(out_buf.float())])
+    l = torch.stack([lse_ctx.float().permute(0, 2, 1).reshape(B * Lq, H),
+                     lse_buf.float().permute(0, 2, 1).reshape(B * Lq, H)]).contiguous()
+    zeros = torch.zeros(B * Lq, H, Dh, device=out_ctx.device, dtype=torch.float32)
+    merged = torch.empty_like(zeros)
+    _lib.check(_lib.lib().artab_buffer_attention_merge(
+        _lib.F32, _lib.ptr(zeros), None, B * Lq, H, Dh, 0, 0, 1, 0, _lib.ptr(o), _lib.ptr(l), 2, B * Lq,
+        _lib.ptr(merged), _lib.stream_ptr()))
+    return _unrows(merged, B, Lq).to(out_ctx.dtype)
+
+
+def _pack_buffer(k_buf: Tensor, v_buf: Tensor) -> Tensor:
+    """[B,H,Nb,Dh] x2 -> [B,H,Nb,2,Dh] (K row and V row of a key adjacent)."""
+    return torch.stack([k_buf, v_buf], dim=3).contiguous()
+
+
+def hybrid_attention(q: Tensor, k_ctx: Tensor, v_ctx: Tensor, k_buf: Tensor, v_buf: Tensor,
+                     buf_mask: Optional[Tensor] = None, use_triton: bool = True) -> Tensor:
+    """Shared-context attention + private-buffer attention merged by log-sum-exp
+    (every query sees every buffer key).  Returns [B,H,Lq,Dh]."""
+    if buf_mask is not None:
+        raise NotImplementedError("arbitrary buffer masks are not supported; "
+                                  "use hybrid_teacher_forcing_attention for the block-causal pattern")
+    B, H, Lq, Dh = q.shape
+    Nb = k_buf.shape[2]
+    if Nb == 0:
+        return triton_context_attention(q, k_ctx, v_ctx)[0]
+    lib = _lib.lib()
+    k, v, Nc, Ncp = pack_context(k_ctx.to(q.dtype), v_ctx.to(q.dtype))
+    kv = _pack_buffer(k_buf.to(q.dtype), v_buf.to(q.dtype))
+    outs = []
+    for j0 in range(0, Lq, 2):
+        n = min(2, Lq - j0)
+        qr = _rows(q[:, :, j0:j0 + n])
+        splits = lib.artab_plan_splits(_lib.dtype_code(q.dtype), B * n, n, 1, H, Nc)
+        o, l = _context_partials(qr, k, v, Nc, Ncp, n, splits)
+        merged = torch.empty(B * n, H, Dh, device=q.device, dtype=torch.float32)
+        _lib.check(lib.artab_buffer_attention_merge(
+            _lib.dtype_code(q.dtype), _lib.ptr(qr), _lib.ptr(kv), B, H, Dh, Nb, 0, n, Nb, _lib.ptr(o), _lib.ptr(l),
+            splits, B * n, _lib.ptr(merged), _lib.stream_ptr()))
+        outs.append(_unrows(merged, B, n))
+    return torch.cat(outs, dim=2).to(q.dtype)
+
+
+def hybrid_teacher_forcing_attention(q: Tensor, k_ctx: Tensor, v_ctx: Tensor, k_buf: Tensor, v_buf: Tensor,
+                                     num_targets: int, use_triton: bool = True) -> Tensor:
+    """q [B,H,2Nt,Dh] ordered [buffers, targets]; buffer i sees buffer keys <= i,
+    target i sees buffer keys < i; everyone sees the whole shared context."""
+    B, H, L2, Dh = q.shape
+    if L2 != 2 * num_targets:
+        raise ValueError("Expected 2*num_targets queries for teacher forcing.")
+    if k_buf.shape[2] != num_targets:
+        raise ValueError("Expected buffer length to match num_targets.")
+    lib = _lib.lib()
+    k, v, Nc, Ncp = pack_context(k_ctx.to(q.dtype), v_ctx.to(q.dtype))
+    kv = _pack_buffer(k_buf.to(q.dtype), v_buf.to(q.dtype))
+    qr = _rows(q)
+    splits = lib.artab_plan_splits(_lib.dtype_code(q.dtype), B * L2, L2, 1, H, Nc)
+    o, l = _context_partials(qr, k, v, Nc, Ncp, L2, splits)
+    merged = torch.empty(B * L2, H, Dh, device=q.device, dtype=torch.float32)
+    _lib.check(lib.artab_buffer_attention_merge(
+        _lib.dtype_code(q.dtype), _lib.ptr(qr), _lib.ptr(kv), B, H, Dh, num_targets, 1, num_targets, 0,
+        _lib.ptr(o), _lib.ptr(l), splits, B * L2, _lib.ptr(merged), _lib.stream_ptr()))
+    return _unrows(merged, B, L2).to(q.dtype)
+
+
+def cross_attention(q: Tensor, k_ctx: Tensor, v_ctx: Tensor, use_triton: bool = True) -> Tensor:
+    """Shared-context attention without the LSE output."""
+    return triton_context_attention(q, k_ctx, v_ctx)[0]

@@ -1,0 +1,41 @@
+// Argument blocks of the attention kernels.
+#pragma once
+#include "common.cuh"
+
+namespace artab {
+
+struct CtxAttnArgs {
+  int dtype;
+  const void* q;      // [rows][H][Dh]
+  const void* k_ctx;  // [G][H][Ncp][Dh]
+  const void* v_ctx;  // [G][H][Ncp][Dh] or transposed [G][H][Dh][Ncp]
+  int v_transposed;
+  int rows, rows_per_group, n_groups, n_heads, head_dim, n_ctx, n_ctx_pad, n_splits;
+  float scale;
+  float* out;         // [splits][rows][H][Dh]
+  float* lse;         // [splits][rows][H]
+  int32_t* status;    // device status word (bounded waits), may be null for SIMT
+};
+
+struct BufMergeArgs {
+  int dtype;
+  const void* q;       // [rows][H][Dh]
+  const void* kv_buf;  // [B][H][T][2][Dh]
+  int n_heads, head_dim, max_buf;
+  int mode_tf, nt, n_new, len0;
+  long n_items;
+  const float* o_part;    // [splits][rows][H][Dh]
+  const float* lse_part;  // [splits][rows][H]
+  int n_splits, rows;
+  float scale;
+  float* out;  // [rows][H][Dh]
+};
+
+int launch_ctx_attn_simt(const CtxAttnArgs& a, cudaStream_t s);
+int launch_ctx_attn_tc(const CtxAttnArgs& a, cudaStream_t s);  // tcgen05, bf16, head_dim 32
+bool ctx_attn_tc_supported(int dtype, int head_dim);
+int launch_buf_merge(const BufMergeArgs& a, cudaStream_t s);
+int launch_kv_append(int dtype, void* kv, const void* k_new, const void* v_new, long n_bh, int dh, int max_buf,
+                     int pos, cudaStream_t s);
+
+}  // namespace artab

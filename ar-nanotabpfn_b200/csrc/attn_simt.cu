@@ -1,0 +1,375 @@
+// SIMT attention kernels.
+//
+//  * ctx_attn_simt_kernel  — queries of many streams against one shared (or one
+//    per-group) context K/V with online softmax and LSE output; fp32 FMA math.
+//    This is the context kernel of the fp32 mode (and of head sizes the
+//    tensor-core kernel is not built for).
+//  * buf_merge_kernel      — the bandwidth-bound warp-level pass over each
+//    stream's private buffer K/V, merged in registers by log-sum-exp with the
+//    context partials (any number of key splits).  Used by both dtypes.
+//  * kv_append_kernel      — in-place append of one K/V row per (stream, head).
+#include "attn.cuh"
+
+namespace artab {
+
+namespace {
+
+constexpr int kQW = 4;        // queries per warp
+constexpr int kWarps = 4;     // warps per CTA
+constexpr int kQB = kQW * kWarps;
+constexpr int kKT = 64;       // keys per tile
+
+template <typename T, int DH>
+__global__ void __launch_bounds__(kWarps * 32) ctx_attn_simt_kernel(const CtxAttnArgs a) {
+  constexpr int NDL = DH >= 32 ? DH / 32 : 1;  // output dims per lane
+  __shared__ float sK[kKT][DH + 1];
+  __shared__ float sV[kKT][DH];
+  __shared__ float sQ[kQB][DH];
+  __shared__ __align__(16) float sP[kWarps][kKT][kQW];
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int h = blockIdx.y;
+  const int g = blockIdx.z / a.n_splits, split = blockIdx.z - g * a.n_splits;
+  const int rows_in_group = a.n_groups == 1 ? a.rows : a.rows_per_group;
+  const long group_row0 = a.n_groups == 1 ? 0 : (long)g * a.rows_per_group;
+  const int q0 = blockIdx.x * kQB;
+  if (q0 >= rows_in_group) return;
+
+  const int tiles = (a.n_ctx + kKT - 1) / kKT;
+  const int tps = (tiles + a.n_splits - 1) / a.n_splits;
+  const int k_begin = split * tps * kKT;
+  const int k_end = min(a.n_ctx, k_begin + tps * kKT);
+
+  const T* Q = reinterpret_cast<const T*>(a.q);
+  const T* Kc = reinterpret_cast<const T*>(a.k_ctx) + ((size_t)(g * a.n_heads + h) * a.n_ctx_pad) * DH;
+  const T* Vc = reinterpret_cast<const T*>(a.v_ctx) + ((size_t)(g * a.n_heads + h) * a.n_ctx_pad) * DH;
+
+  for (int i = threadIdx.x; i < kQB * DH; i += blockDim.x) {
+    const int qi = i / DH, d = i - qi * DH;
+    const int r = q0 + qi;
+    sQ[qi][d] = r < rows_in_group ? to_f32<T>(Q[((size_t)(group_row0 + r) * a.n_heads + h) * DH + d]) : 0.f;
+  }
+
+  float m[kQW], l[kQW], acc[kQW][NDL];
+#pragma unroll
+  for (int qq = 0; qq < kQW; ++qq) {
+    m[qq] = -INFINITY;
+    l[qq] = 0.f;
+#pragma unroll
+    for (int e = 0; e < NDL; ++e) acc[qq][e] = 0.f;
+  }
+  const float sc = a.scale * kLog2e;
+
+  for (int kt = k_begin; kt < k_end; kt += kKT) {
+    __syncthreads();
+    for (int i = threadIdx.x; i < kKT * DH; i += blockDim.x) {
+      const int key = i / DH, d = i - key * DH;
+      sK[key][d] = (kt + key) < a.n_ctx ? to_f32<T>(Kc[(size_t)(kt + key) * DH + d]) : 0.f;
+    }
+    if (a.v_transposed) {
+      for (int i = threadIdx.x; i < kKT * DH; i += blockDim.x) {
+        const int d = i / kKT, key = i - d * kKT;
+        sV[key][d] = (kt + key) < a.n_ctx ? to_f32<T>(Vc[(size_t)d * a.n_ctx_pad + kt + key]) : 0.f;
+      }
+    } else {
+      for (int i = threadIdx.x; i < kKT * DH; i += blockDim.x) {
+        const int key = i / DH, d = i - key * DH;
+        sV[key][d] = (kt + key) < a.n_ctx ? to_f32<T>(Vc[(size_t)(kt + key) * DH + d]) : 0.f;
+      }
+    }
+    __syncthreads();
+
+    float s0[kQW], s1[kQW];
+#pragma unroll
+    for (int qq = 0; qq < kQW; ++qq) s0[qq] = s1[qq] = 0.f;
+#pragma unroll 8
+    for (int d = 0; d < DH; ++d) {
+      const float k0 = sK[lane][d], k1 = sK[lane + 32][d];
+#pragma unroll
+      for (int qq = 0; qq < kQW; ++qq) {
+        const float qv = sQ[warp * kQW + qq][d];
+        s0[qq] = fmaf(qv, k0, s0[qq]);
+        s1[qq] = fmaf(qv, k1, s1[qq]);
+      }
+    }
+    const bool v0 = kt + lane < k_end, v1 = kt + lane + 32 < k_end;
+#pragma unroll
+    for (int qq = 0; qq < kQW; ++qq) {
+      const float a0 = v0 ? s0[qq] * sc : -INFINITY;
+      const float a1 = v1 ? s1[qq] * sc : -INFINITY;
+      const float mn = fmaxf(m[qq], warp_max(fmaxf(a0, a1)));  // finite: every tile holds a valid key
+      const float alpha = exp2f(m[qq] - mn);
+      const float p0 = exp2f(a0 - mn), p1 = exp2f(a1 - mn);
+      l[qq] = l[qq] * alpha + warp_sum(p0 + p1);
+      m[qq] = mn;
+#pragma unroll
+      for (int e = 0; e < NDL; ++e) acc[qq][e] *= alpha;
+      sP[warp][lane][qq] = p0;
+      sP[warp][lane + 32][qq] = p1;
+    }
+    __syncwarp();
+    if (DH >= 32 || lane < DH) {
+#pragma unroll 4
+      for (int key = 0; key < kKT; ++key) {
+        const float4 p4 = *reinterpret_cast<const float4*>(&sP[warp][key][0]);
+#pragma unroll
+        for (int e = 0; e < NDL; ++e) {
+          const float v = sV[key][lane + 32 * e];
+          acc[0][e] = fmaf(p4.x, v, acc[0][e]);
+          acc[1][e] = fmaf(p4.y, v, acc[1][e]);
+          acc[2][e] = fmaf(p4.z, v, acc[2][e]);
+          acc[3][e] = fmaf(p4.w, v, acc[3][e]);
+        }
+      }
+    }
+    __syncwarp();
+  }
+
+#pragma unroll
+  for (int qq = 0; qq < kQW; ++qq) {
+    const int r = q0 + warp * kQW + qq;
+    if (r >= rows_in_group) continue;
+    const size_t ro = ((size_t)split * a.rows + group_row0 + r) * a.n_heads + h;
+    const float inv = l[qq] > 0.f ? 1.0f / l[qq] : 0.f;
+    if (DH >= 32 || lane < DH) {
+#pragma unroll
+      for (int e = 0; e < NDL; ++e) a.out[ro * DH + lane + 32 * e] = acc[qq][e] * inv;
+    }
+    if (lane == 0) a.lse[ro] = l[qq] > 0.f ? (m[qq] + log2f(l[qq])) * kLn2 : -INFINITY;
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Private-buffer pass + merge.  One warp per (stream, head[, item]).
+// Each key's K row and V row are adjacent in memory ([.., T][2][Dh]), so a warp
+// iteration reads one contiguous span of KPI keys; LPK lanes share a key, each
+// holding one 16-byte slice of the K row and of the V row.
+// ---------------------------------------------------------------------------
+template <typename T, int DH>
+__global__ void __launch_bounds__(128) buf_merge_kernel(const BufMergeArgs a) {
+  constexpr int VEC = Vec16<T>::N;
+  constexpr int LPK = DH / VEC;   // lanes per key
+  constexpr int KPI = 32 / LPK;   // keys per warp iteration
+  static_assert(LPK >= 1 && LPK <= 32 && (LPK & (LPK - 1)) == 0, "head_dim must give a power-of-two slice count");
+  const int lane = threadIdx.x & 31;
+  const long item = (long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (item >= a.n_items) return;
+  const int sub = lane % LPK, grp = lane / LPK;
+
+  long b;
+  int h, len;
+  long row_t, row_b;
+  if (a.mode_tf) {
+    const int ips = a.nt + 1;
+    const int i = (int)(item % ips);
+    const long bh = item / ips;
+    b = bh / a.n_heads;
+    h = (int)(bh - b * a.n_heads);
+    len = i;
+    row_t = i < a.nt ? b * 2 * a.nt + a.nt + i : -1;
+    row_b = i >= 1 ? b * 2 * a.nt + i - 1 : -1;
+  } else {
+    b = item / a.n_heads;
+    h = (int)(item - b * a.n_heads);
+    len = a.len0;
+    row_t = b * a.n_new + a.n_new - 1;
+    row_b = a.n_new == 2 ? b * a.n_new : -1;
+  }
+
+  const T* Q = reinterpret_cast<const T*>(a.q);
+  const float sc = a.scale * kLog2e;
+  float q[2][VEC];
+  const long rows2[2] = {row_t, row_b};
+#pragma unroll
+  for (int w = 0; w < 2; ++w) {
+    if (rows2[w] >= 0) {
+      Vec16<T>::load(Q + ((size_t)rows2[w] * a.n_heads + h) * DH + sub * VEC, q[w]);
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) q[w][e] *= sc;
+    } else {
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) q[w][e] = 0.f;
+    }
+  }
+
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f}, acc[2][VEC];
+#pragma unroll
+  for (int w = 0; w < 2; ++w)
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) acc[w][e] = 0.f;
+
+  const T* kv = reinterpret_cast<const T*>(a.kv_buf) + ((size_t)(b * a.n_heads + h) * a.max_buf) * 2 * DH;
+#pragma unroll 2
+  for (int key0 = 0; key0 < len; key0 += KPI) {
+    const int key = key0 + grp;
+    const bool valid = key < len;
+    float kf[VEC], vf[VEC];
+    if (valid) {
+      const T* p = kv + (size_t)key * 2 * DH + sub * VEC;
+      Vec16<T>::load(p, kf);
+      Vec16<T>::load(p + DH, vf);
+    } else {
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) kf[e] = vf[e] = 0.f;
+    }
+    float s[2] = {0.f, 0.f};
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) {
+      s[0] = fmaf(q[0][e], kf[e], s[0]);
+      s[1] = fmaf(q[1][e], kf[e], s[1]);
+    }
+#pragma unroll
+    for (int o = 1; o < LPK; o <<= 1) {
+      s[0] += __shfl_xor_sync(0xffffffffu, s[0], o);
+      s[1] += __shfl_xor_sync(0xffffffffu, s[1], o);
+    }
+    if (valid) {
+#pragma unroll
+      for (int w = 0; w < 2; ++w) {
+        const float mn = fmaxf(m[w], s[w]);
+        const float alpha = exp2f(m[w] - mn);
+        const float p = exp2f(s[w] - mn);
+        l[w] = l[w] * alpha + p;
+        m[w] = mn;
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) acc[w][e] = fmaf(p, vf[e], acc[w][e] * alpha);
+      }
+    }
+  }
+  // fold the KPI per-group partial softmaxes together
+#pragma unroll
+  for (int o = LPK; o < 32; o <<= 1) {
+#pragma unroll
+    for (int w = 0; w < 2; ++w) {
+      const float mo = __shfl_xor_sync(0xffffffffu, m[w], o);
+      const float lo = __shfl_xor_sync(0xffffffffu, l[w], o);
+      const float mn = fmaxf(m[w], mo);
+      const float a1 = mn == -INFINITY ? 0.f : exp2f(m[w] - mn);
+      const float a2 = mn == -INFINITY ? 0.f : exp2f(mo - mn);
+      l[w] = l[w] * a1 + lo * a2;
+      m[w] = mn;
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) {
+        const float ao = __shfl_xor_sync(0xffffffffu, acc[w][e], o);
+        acc[w][e] = acc[w][e] * a1 + ao * a2;
+      }
+    }
+  }
+
+  // log-sum-exp merge with the context partials, all in registers
+#pragma unroll
+  for (int w = 0; w < 2; ++w) {
+    const long r = rows2[w];
+    if (r < 0) continue;
+    float lse_b = l[w] > 0.f ? (m[w] + log2f(l[w])) * kLn2 : -INFINITY;  // natural log, like the partials
+    float top = lse_b;
+    for (int s = 0; s < a.n_splits; ++s)
+      top = fmaxf(top, __ldg(a.lse_part + ((size_t)s * a.rows + r) * a.n_heads + h));
+    float wsum = 0.f, o[VEC];
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) o[e] = 0.f;
+    if (l[w] > 0.f) {
+      const float wb = expf(lse_b - top);
+      wsum = wb;
+      const float inv = wb / l[w];
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) o[e] = acc[w][e] * inv;
+    }
+    for (int s = 0; s < a.n_splits; ++s) {
+      const size_t ro = ((size_t)s * a.rows + r) * a.n_heads + h;
+      const float ls = __ldg(a.lse_part + ro);
+      if (ls == -INFINITY) continue;
+      const float ws = expf(ls - top);
+      wsum += ws;
+      const float* op = a.o_part + ro * DH + sub * VEC;
+#pragma unroll
+      for (int e = 0; e < VEC; e += 4) {
+        const float4 v = *reinterpret_cast<const float4*>(op + e);
+        o[e] = fmaf(ws, v.x, o[e]);
+        o[e + 1] = fmaf(ws, v.y, o[e + 1]);
+        o[e + 2] = fmaf(ws, v.z, o[e + 2]);
+        o[e + 3] = fmaf(ws, v.w, o[e + 3]);
+      }
+    }
+    if (grp == 0) {
+      const float inv = wsum > 0.f ? 1.0f / wsum : 0.f;
+      float* dst = a.out + ((size_t)r * a.n_heads + h) * DH + sub * VEC;
+#pragma unroll
+      for (int e = 0; e < VEC; e += 4)
+        *reinterpret_cast<float4*>(dst + e) = make_float4(o[e] * inv, o[e + 1] * inv, o[e + 2] * inv, o[e + 3] * inv);
+    }
+  }
+}
+
+template <typename T>
+__global__ void kv_append_kernel(T* kv, const T* k_new, const T* v_new, long n_bh, int dh, int max_buf, int pos) {
+  const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n_bh * dh) return;
+  const long bh = i / dh;
+  const int d = (int)(i - bh * dh);
+  T* p = kv + ((size_t)bh * max_buf + pos) * 2 * dh + d;
+  p[0] = k_new[i];
+  p[dh] = v_new[i];
+}
+
+template <typename T>
+int launch_ctx_t(const CtxAttnArgs& a, cudaStream_t s) {
+  const int rows_in_group = a.n_groups == 1 ? a.rows : a.rows_per_group;
+  dim3 grid((rows_in_group + kQB - 1) / kQB, a.n_heads, a.n_groups * a.n_splits);
+  switch (a.head_dim) {
+    case 16: ctx_attn_simt_kernel<T, 16><<<grid, kWarps * 32, 0, s>>>(a); break;
+    case 32: ctx_attn_simt_kernel<T, 32><<<grid, kWarps * 32, 0, s>>>(a); break;
+    case 64: ctx_attn_simt_kernel<T, 64><<<grid, kWarps * 32, 0, s>>>(a); break;
+    default:
+      set_error("context attention: head_dim %d not supported (16, 32, 64)", a.head_dim);
+      return ARTAB_EINVAL;
+  }
+  count_launch();
+  return check_launch("ctx_attn_simt_kernel");
+}
+
+template <typename T>
+int launch_buf_t(const BufMergeArgs& a, cudaStream_t s) {
+  const int wpb = 4;
+  const unsigned grid = (unsigned)((a.n_items + wpb - 1) / wpb);
+  switch (a.head_dim) {
+    case 16: buf_merge_kernel<T, 16><<<grid, wpb * 32, 0, s>>>(a); break;
+    case 32: buf_merge_kernel<T, 32><<<grid, wpb * 32, 0, s>>>(a); break;
+    case 64: buf_merge_kernel<T, 64><<<grid, wpb * 32, 0, s>>>(a); break;
+    default:
+      set_error("buffer attention: head_dim %d not supported (16, 32, 64)", a.head_dim);
+      return ARTAB_EINVAL;
+  }
+  count_launch();
+  return check_launch("buf_merge_kernel");
+}
+
+}  // namespace
+
+int launch_ctx_attn_simt(const CtxAttnArgs& a, cudaStream_t s) {
+  if (a.rows <= 0) return ARTAB_OK;
+  ARTAB_REQUIRE(a.n_ctx > 0 && a.n_splits >= 1, ARTAB_EINVAL, "context attention: empty context or no splits");
+  return a.dtype == ARTAB_BF16 ? launch_ctx_t<__nv_bfloat16>(a, s) : launch_ctx_t<float>(a, s);
+}
+
+int launch_buf_merge(const BufMergeArgs& a, cudaStream_t s) {
+  if (a.n_items <= 0) return ARTAB_OK;
+  return a.dtype == ARTAB_BF16 ? launch_buf_t<__nv_bfloat16>(a, s) : launch_buf_t<float>(a, s);
+}
+
+int launch_kv_append(int dtype, void* kv, const void* k_new, const void* v_new, long n_bh, int dh, int max_buf,
+                     int pos, cudaStream_t s) {
+  const long n = n_bh * dh;
+  if (n <= 0) return ARTAB_OK;
+  const unsigned grid = (unsigned)((n + 255) / 256);
+  if (dtype == ARTAB_BF16)
+    kv_append_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((__nv_bfloat16*)kv, (const __nv_bfloat16*)k_new,
+                                                        (const __nv_bfloat16*)v_new, n_bh, dh, max_buf, pos);
+  else
+    kv_append_kernel<float><<<grid, 256, 0, s>>>((float*)kv, (const float*)k_new, (const float*)v_new, n_bh, dh,
+                                                 max_buf, pos);
+  count_launch();
+  return check_launch("kv_append_kernel");
+}
+
+}  // namespace artab

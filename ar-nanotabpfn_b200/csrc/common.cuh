@@ -1,0 +1,105 @@
+// Shared helpers for the artab sm_100a kernels.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "artab.h"
+
+namespace artab {
+
+// ---- error plumbing (host) ------------------------------------------------
+void set_error(const char* fmt, ...);
+int check_launch(const char* what);
+void count_launch();
+
+#define ARTAB_REQUIRE(cond, code, ...) \
+  do {                                 \
+    if (!(cond)) {                     \
+      ::artab::set_error(__VA_ARGS__); \
+      return (code);                   \
+    }                                  \
+  } while (0)
+
+// ---- storage-type conversion ------------------------------------------------
+template <typename T>
+__device__ __forceinline__ float to_f32(T v);
+template <>
+__device__ __forceinline__ float to_f32<float>(float v) {
+  return v;
+}
+template <>
+__device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) {
+  return __bfloat162float(v);
+}
+template <typename T>
+__device__ __forceinline__ T from_f32(float v);
+template <>
+__device__ __forceinline__ float from_f32<float>(float v) {
+  return v;
+}
+template <>
+__device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) {
+  return __float2bfloat16_rn(v);
+}
+
+// 16-byte vector of storage elements -> floats
+template <typename T>
+struct Vec16;
+template <>
+struct Vec16<float> {
+  static constexpr int N = 4;
+  __device__ static __forceinline__ void load(const float* p, float* out) {
+    float4 v = *reinterpret_cast<const float4*>(p);
+    out[0] = v.x; out[1] = v.y; out[2] = v.z; out[3] = v.w;
+  }
+};
+template <>
+struct Vec16<__nv_bfloat16> {
+  static constexpr int N = 8;
+  __device__ static __forceinline__ void load(const __nv_bfloat16* p, float* out) {
+    uint4 v = *reinterpret_cast<const uint4*>(p);
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      out[2 * i] = __uint_as_float(w[i] << 16);
+      out[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+  }
+};
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
+
+// ---- how a dense kernel scatters freshly projected K / V rows -----------------
+enum KvMode : int { KV_NONE = 0, KV_PREFILL = 1, KV_DECODE = 2, KV_TF = 3 };
+
+struct KvDest {
+  int mode;          // KvMode
+  int dtype;         // ARTAB_F32 / ARTAB_BF16
+  int n_heads, head_dim;
+  // prefill: rows = G * n_ctx, row r -> (g = r / n_ctx, i = r % n_ctx)
+  void* k_ctx;       // [G][H][Ncp][Dh]   (this layer)
+  void* v_ctx;       // fp32 [G][H][Ncp][Dh] / bf16 [G][H][Dh][Ncp]
+  int n_ctx, n_ctx_pad;
+  // decode / teacher forcing: rows = B * tokens_per_stream
+  void* kv_buf;      // [B][H][T][2][Dh]  (this layer)
+  int max_buf;
+  int tokens_per_stream;  // decode: n_new (1 or 2); tf: 2*Nt
+  int n_kv_tokens;        // decode: n_new-1 (0 or 1) leading tokens are buffer rows; tf: Nt
+  int pos0;               // decode: buffer_len (position of the appended row); tf: 0
+};
+
+}  // namespace artab

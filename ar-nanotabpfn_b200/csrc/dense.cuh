@@ -1,0 +1,48 @@
+// Host-visible argument blocks of the row-local ("per token") kernels.
+#pragma once
+#include "common.cuh"
+
+namespace artab {
+
+// Which rows the embedder produces and where their inputs come from.
+enum EmbedMode : int { EMB_ROWS = 0, EMB_DECODE = 1, EMB_TF = 2 };
+
+struct EmbedArgs {
+  int mode, rows, D, F, kind;
+  const float *wx, *bx, *wy, *by, *marker, *ar_tokens;
+  // EMB_ROWS
+  const float* x;        // [rows][F]
+  const float* y;        // [rows] or null
+  const int32_t* ar_idx; // [rows] or null
+  // EMB_DECODE / EMB_TF
+  const float* xt;       // [B][Nt][F]
+  const float* yt;       // decode: samples [B][Nt]; tf: yt [B][Nt]
+  int Nt, t, n_new, S;
+  float* out;            // [rows][D]
+};
+
+struct DenseArgs {
+  int rows, D, Dff, n_comp;
+  int do_post, do_final, do_head, do_pre;
+  artab_layer_weights post_w, pre_w;
+  const float* attn;   // [rows][D]  post input
+  const float* x1_in;  // [rows][D]  post residual input
+  const float* x_in;   // [rows][D]  chain input when !do_post
+  float* x_out;        // [rows][D]  layer output (optional)
+  float* x1_out;       // [rows][D]  pre output
+  void* q_out;         // [rows][D]  pre output, cache dtype
+  KvDest kv;
+  const float *lnf_g, *lnf_b, *wa_t, *ba, *wb_t, *bb, *mean_bias, *std_bias, *weight_bias;
+  float* z_out;        // [rows][D] optional
+  int head_mode;       // 0 none, 1 sample, 2 log-pdf
+  int head_tps, head_first, out_stride, out_col;
+  const float *expo, *normal, *y_in;
+  float* y_out;
+  float* ld_out;
+  int32_t* comp_out;
+};
+
+int launch_embed(const EmbedArgs& a, cudaStream_t s);
+int launch_dense(const DenseArgs& a, cudaStream_t s);
+
+}  // namespace artab

@@ -1,0 +1,334 @@
+// Row-local fp32 kernels: embedder, the fused per-token layer chain
+// (out-proj + LN2 + MLP + LN3 [+ final LN + mixture head] [+ next layer's
+// feature-attention fold + LN1 + QKV + KV-cache scatter]) and the mixture head.
+//
+// Every token row is independent, so one CTA owns R rows and walks the whole
+// chain with the activations resident in shared memory; weights are streamed
+// from L2 with coalesced reads (they are stored [in][out]).  All arithmetic is
+// plain fp32 FMA: this is the path that has to agree with the fp32 CPU
+// reference to 1e-5 on the log density, so no TF32 / bf16 operand rounding.
+#include "dense.cuh"
+
+namespace artab {
+
+namespace {
+
+constexpr int kRows = 8;  // rows per CTA
+
+__device__ __forceinline__ float gelu_erf(float v) { return 0.5f * v * (1.0f + erff(v * 0.70710678118654752f)); }
+
+// out[r][n] = act(bias[n] + sum_k a[r][k] * Wt[k][n]) for the CTA's rows (a in shared memory).
+template <int R>
+__device__ __forceinline__ void gemm_rows(const float* s_a, int lda, const float* __restrict__ Wt, int K, int N,
+                                          const float* __restrict__ bias, bool gelu, float* s_o, int ldo) {
+  for (int n = threadIdx.x; n < N; n += blockDim.x) {
+    float acc[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) acc[r] = 0.f;
+    const float* w = Wt + n;
+#pragma unroll 2
+    for (int k = 0; k < K; k += 4) {
+      const float w0 = __ldg(w + (size_t)(k + 0) * N);
+      const float w1 = __ldg(w + (size_t)(k + 1) * N);
+      const float w2 = __ldg(w + (size_t)(k + 2) * N);
+      const float w3 = __ldg(w + (size_t)(k + 3) * N);
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        const float4 a = *reinterpret_cast<const float4*>(s_a + r * lda + k);
+        acc[r] = fmaf(a.x, w0, acc[r]);
+        acc[r] = fmaf(a.y, w1, acc[r]);
+        acc[r] = fmaf(a.z, w2, acc[r]);
+        acc[r] = fmaf(a.w, w3, acc[r]);
+      }
+    }
+    const float b = bias ? __ldg(bias + n) : 0.f;
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      float v = acc[r] + b;
+      if (gelu) v = gelu_erf(v);
+      s_o[r * ldo + n] = v;
+    }
+  }
+  __syncthreads();
+}
+
+// dst[r][:] = LayerNorm(a[r][:] + b[r][:]) * gamma + beta   (b optional; a, b, dst may alias row-wise)
+template <int R>
+__device__ __forceinline__ void ln_rows(float* dst, int ldd, const float* a, int lda, const float* b, int ldb,
+                                        const float* __restrict__ gamma, const float* __restrict__ beta, int D,
+                                        int n_valid) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  for (int r = warp; r < R; r += nw) {
+    if (r >= n_valid) continue;
+    float s = 0.f;
+    for (int d = lane; d < D; d += 32) {
+      float v = a[r * lda + d];
+      if (b) v += b[(size_t)r * ldb + d];
+      s += v;
+    }
+    const float mean = warp_sum(s) / (float)D;
+    float ss = 0.f;
+    for (int d = lane; d < D; d += 32) {
+      float v = a[r * lda + d];
+      if (b) v += b[(size_t)r * ldb + d];
+      v -= mean;
+      ss = fmaf(v, v, ss);
+    }
+    const float rstd = 1.0f / sqrtf(warp_sum(ss) / (float)D + 1e-5f);
+    for (int d = lane; d < D; d += 32) {
+      float v = a[r * lda + d];
+      if (b) v += b[(size_t)r * ldb + d];
+      dst[r * ldd + d] = (v - mean) * rstd * __ldg(gamma + d) + __ldg(beta + d);
+    }
+  }
+  __syncthreads();
+}
+
+template <typename T>
+__device__ __forceinline__ void scatter_kv(const KvDest& kv, long row, int c, float kval, float vval) {
+  const int h = c / kv.head_dim, d = c - h * kv.head_dim;
+  if (kv.mode == KV_PREFILL) {
+    const long g = row / kv.n_ctx, i = row - g * kv.n_ctx;
+    const size_t base = ((size_t)(g * kv.n_heads + h) * kv.n_ctx_pad);
+    reinterpret_cast<T*>(kv.k_ctx)[(base + i) * kv.head_dim + d] = from_f32<T>(kval);
+    if (kv.dtype == ARTAB_BF16) {  // transposed [.., Dh][Ncp]
+      reinterpret_cast<T*>(kv.v_ctx)[((size_t)(g * kv.n_heads + h) * kv.head_dim + d) * kv.n_ctx_pad + i] =
+          from_f32<T>(vval);
+    } else {
+      reinterpret_cast<T*>(kv.v_ctx)[(base + i) * kv.head_dim + d] = from_f32<T>(vval);
+    }
+  } else {
+    const long b = row / kv.tokens_per_stream;
+    const int j = (int)(row - b * kv.tokens_per_stream);
+    if (j >= kv.n_kv_tokens) return;
+    const int pos = kv.pos0 + j;
+    T* p = reinterpret_cast<T*>(kv.kv_buf) +
+           (((size_t)(b * kv.n_heads + h) * kv.max_buf + pos) * 2) * kv.head_dim + d;
+    p[0] = from_f32<T>(kval);
+    p[kv.head_dim] = from_f32<T>(vval);
+  }
+}
+
+// One warp per head row: mixture parameters from raw[3K], then sample or log-pdf.
+__device__ __forceinline__ void head_row(const DenseArgs& a, const float* raw, long row) {
+  const int lane = threadIdx.x & 31;
+  const int K = a.n_comp;
+  const long b = row / a.head_tps;
+  const int j = (int)(row - b * a.head_tps);
+  if (j < a.head_first) return;
+  const long oidx = b * a.out_stride + a.out_col + (j - a.head_first);
+  float mean = 0.f, stdv = 1.f, lw = -INFINITY;
+  if (lane < K) {
+    mean = raw[3 * lane] + __ldg(a.mean_bias + lane);
+    const float sr = raw[3 * lane + 1] + __ldg(a.std_bias + lane);
+    const float sp = sr > 20.f ? sr : log1pf(expf(sr));  // F.softplus, beta 1, threshold 20
+    stdv = fminf(sp, 2.0f) + 1e-3f;
+    lw = raw[3 * lane + 2] + __ldg(a.weight_bias + lane);
+  }
+  const float mx = warp_max(lw);
+  const float se = warp_sum(lane < K ? expf(lw - mx) : 0.f);
+  const float logw = lw - mx - logf(se);  // log_softmax
+  float y;
+  if (a.head_mode == 1) {
+    // torch.multinomial(w, 1) == argmax_k(w_k / Exp(1)_k); first maximum wins
+    float ratio = -1.f;
+    if (lane < K) ratio = expf(logw) / __ldg(a.expo + b * K + lane);
+    int best = lane;
+    float bv = ratio;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, best, o);
+      if (ov > bv || (ov == bv && oi < best)) {
+        bv = ov;
+        best = oi;
+      }
+    }
+    const float m_sel = __shfl_sync(0xffffffffu, mean, best);
+    const float s_sel = __shfl_sync(0xffffffffu, stdv, best);
+    y = m_sel + s_sel * __ldg(a.normal + b);
+    if (lane == 0) {
+      a.y_out[oidx] = y;
+      if (a.comp_out) a.comp_out[oidx] = best;
+    }
+  } else {
+    y = __ldg(a.y_in + oidx);
+  }
+  if (a.ld_out) {
+    float lp = -INFINITY;
+    if (lane < K) {
+      const float zz = (y - mean) / stdv;
+      lp = -0.5f * (1.8378770664093453f + 2.0f * logf(stdv) + zz * zz) + logw;
+    }
+    const float m2 = warp_max(lp);
+    const float s2 = warp_sum(lane < K ? expf(lp - m2) : 0.f);
+    if (lane == 0) a.ld_out[oidx] = m2 + logf(s2);
+  }
+}
+
+template <int R>
+__global__ void __launch_bounds__(256) dense_chain_kernel(const DenseArgs a) {
+  extern __shared__ __align__(16) float smem[];
+  const int D = a.D, Dff = a.Dff;
+  const int wide = max(3 * D, Dff);
+  float* s_x = smem;              // [R][D]
+  float* s_t = s_x + R * D;       // [R][D]
+  float* s_h = s_t + R * D;       // [R][wide]
+  const long row0 = (long)blockIdx.x * R;
+  const int n_valid = (int)min((long)R, (long)a.rows - row0);
+  float* cur = s_x;
+
+  if (a.do_post) {
+    // s_h[0..R*D) <- attention output rows
+    for (int i = threadIdx.x; i < R * D; i += blockDim.x) {
+      const int r = i / D;
+      s_h[i] = r < n_valid ? a.attn[(size_t)row0 * D + i] : 0.f;
+    }
+    __syncthreads();
+    gemm_rows<R>(s_h, D, a.post_w.wo_t, D, D, nullptr, false, s_t, D);
+    ln_rows<R>(s_x, D, s_t, D, a.x1_in + (size_t)row0 * D, D, a.post_w.ln2_g, a.post_w.ln2_b, D, n_valid);
+    gemm_rows<R>(s_x, D, a.post_w.w1_t, D, Dff, a.post_w.b1, true, s_h, wide);
+    gemm_rows<R>(s_h, wide, a.post_w.w2_t, Dff, D, a.post_w.b2, false, s_t, D);
+    ln_rows<R>(s_x, D, s_x, D, s_t, D, a.post_w.ln3_g, a.post_w.ln3_b, D, n_valid);
+    if (a.x_out) {
+      for (int i = threadIdx.x; i < n_valid * D; i += blockDim.x) a.x_out[(size_t)row0 * D + i] = s_x[i];
+    }
+  } else {
+    for (int i = threadIdx.x; i < R * D; i += blockDim.x) {
+      const int r = i / D;
+      s_x[i] = r < n_valid ? a.x_in[(size_t)row0 * D + i] : 0.f;
+    }
+    __syncthreads();
+  }
+
+  if (a.do_final) {
+    ln_rows<R>(s_t, D, s_x, D, nullptr, 0, a.lnf_g, a.lnf_b, D, n_valid);
+    cur = s_t;
+    if (a.z_out) {
+      for (int i = threadIdx.x; i < n_valid * D; i += blockDim.x) a.z_out[(size_t)row0 * D + i] = s_t[i];
+    }
+  }
+
+  if (a.do_head) {
+    float* s_raw = (cur == s_x) ? s_t : s_x;
+    gemm_rows<R>(cur, D, a.wa_t, D, Dff, a.ba, true, s_h, wide);
+    gemm_rows<R>(s_h, wide, a.wb_t, Dff, 3 * a.n_comp, a.bb, false, s_raw, D);
+    const int warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    for (int r = warp; r < n_valid; r += nw) head_row(a, s_raw + r * D, row0 + r);
+    return;
+  }
+
+  if (a.do_pre) {
+    // feature attention over one token == out_proj(v_proj(x)); folded into wf_t
+    gemm_rows<R>(s_x, D, a.pre_w.wf_t, D, D, nullptr, false, s_t, D);
+    ln_rows<R>(s_x, D, s_x, D, s_t, D, a.pre_w.ln1_g, a.pre_w.ln1_b, D, n_valid);
+    for (int i = threadIdx.x; i < n_valid * D; i += blockDim.x) a.x1_out[(size_t)row0 * D + i] = s_x[i];
+    gemm_rows<R>(s_x, D, a.pre_w.wqkv_t, D, 3 * D, nullptr, false, s_h, wide);
+    const bool bf = a.kv.dtype == ARTAB_BF16;
+    for (int i = threadIdx.x; i < n_valid * D; i += blockDim.x) {
+      const int r = i / D, c = i - r * D;
+      const float qv = s_h[r * wide + c];
+      if (bf)
+        reinterpret_cast<__nv_bfloat16*>(a.q_out)[(size_t)row0 * D + i] = __float2bfloat16_rn(qv);
+      else
+        reinterpret_cast<float*>(a.q_out)[(size_t)row0 * D + i] = qv;
+      if (a.kv.mode != KV_NONE) {
+        const float kv_k = s_h[r * wide + D + c], kv_v = s_h[r * wide + 2 * D + c];
+        if (bf)
+          scatter_kv<__nv_bfloat16>(a.kv, row0 + r, c, kv_k, kv_v);
+        else
+          scatter_kv<float>(a.kv, row0 + r, c, kv_k, kv_v);
+      }
+    }
+  }
+}
+
+__global__ void __launch_bounds__(128) embed_kernel(const EmbedArgs a) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long row = (long)blockIdx.x * (blockDim.x >> 5) + warp;
+  if (row >= a.rows) return;
+  const float* xr;
+  float yv = 0.f;
+  bool has_y = false;
+  int kind = a.kind, ar = -1;
+  if (a.mode == EMB_ROWS) {
+    xr = a.x + (size_t)row * a.F;
+    if (a.y) {
+      yv = a.y[row];
+      has_y = true;
+    }
+    if (a.ar_idx) ar = a.ar_idx[row];
+  } else if (a.mode == EMB_DECODE) {
+    // step t: [buffer(x_{t-1}, y_{t-1}, ar = t mod S), target(x_t)]; t = 0: target only
+    const long b = row / a.n_new;
+    const int j = (int)(row - b * a.n_new);
+    if (a.n_new == 2 && j == 0) {
+      xr = a.xt + ((size_t)b * a.Nt + (a.t - 1)) * a.F;
+      yv = a.yt[(size_t)b * a.Nt + (a.t - 1)];
+      has_y = true;
+      kind = ARTAB_MARK_BUFFER;
+      ar = a.t % a.S;
+    } else {
+      xr = a.xt + ((size_t)b * a.Nt + a.t) * a.F;
+      kind = ARTAB_MARK_TARGET;
+    }
+  } else {
+    // teacher forcing: [Buffer_0..Buffer_{Nt-1}, Target_0..Target_{Nt-1}], buffer j carries ar = j mod S
+    const long b = row / (2 * a.Nt);
+    const int j = (int)(row - b * 2 * a.Nt);
+    if (j < a.Nt) {
+      xr = a.xt + ((size_t)b * a.Nt + j) * a.F;
+      yv = a.yt[(size_t)b * a.Nt + j];
+      has_y = true;
+      kind = ARTAB_MARK_BUFFER;
+      ar = j % a.S;
+    } else {
+      xr = a.xt + ((size_t)b * a.Nt + (j - a.Nt)) * a.F;
+      kind = ARTAB_MARK_TARGET;
+    }
+  }
+  float s = 0.f;
+  for (int f = lane; f < a.F; f += 32) s += xr[f];
+  const float xm = warp_sum(s) / (float)a.F;
+  for (int d = lane; d < a.D; d += 32) {
+    float e = fmaf(xm, __ldg(a.wx + d), __ldg(a.bx + d));
+    if (has_y) e += fmaf(yv, __ldg(a.wy + d), __ldg(a.by + d));
+    e += __ldg(a.marker + kind * a.D + d);
+    if (ar >= 0) e += __ldg(a.ar_tokens + ar * a.D + d);
+    a.out[(size_t)row * a.D + d] = e;
+  }
+}
+
+}  // namespace
+
+int launch_embed(const EmbedArgs& a, cudaStream_t s) {
+  if (a.rows <= 0) return ARTAB_OK;
+  const int wpb = 4;
+  embed_kernel<<<(a.rows + wpb - 1) / wpb, wpb * 32, 0, s>>>(a);
+  count_launch();
+  return check_launch("embed_kernel");
+}
+
+int launch_dense(const DenseArgs& a, cudaStream_t s) {
+  if (a.rows <= 0) return ARTAB_OK;
+  ARTAB_REQUIRE(a.D % 32 == 0 && a.Dff % 4 == 0 && a.D >= 32, ARTAB_EINVAL,
+                "dense chain: d_model must be a multiple of 32 and d_ff a multiple of 4 (got %d, %d)", a.D, a.Dff);
+  ARTAB_REQUIRE(3 * a.n_comp <= a.D && a.n_comp <= 32, ARTAB_EINVAL, "dense chain: need 3*K <= d_model and K <= 32");
+  const int wide = 3 * a.D > a.Dff ? 3 * a.D : a.Dff;
+  const size_t smem = (size_t)kRows * (2 * a.D + wide) * sizeof(float);
+  static size_t configured = 0;
+  if (smem > configured) {
+    cudaError_t e = cudaFuncSetAttribute(dense_chain_kernel<kRows>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)smem);
+    ARTAB_REQUIRE(e == cudaSuccess, ARTAB_ELAUNCH, "dense chain: %zu bytes of shared memory refused: %s", smem,
+                  cudaGetErrorString(e));
+    configured = smem;
+  }
+  const int threads = a.D <= 256 ? a.D : 256;
+  const int grid = (a.rows + kRows - 1) / kRows;
+  dense_chain_kernel<kRows><<<grid, threads, smem, s>>>(a);
+  count_launch();
+  return check_launch("dense_chain_kernel");
+}
+
+}  // namespace artab

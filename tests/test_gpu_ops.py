@@ -1,0 +1,143 @@
+"""GPU parity of the single operators (through the C ABI) against the golden
+vectors of the reference and against the CPU oracle."""
+import pytest
+import torch
+
+import artab_oracle as orc
+from util import load_golden, ref_attention
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ops():
+    return load_golden("ops.pt")
+
+
+@pytest.fixture(scope="module")
+def tk():
+    from ar_tabpfn.model import triton_kernels
+    assert triton_kernels.triton_available()
+    return triton_kernels
+
+
+def cu(t):
+    return t.cuda()
+
+
+@pytest.mark.parametrize("splits", [1, 3])
+def test_context_attention_fp32_golden(ops, tk, splits):
+    for c in ops["attn"]:
+        out, lse = tk.triton_context_attention(cu(c["q"]), cu(c["k_ctx"]), cu(c["v_ctx"]), n_splits=splits)
+        torch.testing.assert_close(out.cpu(), c["out_ctx"], atol=1e-5, rtol=1e-5)
+        torch.testing.assert_close(lse.cpu(), c["lse_ctx"], atol=1e-5, rtol=1e-5)
+
+
+def test_context_attention_strided_views(ops, tk):
+    """q arrives as a transpose of [B,N,H,Dh] in the predictor (a non-contiguous view)."""
+    c = ops["attn"][0]
+    q = cu(c["q"]).transpose(1, 2).contiguous().transpose(1, 2)
+    assert not q.is_contiguous()
+    out, _ = tk.triton_context_attention(q, cu(c["k_ctx"]), cu(c["v_ctx"]))
+    torch.testing.assert_close(out.cpu(), c["out_ctx"], atol=1e-5, rtol=1e-5)
+
+
+def test_merge_fp32_golden(ops, tk):
+    for c in ops["attn"]:
+        if "merged" not in c:
+            continue
+        got = tk.merge_attention_outputs(cu(c["out_ctx"]), cu(c["lse_ctx"]), cu(c["out_buf"]), cu(c["lse_buf"]))
+        torch.testing.assert_close(got.cpu(), c["merged"], atol=1e-5, rtol=1e-5)
+
+
+def test_merge_dominant_and_equal_lse(tk):
+    B, H, Lq, Dh = 2, 2, 1, 16
+    a, b = torch.ones(B, H, Lq, Dh).cuda(), 3 * torch.ones(B, H, Lq, Dh).cuda()
+    big, small = torch.full((B, H, Lq), 50.0).cuda(), torch.full((B, H, Lq), -50.0).cuda()
+    torch.testing.assert_close(tk.merge_attention_outputs(a, big, b, small), a)
+    torch.testing.assert_close(tk.merge_attention_outputs(a, small, b, small), 2 * torch.ones_like(a))
+    ninf = torch.full((B, H, Lq), float("-inf")).cuda()
+    torch.testing.assert_close(tk.merge_attention_outputs(a, small, b, ninf), a)
+
+
+def test_hybrid_fp32_golden(ops, tk):
+    for c in ops["attn"]:
+        got = tk.hybrid_attention(cu(c["q"]), cu(c["k_ctx"]), cu(c["v_ctx"]), cu(c["k_buf"]), cu(c["v_buf"]))
+        torch.testing.assert_close(got.cpu(), c["hybrid"], atol=1e-5, rtol=1e-5)
+
+
+def test_teacher_forcing_fp32_golden(ops, tk):
+    for c in ops["tf"]:
+        got = tk.hybrid_teacher_forcing_attention(cu(c["q"]), cu(c["k_ctx"]), cu(c["v_ctx"]), cu(c["k_buf"]),
+                                                  cu(c["v_buf"]), c["num_targets"])
+        torch.testing.assert_close(got.cpu(), c["hybrid"], atol=1e-5, rtol=1e-5)
+    with pytest.raises(ValueError):
+        c = ops["tf"][0]
+        tk.hybrid_teacher_forcing_attention(cu(c["q"]), cu(c["k_ctx"]), cu(c["v_ctx"]), cu(c["k_buf"]),
+                                            cu(c["v_buf"]), c["num_targets"] + 1)
+
+
+@pytest.mark.parametrize("shape", [(37, 4, 1, 64, 32, 5), (64, 4, 2, 300, 32, 63), (130, 6, 1, 1024, 32, 17),
+                                   (5, 2, 2, 100, 16, 9), (9, 2, 1, 77, 64, 3)])
+def test_hybrid_bf16_vs_fp32_torch(tk, shape):
+    """bf16 mode: attention outputs within 1e-2 relative of fp32 attention on the same bf16 tensors."""
+    B, H, Lq, Nc, Dh, Nb = shape
+    g = torch.Generator().manual_seed(1)
+    q, k, v = (torch.randn(*s, generator=g).bfloat16().cuda() for s in ((B, H, Lq, Dh), (H, Nc, Dh), (H, Nc, Dh)))
+    kb, vb = (torch.randn(B, H, Nb, Dh, generator=g).bfloat16().cuda() for _ in range(2))
+    got = tk.hybrid_attention(q, k, v, kb, vb).float()
+    kf = torch.cat([k.unsqueeze(0).expand(B, -1, -1, -1), kb], dim=2)
+    vf = torch.cat([v.unsqueeze(0).expand(B, -1, -1, -1), vb], dim=2)
+    want, _ = ref_attention(q, kf, vf)
+    err = (got - want).abs().max() / want.abs().max()
+    assert err < 1e-2, err
+    out_c, lse_c = tk.triton_context_attention(q, k, v)
+    want_c, want_l = ref_attention(q, k.unsqueeze(0).expand(B, -1, -1, -1), v.unsqueeze(0).expand(B, -1, -1, -1))
+    assert (out_c.float() - want_c).abs().max() / want_c.abs().max() < 1e-2
+    torch.testing.assert_close(lse_c, want_l, atol=2e-3, rtol=2e-3)
+
+
+def test_kv_append_in_place():
+    import ctypes as C
+    from ar_tabpfn import _lib
+    lib = _lib.lib()
+    B, H, Dh, T = 5, 3, 32, 7
+    for dt in (torch.float32, torch.bfloat16):
+        kv = torch.zeros(B, H, T, 2, Dh, device="cuda", dtype=dt)
+        ptr0 = kv.data_ptr()
+        want = kv.clone()
+        for pos in (0, 3, 6):
+            k, v = torch.randn(B, H, Dh, device="cuda").to(dt), torch.randn(B, H, Dh, device="cuda").to(dt)
+            _lib.check(lib.artab_kv_append(_lib.dtype_code(dt), _lib.ptr(kv), _lib.ptr(k), _lib.ptr(v), B, H, Dh, T,
+                                           pos, _lib.stream_ptr()))
+            want[:, :, pos, 0], want[:, :, pos, 1] = k, v
+        assert kv.data_ptr() == ptr0 and torch.equal(kv, want)
+        with pytest.raises(ValueError):
+            _lib.check(lib.artab_kv_append(_lib.dtype_code(dt), _lib.ptr(kv), _lib.ptr(k), _lib.ptr(v), B, H, Dh, T,
+                                           T, _lib.stream_ptr()))
+
+
+def test_embedder_and_head_vs_oracle():
+    from util import build_model
+    fx = load_golden("config1.pt")
+    m, sd = build_model(fx)
+    x, y = fx["xc"][:2, :9], fx["yc"][:2, :9]
+    for kind, fn, yy, mk in (("context", m.embedder.embed_context, y, orc.MARKER_CONTEXT),
+                             ("buffer", m.embedder.embed_buffer, y, orc.MARKER_BUFFER),
+                             ("target", lambda a, b: m.embedder.embed_target(a), None, orc.MARKER_TARGET)):
+        got = fn(x.cuda(), None if yy is None else yy.cuda())
+        torch.testing.assert_close(got.cpu(), orc.embed_rows(sd, x, yy, mk), atol=1e-6, rtol=1e-6)
+    z = fx["z_shared"]
+    yt = fx["samples_shared"]
+    got = m.head.log_likelihood(z.cuda(), yt.unsqueeze(-1).cuda())
+    torch.testing.assert_close(got.cpu(), fx["sample_logdens_shared"], atol=3e-5, rtol=1e-5)
+    # sampling consumes the generator like the reference: Exp(1) [B*T,K] then N(0,1) [B,T,1,1]
+    torch.manual_seed(3)
+    ys = m.head.sample(z.cuda())
+    torch.manual_seed(3)
+    B, T, _ = z.shape
+    expo = torch.empty(B * T, 5, device="cuda").exponential_(1)
+    normal = torch.randn(B, T, 1, 1, device="cuda")
+    mean, std, w, _ = orc.head_params(sd, z)
+    want, _ = orc.head_sample(mean, std, w, expo.cpu().view(B, T, 5), normal.cpu().view(B, T))
+    torch.testing.assert_close(ys.cpu().view(B, T), want, atol=1e-5, rtol=1e-5)
