@@ -97,6 +97,8 @@ class ARTabPFNPredictor:
             device = device or param.device
             dtype = dtype or param.dtype
         self._device = torch.device(device)
+        if self._device.type == "cuda" and self._device.index is None:
+            self._device = torch.device("cuda", torch.cuda.current_device())
         self._dtype = dtype
         self._batch = int(batch_size)
         self._max_seq = int(max_seq_len)

@@ -17,6 +17,9 @@ from torch import Tensor
 from .. import _lib
 
 
+last_status = None
+
+
 def triton_available() -> bool:
     """True when the CUDA library can be used (the name is the reference's)."""
     try:
@@ -66,7 +69,9 @@ def _context_partials(qr: Tensor, k: Tensor, v: Tensor, Nc: int, Ncp: int, rows_
     G = k.shape[0]
     out = torch.empty(n_splits, rows, H, Dh, device=qr.device, dtype=torch.float32)
     lse = torch.empty(n_splits, rows, H, device=qr.device, dtype=torch.float32)
+    global last_status
     status = torch.zeros(1, device=qr.device, dtype=torch.int32)
+    last_status = status  # non-zero after the launch completes = a bounded device-side wait gave up
     _lib.check(lib.artab_context_attention(_lib.dtype_code(qr.dtype), _lib.ptr(qr), _lib.ptr(k), _lib.ptr(v), rows,
                                            rows_per_group, G, H, Dh, Nc, Ncp, n_splits, _lib.ptr(out),
                                            _lib.ptr(lse), _lib.ptr(status), _lib.stream_ptr()))

@@ -1,6 +1,481 @@
-// placeholder until the tcgen05 kernel lands
+// Shared-context attention on the 5th-generation tensor cores (sm_100a).
+//
+// Queries of every sample stream are stacked into 128-row M tiles and contracted
+// against the shared context K/V: S = Q.K^T and O = P.V are tcgen05.mma
+// instructions with the accumulators in tensor memory (TMEM); Q, K and V^T tiles
+// arrive in shared memory by TMA (plain loads, no cluster multicast) in the
+// swizzled K-major layouts the MMA descriptors name.  Softmax runs on four warps
+// that own one query row per thread (TMEM lane == row), keeps the running
+// max / sum / output in registers and hands P back to the tensor core through
+// TMEM (P aliases the S columns as packed bf16).
+//
+// One CTA = one (M tile, head, context group, key split).  Warp 0 issues TMA,
+// warp 1 issues MMA and owns the TMEM allocation, warps 2-5 do softmax.  Two
+// CTAs are resident per SM (256 TMEM columns each), so the MMA of one overlaps
+// the softmax of the other.  Every mbarrier wait is bounded: on expiry the CTA
+// raises its abort flag, records a code in the status word, drains its own
+// copies, frees its TMEM and returns.
+//
+// Output per (split, row, head): normalised O [32] fp32 and the natural-log LSE,
+// merged later with the private-buffer pass (buf_merge_kernel).
+#include <cuda.h>
+
 #include "attn.cuh"
+
 namespace artab {
-bool ctx_attn_tc_supported(int, int) { return false; }
-int launch_ctx_attn_tc(const CtxAttnArgs&, cudaStream_t) { set_error("tcgen05 context attention not built"); return ARTAB_EINVAL; }
+
+namespace {
+
+constexpr int BM = 128;       // query rows per tile
+constexpr int BN = 128;       // keys per tile
+constexpr int DH = 32;        // head dim this kernel is built for
+constexpr int NSTAGE = 4;     // K/V pipeline depth
+constexpr int kThreads = 192;
+constexpr uint32_t kTmemCols = 256;
+constexpr uint32_t kColS = 0;    // S: 128 fp32 columns; P (packed bf16) aliases columns [0, 64)
+constexpr uint32_t kColO = 128;  // O tile: 32 fp32 columns
+constexpr long long kWaitCycles = 2000000000LL;  // about one second
+
+struct __align__(1024) Smem {
+  uint8_t q[BM * 64];               // [128 rows][32 bf16], 64-byte swizzle
+  uint8_t k[NSTAGE][BN * 64];       // [128 keys][32 bf16], 64-byte swizzle
+  uint8_t v[NSTAGE][2][32 * 128];   // V^T: two boxes of [32 dims][64 keys], 128-byte swizzle
+  uint64_t q_full, s_full, p_full, o_full;
+  uint64_t kv_full[NSTAGE], kv_empty[NSTAGE];
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* b, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(b)), "r"(count) : "memory");
 }
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* b, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(b)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* b) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(b)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint64_t* b, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(b)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait: false when the CTA is aborting (this wait or another one gave up).
+__device__ __forceinline__ bool mbar_wait(uint64_t* b, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_try(b, parity)) return true;
+  const long long t0 = clock64();
+  for (;;) {
+    if (mbar_try(b, parity)) return true;
+    if (*abort_flag) return false;
+    if (clock64() - t0 > kWaitCycles) {
+      *abort_flag = 1;
+      return false;
+    }
+  }
+}
+
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* tm, int c0, int c1, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(tm), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
+      : "memory");
+}
+
+// K-major shared-memory matrix descriptor: rows of `swizzle` bytes, 8-row groups `sbo` bytes apart.
+constexpr uint64_t kLayoutSw128 = 2, kLayoutSw64 = 4;
+__device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t sbo_bytes, uint64_t layout) {
+  uint64_t d = (uint64_t)((saddr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)1 << 16;                  // leading byte offset: unused for swizzled K-major
+  d |= (uint64_t)(sbo_bytes >> 4) << 32;   // stride byte offset
+  d |= (uint64_t)1 << 46;                  // descriptor version (sm_100)
+  d |= layout << 61;
+  return d;
+}
+
+// kind::f16 instruction descriptor: fp32 accumulate, bf16 A and B, both K-major.
+constexpr uint32_t make_idesc(int M, int N) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+}
+
+__device__ __forceinline__ void umma_ss(uint32_t d_tmem, uint64_t a, uint64_t b, uint32_t idesc, uint32_t acc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a), "l"(b), "r"(idesc), "r"(acc)
+      : "memory");
+}
+__device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b, uint32_t idesc, uint32_t acc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b), "r"(idesc), "r"(acc)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,"
+      "%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t* r) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+        "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+struct TcParams {
+  int rows, rows_per_group, n_groups, n_heads, n_ctx, n_ctx_pad, n_splits;
+  float scale_log2e;
+  float* out;
+  float* lse;
+  int32_t* status;
+};
+
+// Softmax of one 128 x 128 score tile for one row (thread).  MASKED: columns >= n_valid are -inf.
+template <bool MASKED>
+__device__ __forceinline__ void softmax_tile(uint32_t t_row, float sc, int n_valid, float& m, float& l, float& alpha) {
+  uint32_t r[32];
+  float mx = -INFINITY;
+#pragma unroll 1  // one 32-column chunk in flight: keeps the register count low enough for two CTAs per SM
+  for (int c = 0; c < 4; ++c) {
+    tmem_ld32(t_row + kColS + 32 * c, r);
+    tmem_wait_ld();
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      float s = __uint_as_float(r[i]);
+      if (MASKED && 32 * c + i >= n_valid) s = -INFINITY;
+      mx = fmaxf(mx, s);
+    }
+  }
+  const float m_new = fmaxf(m, mx * sc);  // at least one column of every tile is valid
+  alpha = ex2_approx(m - m_new);          // m = -inf on the first tile gives 0
+  float sum = 0.f;
+#pragma unroll 1
+  for (int c = 0; c < 4; ++c) {
+    tmem_ld32(t_row + kColS + 32 * c, r);
+    tmem_wait_ld();
+    uint32_t pk[16];
+#pragma unroll
+    for (int i = 0; i < 32; i += 2) {
+      float p0 = ex2_approx(fmaf(__uint_as_float(r[i]), sc, -m_new));
+      float p1 = ex2_approx(fmaf(__uint_as_float(r[i + 1]), sc, -m_new));
+      if (MASKED) {
+        if (32 * c + i >= n_valid) p0 = 0.f;
+        if (32 * c + i + 1 >= n_valid) p1 = 0.f;
+      }
+      sum += p0 + p1;
+      pk[i >> 1] = pack_bf16(p0, p1);
+    }
+    // P chunk c lands in columns [16c, 16c+16): S columns already consumed by this thread
+    tmem_st16(t_row + kColS + 16 * c, pk);
+  }
+  l = l * alpha + sum;
+  m = m_new;
+}
+
+__global__ void __launch_bounds__(kThreads, 2)
+ctx_attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                   const __grid_constant__ CUtensorMap tm_v, const TcParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  Smem* sm = reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int h = blockIdx.y;
+  const int g = blockIdx.z / p.n_splits, split = blockIdx.z - g * p.n_splits;
+  const int rows_in_group = p.n_groups == 1 ? p.rows : p.rows_per_group;
+  const long group_row0 = p.n_groups == 1 ? 0 : (long)g * p.rows_per_group;
+  const int m0 = blockIdx.x * BM;
+
+  const int tiles = (p.n_ctx + BN - 1) / BN;
+  const int tps = (tiles + p.n_splits - 1) / p.n_splits;
+  const int tile_begin = split * tps;
+  const int tile_end = min(tiles, tile_begin + tps);
+  const int nt = tile_end - tile_begin;
+
+  // softmax threads: TMEM lane (= tile row) owned by this thread
+  const int lane_base = 32 * (warp & 3);
+  const int row = lane_base + lane;
+  const bool row_valid = warp >= 2 && (m0 + row) < rows_in_group;
+  const size_t out_row = ((size_t)split * p.rows + group_row0 + m0 + row) * p.n_heads + h;
+
+  if (nt <= 0) {  // empty split: contributes nothing to the merge
+    if (row_valid) {
+      float4* o = reinterpret_cast<float4*>(p.out + out_row * DH);
+#pragma unroll
+      for (int i = 0; i < DH / 4; ++i) o[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+      p.lse[out_row] = -INFINITY;
+    }
+    return;
+  }
+
+  if (threadIdx.x == 0) {
+    mbar_init(&sm->q_full, 1);
+    mbar_init(&sm->s_full, 1);
+    mbar_init(&sm->p_full, 128);
+    mbar_init(&sm->o_full, 1);
+    for (int s = 0; s < NSTAGE; ++s) {
+      mbar_init(&sm->kv_full[s], 1);
+      mbar_init(&sm->kv_empty[s], 1);
+    }
+    sm->abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm->tmem_base)),
+                 "r"(kTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = sm->tmem_base;
+  volatile int* abort_flag = &sm->abort_flag;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      mbar_expect_tx(&sm->q_full, BM * 64);
+      tma_load_2d(sm->q, &tm_q, h * DH, (int)(group_row0 + m0), &sm->q_full);
+      const int krow0 = (g * p.n_heads + h) * p.n_ctx_pad;
+      const int vrow0 = (g * p.n_heads + h) * DH;
+      int issued = 0;
+      for (int j = 0; j < nt; ++j) {
+        const int st = j % NSTAGE;
+        if (j >= NSTAGE && !mbar_wait(&sm->kv_empty[st], ((j / NSTAGE) + 1) & 1, abort_flag)) break;
+        const int key0 = (tile_begin + j) * BN;
+        mbar_expect_tx(&sm->kv_full[st], BN * 64 + 2 * 32 * 128);
+        tma_load_2d(sm->k[st], &tm_k, 0, krow0 + key0, &sm->kv_full[st]);
+        tma_load_2d(sm->v[st][0], &tm_v, key0, vrow0, &sm->kv_full[st]);
+        tma_load_2d(sm->v[st][1], &tm_v, key0 + 64, vrow0, &sm->kv_full[st]);
+        issued = j + 1;
+      }
+      if (*abort_flag) {  // drain our own copies before the CTA may exit
+        {
+          const long long t0 = clock64();
+          while (!mbar_try(&sm->q_full, 0) && clock64() - t0 < kWaitCycles) {
+          }
+        }
+        for (int j = max(0, issued - NSTAGE); j < issued; ++j) {
+          const long long t0 = clock64();
+          while (!mbar_try(&sm->kv_full[j % NSTAGE], (j / NSTAGE) & 1) && clock64() - t0 < kWaitCycles) {
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------- MMA issuer -------------------------------
+    if (lane == 0) {
+      constexpr uint32_t idesc_qk = make_idesc(BM, BN);
+      constexpr uint32_t idesc_pv = make_idesc(BM, DH);
+      bool ok = mbar_wait(&sm->q_full, 0, abort_flag);
+      const uint32_t q_addr = smem_u32(sm->q);
+      for (int j = 0; ok && j < nt; ++j) {
+        const int st = j % NSTAGE;
+        ok = mbar_wait(&sm->kv_full[st], (j / NSTAGE) & 1, abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+        // S = Q . K^T   (M 128, N 128, K 32 = two k-steps of 16 bf16 = 32 bytes)
+        const uint32_t k_addr = smem_u32(sm->k[st]);
+#pragma unroll
+        for (int ks = 0; ks < 2; ++ks)
+          umma_ss(tmem + kColS, make_desc(q_addr + 32 * ks, 512, kLayoutSw64),
+                  make_desc(k_addr + 32 * ks, 512, kLayoutSw64), idesc_qk, ks);
+        umma_commit(&sm->s_full);
+        // softmax writes P (and has folded the previous O tile) -> O = P . V
+        ok = mbar_wait(&sm->p_full, j & 1, abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+          const uint32_t v_addr = smem_u32(sm->v[st][ks >> 2]) + 32 * (ks & 3);
+          umma_ts(tmem + kColO, tmem + kColS + 8 * ks, make_desc(v_addr, 1024, kLayoutSw128), idesc_pv, ks);
+        }
+        umma_commit(&sm->o_full);
+        umma_commit(&sm->kv_empty[st]);
+      }
+    }
+  } else {
+    // --------------------------------- softmax ---------------------------------
+    const uint32_t t_row = tmem + ((uint32_t)lane_base << 16);
+    const float sc = p.scale_log2e;
+    float m = -INFINITY, l = 0.f, alpha = 0.f;
+    float o[DH];
+#pragma unroll
+    for (int d = 0; d < DH; ++d) o[d] = 0.f;
+    uint32_t r[32];
+    bool ok = true;
+    for (int j = 0; j < nt; ++j) {
+      ok = mbar_wait(&sm->s_full, j & 1, abort_flag);
+      if (!ok) break;
+      tc_fence_after();
+      const int n_valid = p.n_ctx - (tile_begin + j) * BN;
+      if (n_valid >= BN)
+        softmax_tile<false>(t_row, sc, BN, m, l, alpha);
+      else
+        softmax_tile<true>(t_row, sc, n_valid, m, l, alpha);
+      // fold the previous tile's O (its MMA completed before this tile's S) and rescale; this
+      // read must precede the arrival below, which lets the next P.V overwrite the O columns
+      if (j > 0) {
+        ok = mbar_wait(&sm->o_full, (j - 1) & 1, abort_flag);  // already complete: keeps the phase in step
+        if (!ok) break;
+        tmem_ld32(t_row + kColO, r);
+        tmem_wait_ld();
+#pragma unroll
+        for (int d = 0; d < DH; ++d) o[d] = (o[d] + __uint_as_float(r[d])) * alpha;
+      }
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(&sm->p_full);
+    }
+    if (ok) ok = mbar_wait(&sm->o_full, (nt - 1) & 1, abort_flag);
+    if (ok) {
+      tc_fence_after();
+      tmem_ld32(t_row + kColO, r);
+      tmem_wait_ld();
+      if (row_valid) {
+        const float inv = 1.0f / l;
+        float4* dst = reinterpret_cast<float4*>(p.out + out_row * DH);
+#pragma unroll
+        for (int d = 0; d < DH; d += 4)
+          dst[d >> 2] = make_float4((o[d] + __uint_as_float(r[d])) * inv, (o[d + 1] + __uint_as_float(r[d + 1])) * inv,
+                                    (o[d + 2] + __uint_as_float(r[d + 2])) * inv,
+                                    (o[d + 3] + __uint_as_float(r[d + 3])) * inv);
+        p.lse[out_row] = (m + log2f(l)) * kLn2;
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
+  }
+  if (threadIdx.x == 0 && sm->abort_flag && p.status) atomicExch(p.status, 1);
+}
+
+// ---------------------------------- host side ----------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(sym);
+  }
+  return fn;
+}
+
+int make_map_2d(CUtensorMap* tm, const void* base, uint64_t inner, uint64_t outer, uint64_t row_bytes, uint32_t box_inner,
+                uint32_t box_outer, CUtensorMapSwizzle swz, const char* what) {
+  EncodeTiledFn fn = encode_fn();
+  ARTAB_REQUIRE(fn, ARTAB_EDRIVER, "cuTensorMapEncodeTiled is not available from the driver");
+  const cuuint64_t dims[2] = {inner, outer};
+  const cuuint64_t strides[1] = {row_bytes};
+  const cuuint32_t box[2] = {box_inner, box_outer};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = fn(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  ARTAB_REQUIRE(r == CUDA_SUCCESS, ARTAB_EINVAL, "tensor map for %s refused (CUresult %d): base %p, dims %llu x %llu",
+                what, (int)r, base, (unsigned long long)inner, (unsigned long long)outer);
+  return ARTAB_OK;
+}
+
+}  // namespace
+
+bool ctx_attn_tc_supported(int dtype, int head_dim) { return dtype == ARTAB_BF16 && head_dim == DH; }
+
+int launch_ctx_attn_tc(const CtxAttnArgs& a, cudaStream_t s) {
+  if (a.rows <= 0) return ARTAB_OK;
+  ARTAB_REQUIRE(a.dtype == ARTAB_BF16 && a.head_dim == DH && a.v_transposed, ARTAB_EINVAL,
+                "tensor-core context attention needs bf16, head_dim 32 and a transposed V cache");
+  ARTAB_REQUIRE(a.n_ctx > 0 && a.n_ctx_pad % 8 == 0 && a.n_splits >= 1, ARTAB_EINVAL,
+                "tensor-core context attention: bad context size");
+  ARTAB_REQUIRE(((uintptr_t)a.q % 16) == 0 && ((uintptr_t)a.k_ctx % 16) == 0 && ((uintptr_t)a.v_ctx % 16) == 0,
+                ARTAB_EINVAL, "tensor-core context attention: q / k / v must be 16-byte aligned");
+  const int D = a.n_heads * DH;
+  CUtensorMap tq, tk, tv;
+  int rc = make_map_2d(&tq, a.q, (uint64_t)D, (uint64_t)a.rows, (uint64_t)D * 2, DH, BM, CU_TENSOR_MAP_SWIZZLE_64B, "q");
+  if (rc) return rc;
+  const uint64_t gh = (uint64_t)a.n_groups * a.n_heads;
+  rc = make_map_2d(&tk, a.k_ctx, DH, gh * a.n_ctx_pad, DH * 2, DH, BN, CU_TENSOR_MAP_SWIZZLE_64B, "k_ctx");
+  if (rc) return rc;
+  rc = make_map_2d(&tv, a.v_ctx, (uint64_t)a.n_ctx_pad, gh * DH, (uint64_t)a.n_ctx_pad * 2, 64, DH,
+                   CU_TENSOR_MAP_SWIZZLE_128B, "v_ctx");
+  if (rc) return rc;
+
+  // two CTAs per SM at most: each holds 256 of the SM's 512 TMEM columns
+  const size_t smem = 100 * 1024;
+  static_assert(sizeof(Smem) + 1024 <= 100 * 1024, "shared-memory plan exceeds the request");
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(ctx_attn_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    ARTAB_REQUIRE(e == cudaSuccess, ARTAB_ELAUNCH, "ctx_attn_tc_kernel: shared memory refused: %s",
+                  cudaGetErrorString(e));
+    configured = true;
+  }
+  TcParams p;
+  p.rows = a.rows;
+  p.rows_per_group = a.rows_per_group;
+  p.n_groups = a.n_groups;
+  p.n_heads = a.n_heads;
+  p.n_ctx = a.n_ctx;
+  p.n_ctx_pad = a.n_ctx_pad;
+  p.n_splits = a.n_splits;
+  p.scale_log2e = a.scale * kLog2e;
+  p.out = a.out;
+  p.lse = a.lse;
+  p.status = a.status;
+  const int rows_in_group = a.n_groups == 1 ? a.rows : a.rows_per_group;
+  dim3 grid((rows_in_group + BM - 1) / BM, a.n_heads, a.n_groups * a.n_splits);
+  ctx_attn_tc_kernel<<<grid, kThreads, smem, s>>>(tq, tk, tv, p);
+  count_launch();
+  return check_launch("ctx_attn_tc_kernel");
+}
+
+}  // namespace artab

@@ -35,7 +35,7 @@ def test_context_attention_fp32_golden(ops, tk, splits):
 
 def test_context_attention_strided_views(ops, tk):
     """q arrives as a transpose of [B,N,H,Dh] in the predictor (a non-contiguous view)."""
-    c = ops["attn"][0]
+    c = ops["attn"][3]
     q = cu(c["q"]).transpose(1, 2).contiguous().transpose(1, 2)
     assert not q.is_contiguous()
     out, _ = tk.triton_context_attention(q, cu(c["k_ctx"]), cu(c["v_ctx"]))
