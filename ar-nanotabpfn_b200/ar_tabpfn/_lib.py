@@ -55,6 +55,8 @@ _SIGNATURES = {
     "artab_head_logpdf": (_i, [C.POINTER(Model), _p, _p, _i, _p, _p]),
     "artab_head_sample": (_i, [C.POINTER(Model), _p, _p, _p, _i, _p, _p, _p, _p]),
     "artab_plan_splits": (_i, [_i, _i, _i, _i, _i, _i]),
+    "artab_profile_enable": (None, [_i]),
+    "artab_profile_read": (_i, [C.POINTER(C.c_double), C.POINTER(C.c_int64), _i]),
     "artab_launch_count": (C.c_int64, []),
     "artab_launch_count_reset": (None, []),
     "artab_last_error": (C.c_char_p, []),
@@ -101,6 +103,18 @@ def check(rc: int) -> None:
     if rc in (-1, -2):
         raise ValueError(msg)
     raise ArtabError(f"artab error {rc}: {msg}")
+
+
+PROFILE_KINDS = ("embed", "dense_chain", "context_attention", "buffer_merge", "kv_append")
+
+
+def profile_read():
+    """{kind: (milliseconds, launches)} recorded since artab_profile_enable(1); sync first."""
+    n = len(PROFILE_KINDS)
+    ms = (C.c_double * n)()
+    cnt = (C.c_int64 * n)()
+    load_library().artab_profile_read(ms, cnt, n)
+    return {k: (ms[i], cnt[i]) for i, k in enumerate(PROFILE_KINDS)}
 
 
 def ptr(t: Optional[torch.Tensor]):

@@ -4,6 +4,7 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
+#include <vector>
 
 #include "attn.cuh"
 #include "dense.cuh"
@@ -20,7 +21,41 @@ void set_error(const char* fmt, ...) {
   va_end(ap);
 }
 
+// ---- optional per-launch timing (benchmarks) -----------------------------------
+// When enabled, every kernel launch of this library is bracketed by a pair of CUDA
+// events on the launching stream; artab_profile_read sums the elapsed time per
+// kernel kind after the caller has synchronised.  Off by default: no events.
+struct ProfSlot {
+  cudaEvent_t a, b;
+  int kind;
+};
+static thread_local bool g_prof_on = false;
+static thread_local std::vector<ProfSlot>* g_prof = nullptr;
+static thread_local std::vector<ProfSlot>* g_prof_pool = nullptr;
+
 void count_launch() { ++g_launches; }
+
+void prof_begin(int kind, cudaStream_t s) {
+  if (!g_prof_on) return;
+  if (!g_prof) g_prof = new std::vector<ProfSlot>();
+  if (!g_prof_pool) g_prof_pool = new std::vector<ProfSlot>();
+  ProfSlot sl;
+  if (!g_prof_pool->empty()) {
+    sl = g_prof_pool->back();
+    g_prof_pool->pop_back();
+  } else {
+    cudaEventCreate(&sl.a);
+    cudaEventCreate(&sl.b);
+  }
+  sl.kind = kind;
+  cudaEventRecord(sl.a, s);
+  g_prof->push_back(sl);
+}
+
+void prof_end(cudaStream_t s) {
+  if (!g_prof_on || !g_prof || g_prof->empty()) return;
+  cudaEventRecord(g_prof->back().b, s);
+}
 
 int check_launch(const char* what) {
   const cudaError_t e = cudaPeekAtLastError();
@@ -147,6 +182,7 @@ DenseArgs dense_base(const artab_model* m, const artab_state* st, int rows) {
   d.kv.dtype = st->dtype;
   d.kv.n_heads = m->n_heads;
   d.kv.head_dim = m->head_dim;
+  d.status = st->status;
   fill_head(m, d);
   return d;
 }
@@ -276,6 +312,28 @@ extern "C" {
 
 int artab_plan_splits(int dtype, int rows, int rows_per_group, int n_groups, int n_heads, int n_ctx) {
   return plan_splits(dtype, 32, rows, rows_per_group, n_groups, n_heads, n_ctx, kMaxSplits);
+}
+
+void artab_profile_enable(int on) { g_prof_on = on != 0; }
+
+int artab_profile_read(double* ms_per_kind, int64_t* launches_per_kind, int n_kinds) {
+  for (int i = 0; i < n_kinds; ++i) {
+    ms_per_kind[i] = 0.0;
+    launches_per_kind[i] = 0;
+  }
+  if (!g_prof) return 0;
+  int n = 0;
+  for (ProfSlot& sl : *g_prof) {
+    float ms = 0.f;
+    if (cudaEventElapsedTime(&ms, sl.a, sl.b) == cudaSuccess && sl.kind >= 0 && sl.kind < n_kinds) {
+      ms_per_kind[sl.kind] += ms;
+      launches_per_kind[sl.kind] += 1;
+      ++n;
+    }
+    g_prof_pool->push_back(sl);
+  }
+  g_prof->clear();
+  return n;
 }
 
 int64_t artab_launch_count(void) { return g_launches; }

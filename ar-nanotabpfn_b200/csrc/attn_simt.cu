@@ -316,6 +316,7 @@ template <typename T>
 int launch_ctx_t(const CtxAttnArgs& a, cudaStream_t s) {
   const int rows_in_group = a.n_groups == 1 ? a.rows : a.rows_per_group;
   dim3 grid((rows_in_group + kQB - 1) / kQB, a.n_heads, a.n_groups * a.n_splits);
+  prof_begin(PROF_CTX, s);
   switch (a.head_dim) {
     case 16: ctx_attn_simt_kernel<T, 16><<<grid, kWarps * 32, 0, s>>>(a); break;
     case 32: ctx_attn_simt_kernel<T, 32><<<grid, kWarps * 32, 0, s>>>(a); break;
@@ -324,6 +325,7 @@ int launch_ctx_t(const CtxAttnArgs& a, cudaStream_t s) {
       set_error("context attention: head_dim %d not supported (16, 32, 64)", a.head_dim);
       return ARTAB_EINVAL;
   }
+  prof_end(s);
   count_launch();
   return check_launch("ctx_attn_simt_kernel");
 }
@@ -332,6 +334,7 @@ template <typename T>
 int launch_buf_t(const BufMergeArgs& a, cudaStream_t s) {
   const int wpb = 4;
   const unsigned grid = (unsigned)((a.n_items + wpb - 1) / wpb);
+  prof_begin(PROF_BUF, s);
   switch (a.head_dim) {
     case 16: buf_merge_kernel<T, 16><<<grid, wpb * 32, 0, s>>>(a); break;
     case 32: buf_merge_kernel<T, 32><<<grid, wpb * 32, 0, s>>>(a); break;
@@ -340,6 +343,7 @@ int launch_buf_t(const BufMergeArgs& a, cudaStream_t s) {
       set_error("buffer attention: head_dim %d not supported (16, 32, 64)", a.head_dim);
       return ARTAB_EINVAL;
   }
+  prof_end(s);
   count_launch();
   return check_launch("buf_merge_kernel");
 }
@@ -362,12 +366,14 @@ int launch_kv_append(int dtype, void* kv, const void* k_new, const void* v_new, 
   const long n = n_bh * dh;
   if (n <= 0) return ARTAB_OK;
   const unsigned grid = (unsigned)((n + 255) / 256);
+  prof_begin(PROF_APPEND, s);
   if (dtype == ARTAB_BF16)
     kv_append_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((__nv_bfloat16*)kv, (const __nv_bfloat16*)k_new,
                                                         (const __nv_bfloat16*)v_new, n_bh, dh, max_buf, pos);
   else
     kv_append_kernel<float><<<grid, 256, 0, s>>>((float*)kv, (const float*)k_new, (const float*)v_new, n_bh, dh,
                                                  max_buf, pos);
+  prof_end(s);
   count_launch();
   return check_launch("kv_append_kernel");
 }

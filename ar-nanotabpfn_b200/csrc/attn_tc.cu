@@ -473,7 +473,9 @@ int launch_ctx_attn_tc(const CtxAttnArgs& a, cudaStream_t s) {
   p.status = a.status;
   const int rows_in_group = a.n_groups == 1 ? a.rows : a.rows_per_group;
   dim3 grid((rows_in_group + BM - 1) / BM, a.n_heads, a.n_groups * a.n_splits);
+  prof_begin(PROF_CTX, s);
   ctx_attn_tc_kernel<<<grid, kThreads, smem, s>>>(tq, tk, tv, p);
+  prof_end(s);
   count_launch();
   return check_launch("ctx_attn_tc_kernel");
 }

@@ -13,6 +13,10 @@ namespace artab {
 void set_error(const char* fmt, ...);
 int check_launch(const char* what);
 void count_launch();
+// per-launch CUDA-event timing, active only after artab_profile_enable(1)
+enum ProfKind : int { PROF_EMBED = 0, PROF_DENSE = 1, PROF_CTX = 2, PROF_BUF = 3, PROF_APPEND = 4, PROF_KINDS = 5 };
+void prof_begin(int kind, cudaStream_t s);
+void prof_end(cudaStream_t s);
 
 #define ARTAB_REQUIRE(cond, code, ...) \
   do {                                 \

@@ -40,6 +40,7 @@ struct DenseArgs {
   float* y_out;
   float* ld_out;
   int32_t* comp_out;
+  int32_t* status;     // device status word (bounded waits), may be null
 };
 
 int launch_embed(const EmbedArgs& a, cudaStream_t s);

@@ -17,47 +17,216 @@ constexpr int kRows = 8;  // rows per CTA
 
 __device__ __forceinline__ float gelu_erf(float v) { return 0.5f * v * (1.0f + erff(v * 0.70710678118654752f)); }
 
-// out[r][n] = act(bias[n] + sum_k a[r][k] * Wt[k][n]) for the CTA's rows (a in shared memory).
-template <int R>
-__device__ __forceinline__ void gemm_rows(const float* s_a, int lda, const float* __restrict__ Wt, int K, int N,
-                                          const float* __restrict__ bias, bool gelu, float* s_o, int ldo) {
-  for (int n = threadIdx.x; n < N; n += blockDim.x) {
-    float acc[R];
-#pragma unroll
-    for (int r = 0; r < R; ++r) acc[r] = 0.f;
-    const float* w = Wt + n;
-#pragma unroll 2
-    for (int k = 0; k < K; k += 4) {
-      const float w0 = __ldg(w + (size_t)(k + 0) * N);
-      const float w1 = __ldg(w + (size_t)(k + 1) * N);
-      const float w2 = __ldg(w + (size_t)(k + 2) * N);
-      const float w3 = __ldg(w + (size_t)(k + 3) * N);
-#pragma unroll
-      for (int r = 0; r < R; ++r) {
-        const float4 a = *reinterpret_cast<const float4*>(s_a + r * lda + k);
-        acc[r] = fmaf(a.x, w0, acc[r]);
-        acc[r] = fmaf(a.y, w1, acc[r]);
-        acc[r] = fmaf(a.z, w2, acc[r]);
-        acc[r] = fmaf(a.w, w3, acc[r]);
-      }
-    }
-    const float b = bias ? __ldg(bias + n) : 0.f;
-#pragma unroll
-    for (int r = 0; r < R; ++r) {
-      float v = acc[r] + b;
-      if (gelu) v = gelu_erf(v);
-      s_o[r * ldo + n] = v;
+// ---------------------------------------------------------------------------
+// Weight streaming.  The chain's GEMMs run back to back over the same R rows, so
+// the CTA walks one fixed schedule of weight slabs (KC consecutive rows of a
+// [K][N] matrix = one contiguous span).  A dedicated producer warp keeps kNBuf
+// bulk copies (cp.async.bulk, completion on an mbarrier) in flight into a
+// shared-memory ring, across GEMM and LayerNorm boundaries; the compute warps
+// consume slab by slab and hand ring slots back through "empty" mbarriers, so
+// no CTA-wide barrier sits between slabs.
+// ---------------------------------------------------------------------------
+#ifndef ARTAB_NBUF
+#define ARTAB_NBUF 6
+#endif
+#ifndef ARTAB_BUFBYTES
+#define ARTAB_BUFBYTES 24576
+#endif
+constexpr int kNBuf = ARTAB_NBUF;
+constexpr int kBufBytes = ARTAB_BUFBYTES;
+constexpr long long kWaitCycles = 2000000000LL;
+
+struct Stream {
+  uint64_t full[kNBuf];
+  uint64_t empty[kNBuf];
+  int abort_flag;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ bool mbar_try(uint64_t* b, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(b)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
+// Bounded wait; false once the CTA is aborting (its results are void and the status word is set).
+__device__ __forceinline__ bool mbar_wait(uint64_t* b, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_try(b, parity)) return true;
+  const long long t0 = clock64();
+  while (!mbar_try(b, parity)) {
+    if (*abort_flag) return false;
+    if (clock64() - t0 > kWaitCycles) {
+      *abort_flag = 1;
+      return false;
     }
   }
-  __syncthreads();
+  return true;
+}
+
+// compute threads only (the producer warp never joins)
+__device__ __forceinline__ void sync_compute(int n_threads) { asm volatile("bar.sync 1, %0;" ::"r"(n_threads) : "memory"); }
+
+// columns-per-thread / k-split plan for an [R x K] . [K x N] product on T threads
+__host__ __device__ inline void plan_gemm(int N, int T, int& cpt, int& ksplit) {
+  for (cpt = 4; cpt >= 1; --cpt) {
+    if (N % cpt) continue;
+    const int cols = N / cpt;
+    if (cols <= T && T % cols == 0 && T / cols <= 4) {
+      ksplit = T / cols;
+      return;
+    }
+  }
+  cpt = 1;      // narrow outputs (the head's 3K columns): threads beyond N idle
+  ksplit = 1;
+}
+
+// rows of W per slab: as many as fit a ring slot, a multiple of 4 per k-group
+__host__ __device__ inline int slab_rows(int K, int N, int T) {
+  int cpt, ks;
+  plan_gemm(N, T, cpt, ks);
+  const int q = 4 * ks;
+  int kc = (kBufBytes / (4 * N)) / q * q;
+  if (kc < q) kc = q;
+  return kc > K ? K : kc;
+}
+
+// producer: stream every slab of one matrix (lane 0 of the producer warp)
+__device__ __forceinline__ bool produce(Stream* st, float* ring, int& issued, const float* w, int K, int N, int T) {
+  const int kc = slab_rows(K, N, T);
+  for (int k0 = 0; k0 < K; k0 += kc) {
+    const int rows = min(kc, K - k0);
+    const uint32_t bytes = (uint32_t)rows * N * 4u;
+    const int buf = issued % kNBuf;
+    if (issued >= kNBuf && !mbar_wait(&st->empty[buf], ((issued / kNBuf) + 1) & 1, &st->abort_flag)) return false;
+    uint64_t* bar = &st->full[buf];
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+                 : "memory");
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(smem_u32(ring + (size_t)buf * (kBufBytes / 4))), "l"(w + (size_t)k0 * N), "r"(bytes),
+                 "r"(smem_u32(bar))
+                 : "memory");
+    ++issued;
+  }
+  return true;
+}
+
+struct Chain {
+  Stream* st;
+  float* ring;     // kNBuf slots of kBufBytes
+  float* scratch;  // k-split partial sums [ksplit-1][R][N]
+  int consumed;    // slabs consumed so far
+  int T;           // compute threads
+};
+
+// out[r][n] = act(bias[n] + sum_k a[r][k] * W[k][n]) for the CTA's R rows; a and out in shared memory.
+template <int R, int CPT>
+__device__ __noinline__ void gemm_body(Chain& ch, int K, int N, int ksplit, const float* s_a, int lda,
+                                       const float* __restrict__ bias, bool gelu, float* s_o, int ldo) {
+  const int cols = (N + CPT - 1) / CPT;
+  const int cg = threadIdx.x % cols, kg = threadIdx.x / cols;
+  const bool active = kg < ksplit && (CPT > 1 || cg < N);
+  const int kc = slab_rows(K, N, ch.T);
+  float acc[CPT][R];
+#pragma unroll
+  for (int c = 0; c < CPT; ++c)
+#pragma unroll
+    for (int r = 0; r < R; ++r) acc[c][r] = 0.f;
+
+  for (int k0 = 0; k0 < K; k0 += kc) {
+    const int buf = ch.consumed % kNBuf;
+#ifndef EXP_NOWAIT
+    mbar_wait(&ch.st->full[buf], (ch.consumed / kNBuf) & 1, &ch.st->abort_flag);
+#endif
+    const float* ws = ch.ring + (size_t)buf * (kBufBytes / 4);
+    const int rows = min(kc, K - k0);
+#ifdef EXP_NOFMA
+    const int per = 0;
+#else
+    const int per = rows / ksplit;  // rows of this slab handled by one k-group
+#endif
+    if (active) {
+      const float* wp = ws + (size_t)(kg * per) * N + cg;
+      const float* ap = s_a + k0 + kg * per;
+#pragma unroll 2
+      for (int k = 0; k < per; k += 4) {
+        float w[CPT][4];
+#pragma unroll
+        for (int c = 0; c < CPT; ++c)
+#pragma unroll
+          for (int i = 0; i < 4; ++i) w[c][i] = wp[(size_t)(k + i) * N + c * cols];
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+          const float4 a = *reinterpret_cast<const float4*>(ap + r * lda + k);
+#pragma unroll
+          for (int c = 0; c < CPT; ++c) {
+            acc[c][r] = fmaf(a.x, w[c][0], acc[c][r]);
+            acc[c][r] = fmaf(a.y, w[c][1], acc[c][r]);
+            acc[c][r] = fmaf(a.z, w[c][2], acc[c][r]);
+            acc[c][r] = fmaf(a.w, w[c][3], acc[c][r]);
+          }
+        }
+      }
+    }
+    ++ch.consumed;
+    __syncwarp();
+    if ((threadIdx.x & 31) == 0)  // this warp is done with the ring slot
+      asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&ch.st->empty[buf])) : "memory");
+  }
+
+  // k-groups 1.. park their partial sums; group 0 adds them in a fixed order
+  if (ksplit > 1) {
+    if (active && kg > 0) {
+#pragma unroll
+      for (int c = 0; c < CPT; ++c)
+#pragma unroll
+        for (int r = 0; r < R; ++r) ch.scratch[((size_t)(kg - 1) * R + r) * N + cg + c * cols] = acc[c][r];
+    }
+    sync_compute(ch.T);
+  }
+  if (active && kg == 0) {
+#pragma unroll
+    for (int c = 0; c < CPT; ++c) {
+      const int n = cg + c * cols;
+      const float b = bias ? __ldg(bias + n) : 0.f;
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        float v = acc[c][r];
+        for (int kk = 1; kk < ksplit; ++kk) v += ch.scratch[((size_t)(kk - 1) * R + r) * N + n];
+        v += b;
+        if (gelu) v = gelu_erf(v);
+        s_o[r * ldo + n] = v;
+      }
+    }
+  }
+  sync_compute(ch.T);
+}
+
+template <int R>
+__device__ __forceinline__ void gemm_rows(Chain& ch, int K, int N, const float* s_a, int lda,
+                                          const float* __restrict__ bias, bool gelu, float* s_o, int ldo) {
+  int cpt, ksplit;
+  plan_gemm(N, ch.T, cpt, ksplit);
+  switch (cpt) {
+    case 4: gemm_body<R, 4>(ch, K, N, ksplit, s_a, lda, bias, gelu, s_o, ldo); break;
+    case 3: gemm_body<R, 3>(ch, K, N, ksplit, s_a, lda, bias, gelu, s_o, ldo); break;
+    case 2: gemm_body<R, 2>(ch, K, N, ksplit, s_a, lda, bias, gelu, s_o, ldo); break;
+    default: gemm_body<R, 1>(ch, K, N, ksplit, s_a, lda, bias, gelu, s_o, ldo); break;
+  }
 }
 
 // dst[r][:] = LayerNorm(a[r][:] + b[r][:]) * gamma + beta   (b optional; a, b, dst may alias row-wise)
 template <int R>
 __device__ __forceinline__ void ln_rows(float* dst, int ldd, const float* a, int lda, const float* b, int ldb,
                                         const float* __restrict__ gamma, const float* __restrict__ beta, int D,
-                                        int n_valid) {
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+                                        int n_valid, int T) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = T >> 5;
   for (int r = warp; r < R; r += nw) {
     if (r >= n_valid) continue;
     float s = 0.f;
@@ -81,7 +250,7 @@ __device__ __forceinline__ void ln_rows(float* dst, int ldd, const float* a, int
       dst[r * ldd + d] = (v - mean) * rstd * __ldg(gamma + d) + __ldg(beta + d);
     }
   }
-  __syncthreads();
+  sync_compute(T);
 }
 
 template <typename T>
@@ -167,65 +336,109 @@ __device__ __forceinline__ void head_row(const DenseArgs& a, const float* raw, l
 }
 
 template <int R>
-__global__ void __launch_bounds__(256) dense_chain_kernel(const DenseArgs a) {
-  extern __shared__ __align__(16) float smem[];
+__global__ void __launch_bounds__(288) dense_chain_kernel(const DenseArgs a) {
+  extern __shared__ __align__(128) float smem[];
   const int D = a.D, Dff = a.Dff;
   const int wide = max(3 * D, Dff);
-  float* s_x = smem;              // [R][D]
-  float* s_t = s_x + R * D;       // [R][D]
-  float* s_h = s_t + R * D;       // [R][wide]
+  const int T = blockDim.x - 32;                    // compute threads; the last warp streams weights
+  float* ring = smem;                               // weight ring
+  float* s_x = ring + kNBuf * (kBufBytes / 4);      // [R][D]
+  float* s_t = s_x + R * D;                         // [R][D]
+  float* s_h = s_t + R * D;                         // [R][wide]
+  float* scratch = s_h + R * wide;                  // [3][R][D]
+  Stream* st = reinterpret_cast<Stream*>(scratch + 3 * R * D);
   const long row0 = (long)blockIdx.x * R;
   const int n_valid = (int)min((long)R, (long)a.rows - row0);
+
+  if (threadIdx.x == 0) {
+    st->abort_flag = 0;
+    for (int i = 0; i < kNBuf; ++i) {
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&st->full[i])) : "memory");
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(&st->empty[i])), "r"(T >> 5) : "memory");
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+
+  if ((int)threadIdx.x >= T) {
+    // ------------------------------ producer warp ------------------------------
+#ifdef EXP_NOWAIT
+    return;
+#endif
+    if (threadIdx.x == T) {
+      int issued = 0;
+      bool ok = true;
+      if (a.do_post) {
+        ok = ok && produce(st, ring, issued, a.post_w.wo_t, D, D, T);
+        ok = ok && produce(st, ring, issued, a.post_w.w1_t, D, Dff, T);
+        ok = ok && produce(st, ring, issued, a.post_w.w2_t, Dff, D, T);
+      }
+      if (a.do_head) {
+        ok = ok && produce(st, ring, issued, a.wa_t, D, Dff, T);
+        ok = ok && produce(st, ring, issued, a.wb_t, Dff, 3 * a.n_comp, T);
+      } else if (a.do_pre) {
+        ok = ok && produce(st, ring, issued, a.pre_w.wf_t, D, D, T);
+        ok = ok && produce(st, ring, issued, a.pre_w.wqkv_t, D, 3 * D, T);
+      }
+    }
+    return;
+  }
+
+  Chain ch;
+  ch.st = st;
+  ch.ring = ring;
+  ch.scratch = scratch;
+  ch.consumed = 0;
+  ch.T = T;
   float* cur = s_x;
 
   if (a.do_post) {
     // s_h[0..R*D) <- attention output rows
-    for (int i = threadIdx.x; i < R * D; i += blockDim.x) {
+    for (int i = threadIdx.x; i < R * D; i += T) {
       const int r = i / D;
       s_h[i] = r < n_valid ? a.attn[(size_t)row0 * D + i] : 0.f;
     }
-    __syncthreads();
-    gemm_rows<R>(s_h, D, a.post_w.wo_t, D, D, nullptr, false, s_t, D);
-    ln_rows<R>(s_x, D, s_t, D, a.x1_in + (size_t)row0 * D, D, a.post_w.ln2_g, a.post_w.ln2_b, D, n_valid);
-    gemm_rows<R>(s_x, D, a.post_w.w1_t, D, Dff, a.post_w.b1, true, s_h, wide);
-    gemm_rows<R>(s_h, wide, a.post_w.w2_t, Dff, D, a.post_w.b2, false, s_t, D);
-    ln_rows<R>(s_x, D, s_x, D, s_t, D, a.post_w.ln3_g, a.post_w.ln3_b, D, n_valid);
+    sync_compute(T);
+    gemm_rows<R>(ch, D, D, s_h, D, nullptr, false, s_t, D);
+    ln_rows<R>(s_x, D, s_t, D, a.x1_in + (size_t)row0 * D, D, a.post_w.ln2_g, a.post_w.ln2_b, D, n_valid, T);
+    gemm_rows<R>(ch, D, Dff, s_x, D, a.post_w.b1, true, s_h, wide);
+    gemm_rows<R>(ch, Dff, D, s_h, wide, a.post_w.b2, false, s_t, D);
+    ln_rows<R>(s_x, D, s_x, D, s_t, D, a.post_w.ln3_g, a.post_w.ln3_b, D, n_valid, T);
     if (a.x_out) {
-      for (int i = threadIdx.x; i < n_valid * D; i += blockDim.x) a.x_out[(size_t)row0 * D + i] = s_x[i];
+      for (int i = threadIdx.x; i < n_valid * D; i += T) a.x_out[(size_t)row0 * D + i] = s_x[i];
     }
   } else {
-    for (int i = threadIdx.x; i < R * D; i += blockDim.x) {
+    for (int i = threadIdx.x; i < R * D; i += T) {
       const int r = i / D;
       s_x[i] = r < n_valid ? a.x_in[(size_t)row0 * D + i] : 0.f;
     }
-    __syncthreads();
+    sync_compute(T);
   }
 
   if (a.do_final) {
-    ln_rows<R>(s_t, D, s_x, D, nullptr, 0, a.lnf_g, a.lnf_b, D, n_valid);
+    ln_rows<R>(s_t, D, s_x, D, nullptr, 0, a.lnf_g, a.lnf_b, D, n_valid, T);
     cur = s_t;
     if (a.z_out) {
-      for (int i = threadIdx.x; i < n_valid * D; i += blockDim.x) a.z_out[(size_t)row0 * D + i] = s_t[i];
+      for (int i = threadIdx.x; i < n_valid * D; i += T) a.z_out[(size_t)row0 * D + i] = s_t[i];
     }
   }
 
   if (a.do_head) {
     float* s_raw = (cur == s_x) ? s_t : s_x;
-    gemm_rows<R>(cur, D, a.wa_t, D, Dff, a.ba, true, s_h, wide);
-    gemm_rows<R>(s_h, wide, a.wb_t, Dff, 3 * a.n_comp, a.bb, false, s_raw, D);
-    const int warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
-    for (int r = warp; r < n_valid; r += nw) head_row(a, s_raw + r * D, row0 + r);
-    return;
-  }
-
-  if (a.do_pre) {
+    gemm_rows<R>(ch, D, Dff, cur, D, a.ba, true, s_h, wide);
+    gemm_rows<R>(ch, Dff, 3 * a.n_comp, s_h, wide, a.bb, false, s_raw, D);
+    if (!st->abort_flag) {
+      const int warp = threadIdx.x >> 5, nw = T >> 5;
+      for (int r = warp; r < n_valid; r += nw) head_row(a, s_raw + r * D, row0 + r);
+    }
+  } else if (a.do_pre) {
     // feature attention over one token == out_proj(v_proj(x)); folded into wf_t
-    gemm_rows<R>(s_x, D, a.pre_w.wf_t, D, D, nullptr, false, s_t, D);
-    ln_rows<R>(s_x, D, s_x, D, s_t, D, a.pre_w.ln1_g, a.pre_w.ln1_b, D, n_valid);
-    for (int i = threadIdx.x; i < n_valid * D; i += blockDim.x) a.x1_out[(size_t)row0 * D + i] = s_x[i];
-    gemm_rows<R>(s_x, D, a.pre_w.wqkv_t, D, 3 * D, nullptr, false, s_h, wide);
+    gemm_rows<R>(ch, D, D, s_x, D, nullptr, false, s_t, D);
+    ln_rows<R>(s_x, D, s_x, D, s_t, D, a.pre_w.ln1_g, a.pre_w.ln1_b, D, n_valid, T);
+    for (int i = threadIdx.x; i < n_valid * D; i += T) a.x1_out[(size_t)row0 * D + i] = s_x[i];
+    gemm_rows<R>(ch, D, 3 * D, s_x, D, nullptr, false, s_h, wide);
     const bool bf = a.kv.dtype == ARTAB_BF16;
-    for (int i = threadIdx.x; i < n_valid * D; i += blockDim.x) {
+    for (int i = threadIdx.x; i < n_valid * D; i += T) {
       const int r = i / D, c = i - r * D;
       const float qv = s_h[r * wide + c];
       if (bf)
@@ -241,6 +454,7 @@ __global__ void __launch_bounds__(256) dense_chain_kernel(const DenseArgs a) {
       }
     }
   }
+  if (threadIdx.x == 0 && st->abort_flag && a.status) atomicExch(a.status, 2);
 }
 
 __global__ void __launch_bounds__(128) embed_kernel(const EmbedArgs a) {
@@ -304,7 +518,9 @@ __global__ void __launch_bounds__(128) embed_kernel(const EmbedArgs a) {
 int launch_embed(const EmbedArgs& a, cudaStream_t s) {
   if (a.rows <= 0) return ARTAB_OK;
   const int wpb = 4;
+  prof_begin(PROF_EMBED, s);
   embed_kernel<<<(a.rows + wpb - 1) / wpb, wpb * 32, 0, s>>>(a);
+  prof_end(s);
   count_launch();
   return check_launch("embed_kernel");
 }
@@ -314,8 +530,10 @@ int launch_dense(const DenseArgs& a, cudaStream_t s) {
   ARTAB_REQUIRE(a.D % 32 == 0 && a.Dff % 4 == 0 && a.D >= 32, ARTAB_EINVAL,
                 "dense chain: d_model must be a multiple of 32 and d_ff a multiple of 4 (got %d, %d)", a.D, a.Dff);
   ARTAB_REQUIRE(3 * a.n_comp <= a.D && a.n_comp <= 32, ARTAB_EINVAL, "dense chain: need 3*K <= d_model and K <= 32");
+  ARTAB_REQUIRE(a.D % 16 == 0 && a.Dff % 16 == 0, ARTAB_EINVAL, "dense chain: d_model and d_ff must be multiples of 16");
   const int wide = 3 * a.D > a.Dff ? 3 * a.D : a.Dff;
-  const size_t smem = (size_t)kRows * (2 * a.D + wide) * sizeof(float);
+  const size_t smem = (size_t)kNBuf * kBufBytes + (size_t)kRows * (2 * a.D + wide + 3 * a.D) * sizeof(float) +
+                      sizeof(Stream) + 128;
   static size_t configured = 0;
   if (smem > configured) {
     cudaError_t e = cudaFuncSetAttribute(dense_chain_kernel<kRows>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -324,9 +542,11 @@ int launch_dense(const DenseArgs& a, cudaStream_t s) {
                   cudaGetErrorString(e));
     configured = smem;
   }
-  const int threads = a.D <= 256 ? a.D : 256;
+  const int threads = (a.D <= 256 ? a.D : 256) + 32;  // compute threads + the weight-streaming warp
   const int grid = (a.rows + kRows - 1) / kRows;
+  prof_begin(PROF_DENSE, s);
   dense_chain_kernel<kRows><<<grid, threads, smem, s>>>(a);
+  prof_end(s);
   count_launch();
   return check_launch("dense_chain_kernel");
 }

@@ -231,6 +231,14 @@ ARTAB_API int artab_head_sample(const artab_model* m, const float* z, const floa
  * query rows (workspace sizing). */
 ARTAB_API int artab_plan_splits(int dtype, int rows, int rows_per_group, int n_groups, int n_heads, int n_ctx);
 
+/* Per-launch timing for benchmarks: after artab_profile_enable(1) every kernel launch of
+ * this library (on the calling thread) is bracketed by CUDA events on its stream.
+ * artab_profile_read (call after synchronising) sums elapsed milliseconds and launch
+ * counts per kernel kind (0 embed, 1 per-token dense chain, 2 context attention,
+ * 3 buffer pass + merge, 4 KV append), clears the record and returns the number read. */
+ARTAB_API void artab_profile_enable(int on);
+ARTAB_API int artab_profile_read(double* ms_per_kind, int64_t* launches_per_kind, int n_kinds);
+
 /* Kernels launched by this library on the calling thread since the last reset
  * (a host-side counter for benchmarks). */
 ARTAB_API int64_t artab_launch_count(void);
