@@ -15,6 +15,10 @@ namespace {
 
 constexpr int kRows = 8;  // rows per CTA
 
+// Dynamic shared memory of the chain kernel.  Everything is addressed as an offset into this
+// array so that the compiler emits shared-space loads with 32-bit address arithmetic.
+extern __shared__ __align__(128) float g_smem[];
+
 __device__ __forceinline__ float gelu_erf(float v) { return 0.5f * v * (1.0f + erff(v * 0.70710678118654752f)); }
 
 // ---------------------------------------------------------------------------
@@ -119,20 +123,20 @@ __device__ __forceinline__ bool produce(Stream* st, float* ring, int& issued, co
 
 struct Chain {
   Stream* st;
-  float* ring;     // kNBuf slots of kBufBytes
-  float* scratch;  // k-split partial sums [ksplit-1][R][N]
+  int scratch;     // offset of the k-split partial sums [ksplit-1][R][N]
   int consumed;    // slabs consumed so far
   int T;           // compute threads
 };
 
 // out[r][n] = act(bias[n] + sum_k a[r][k] * W[k][n]) for the CTA's R rows; a and out in shared memory.
 template <int R, int CPT>
-__device__ __noinline__ void gemm_body(Chain& ch, int K, int N, int ksplit, const float* s_a, int lda,
-                                       const float* __restrict__ bias, bool gelu, float* s_o, int ldo) {
+__device__ __noinline__ void gemm_body(Chain& ch, int K, int N, int ksplit, int a_off, int lda,
+                                       const float* __restrict__ bias, bool gelu, int o_off, int ldo) {
   const int cols = (N + CPT - 1) / CPT;
   const int cg = threadIdx.x % cols, kg = threadIdx.x / cols;
   const bool active = kg < ksplit && (CPT > 1 || cg < N);
   const int kc = slab_rows(K, N, ch.T);
+  int consumed = ch.consumed;
   float acc[CPT][R];
 #pragma unroll
   for (int c = 0; c < CPT; ++c)
@@ -140,30 +144,25 @@ __device__ __noinline__ void gemm_body(Chain& ch, int K, int N, int ksplit, cons
     for (int r = 0; r < R; ++r) acc[c][r] = 0.f;
 
   for (int k0 = 0; k0 < K; k0 += kc) {
-    const int buf = ch.consumed % kNBuf;
+    const int buf = consumed % kNBuf;
 #ifndef EXP_NOWAIT
-    mbar_wait(&ch.st->full[buf], (ch.consumed / kNBuf) & 1, &ch.st->abort_flag);
+    mbar_wait(&ch.st->full[buf], (consumed / kNBuf) & 1, &ch.st->abort_flag);
 #endif
-    const float* ws = ch.ring + (size_t)buf * (kBufBytes / 4);
     const int rows = min(kc, K - k0);
-#ifdef EXP_NOFMA
-    const int per = 0;
-#else
     const int per = rows / ksplit;  // rows of this slab handled by one k-group
-#endif
     if (active) {
-      const float* wp = ws + (size_t)(kg * per) * N + cg;
-      const float* ap = s_a + k0 + kg * per;
+      int wo = buf * (kBufBytes / 4) + (kg * per) * N + cg;  // ring lives at offset 0
+      int ao = a_off + k0 + kg * per;
 #pragma unroll 2
       for (int k = 0; k < per; k += 4) {
         float w[CPT][4];
 #pragma unroll
-        for (int c = 0; c < CPT; ++c)
+        for (int i = 0; i < 4; ++i)
 #pragma unroll
-          for (int i = 0; i < 4; ++i) w[c][i] = wp[(size_t)(k + i) * N + c * cols];
+          for (int c = 0; c < CPT; ++c) w[c][i] = g_smem[wo + i * N + c * cols];
 #pragma unroll
         for (int r = 0; r < R; ++r) {
-          const float4 a = *reinterpret_cast<const float4*>(ap + r * lda + k);
+          const float4 a = *reinterpret_cast<const float4*>(&g_smem[ao + r * lda]);
 #pragma unroll
           for (int c = 0; c < CPT; ++c) {
             acc[c][r] = fmaf(a.x, w[c][0], acc[c][r]);
@@ -172,13 +171,16 @@ __device__ __noinline__ void gemm_body(Chain& ch, int K, int N, int ksplit, cons
             acc[c][r] = fmaf(a.w, w[c][3], acc[c][r]);
           }
         }
+        wo += 4 * N;
+        ao += 4;
       }
     }
-    ++ch.consumed;
+    ++consumed;
     __syncwarp();
     if ((threadIdx.x & 31) == 0)  // this warp is done with the ring slot
       asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&ch.st->empty[buf])) : "memory");
   }
+  ch.consumed = consumed;
 
   // k-groups 1.. park their partial sums; group 0 adds them in a fixed order
   if (ksplit > 1) {
@@ -186,7 +188,7 @@ __device__ __noinline__ void gemm_body(Chain& ch, int K, int N, int ksplit, cons
 #pragma unroll
       for (int c = 0; c < CPT; ++c)
 #pragma unroll
-        for (int r = 0; r < R; ++r) ch.scratch[((size_t)(kg - 1) * R + r) * N + cg + c * cols] = acc[c][r];
+        for (int r = 0; r < R; ++r) g_smem[ch.scratch + ((kg - 1) * R + r) * N + cg + c * cols] = acc[c][r];
     }
     sync_compute(ch.T);
   }
@@ -198,10 +200,10 @@ __device__ __noinline__ void gemm_body(Chain& ch, int K, int N, int ksplit, cons
 #pragma unroll
       for (int r = 0; r < R; ++r) {
         float v = acc[c][r];
-        for (int kk = 1; kk < ksplit; ++kk) v += ch.scratch[((size_t)(kk - 1) * R + r) * N + n];
+        for (int kk = 1; kk < ksplit; ++kk) v += g_smem[ch.scratch + ((kk - 1) * R + r) * N + n];
         v += b;
         if (gelu) v = gelu_erf(v);
-        s_o[r * ldo + n] = v;
+        g_smem[o_off + r * ldo + n] = v;
       }
     }
   }
@@ -211,13 +213,14 @@ __device__ __noinline__ void gemm_body(Chain& ch, int K, int N, int ksplit, cons
 template <int R>
 __device__ __forceinline__ void gemm_rows(Chain& ch, int K, int N, const float* s_a, int lda,
                                           const float* __restrict__ bias, bool gelu, float* s_o, int ldo) {
+  const int a_off = (int)(s_a - g_smem), o_off = (int)(s_o - g_smem);
   int cpt, ksplit;
   plan_gemm(N, ch.T, cpt, ksplit);
   switch (cpt) {
-    case 4: gemm_body<R, 4>(ch, K, N, ksplit, s_a, lda, bias, gelu, s_o, ldo); break;
-    case 3: gemm_body<R, 3>(ch, K, N, ksplit, s_a, lda, bias, gelu, s_o, ldo); break;
-    case 2: gemm_body<R, 2>(ch, K, N, ksplit, s_a, lda, bias, gelu, s_o, ldo); break;
-    default: gemm_body<R, 1>(ch, K, N, ksplit, s_a, lda, bias, gelu, s_o, ldo); break;
+    case 4: gemm_body<R, 4>(ch, K, N, ksplit, a_off, lda, bias, gelu, o_off, ldo); break;
+    case 3: gemm_body<R, 3>(ch, K, N, ksplit, a_off, lda, bias, gelu, o_off, ldo); break;
+    case 2: gemm_body<R, 2>(ch, K, N, ksplit, a_off, lda, bias, gelu, o_off, ldo); break;
+    default: gemm_body<R, 1>(ch, K, N, ksplit, a_off, lda, bias, gelu, o_off, ldo); break;
   }
 }
 
@@ -337,7 +340,7 @@ __device__ __forceinline__ void head_row(const DenseArgs& a, const float* raw, l
 
 template <int R>
 __global__ void __launch_bounds__(288) dense_chain_kernel(const DenseArgs a) {
-  extern __shared__ __align__(128) float smem[];
+  float* const smem = g_smem;
   const int D = a.D, Dff = a.Dff;
   const int wide = max(3 * D, Dff);
   const int T = blockDim.x - 32;                    // compute threads; the last warp streams weights
@@ -386,8 +389,7 @@ __global__ void __launch_bounds__(288) dense_chain_kernel(const DenseArgs a) {
 
   Chain ch;
   ch.st = st;
-  ch.ring = ring;
-  ch.scratch = scratch;
+  ch.scratch = (int)(scratch - g_smem);
   ch.consumed = 0;
   ch.T = T;
   float* cur = s_x;

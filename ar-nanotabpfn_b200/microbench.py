@@ -1,0 +1,189 @@
+"""Kernel micro-benchmarks through the C ABI (CUDA-event timed, one JSON line each).
+
+    python ar-nanotabpfn_b200/microbench.py ctx     [--streams 1024 --heads 4 --ctx 4096 --lq 1 --splits 0]
+    python ar-nanotabpfn_b200/microbench.py buffer  [--streams 1024 --heads 4 --len 63 --uniform]
+    python ar-nanotabpfn_b200/microbench.py append  [--streams 4096 --heads 6 --max-buf 256]
+
+``ctx`` is the shared-context decode-attention micro-benchmark: bf16, head_dim 32,
+every stream carries ``lq`` queries against one shared context K/V ~ N(0,1); the
+tcgen05 context contraction is timed alone.  ``buffer`` times the warp-level pass
+over the private buffer K/V with the log-sum-exp merge (per-stream lengths are
+uniform in [0, len] with --uniform, the kernel is launched once per distinct
+length group otherwise all streams use ``len``).  ``append`` times the in-place
+K/V append.  Inputs are larger than L2 where the kernel is bandwidth bound, or an
+L2-sized buffer is written between iterations.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, HERE)
+
+import torch  # noqa: E402
+
+from ar_tabpfn import _lib  # noqa: E402
+from ar_tabpfn.model import triton_kernels as tk  # noqa: E402
+
+
+def peaks():
+    try:
+        return json.load(open(os.path.join(os.path.dirname(HERE), "MEASURED_PEAKS.json")))
+    except OSError:
+        return {}
+
+
+def time_launches(fn, iters, warmup, flush=None):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    tot = 0.0
+    for _ in range(iters):
+        if flush is not None:
+            flush.zero_()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        fn()
+        e.record()
+        e.synchronize()
+        tot += s.elapsed_time(e)
+    return tot / iters
+
+
+def bench_ctx(a):
+    lib = _lib.lib()
+    dev = torch.device("cuda")
+    g = torch.Generator(device=dev).manual_seed(1)
+    B, H, Lq, Nc, Dh = a.streams, a.heads, a.lq, a.ctx, 32
+    rows = B * Lq
+    q = torch.randn(rows, H, Dh, device=dev, generator=g).bfloat16()
+    k = torch.randn(H, Nc, Dh, device=dev, generator=g).bfloat16()
+    v = torch.randn(H, Nc, Dh, device=dev, generator=g).bfloat16()
+    kp, vp, _, Ncp = tk.pack_context(k, v)
+    splits = a.splits or lib.artab_plan_splits(_lib.BF16, rows, rows, 1, H, Nc)
+    out = torch.empty(splits, rows, H, Dh, device=dev)
+    lse = torch.empty(splits, rows, H, device=dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    st = _lib.stream_ptr()
+
+    def fn():
+        _lib.check(lib.artab_context_attention(_lib.BF16, _lib.ptr(q), _lib.ptr(kp), _lib.ptr(vp), rows, rows, 1, H,
+                                               Dh, Nc, Ncp, splits, _lib.ptr(out), _lib.ptr(lse), _lib.ptr(status),
+                                               st))
+
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    ms = time_launches(fn, a.iters, a.warmup, flush)
+    # parity against plain fp32 attention on the same bf16 tensors
+    qq = q.view(B, Lq, H, Dh).permute(0, 2, 1, 3).float()
+    s = torch.matmul(qq, k.float().transpose(-1, -2).unsqueeze(0)) * Dh ** -0.5
+    want = torch.matmul(torch.softmax(s, -1), v.float().unsqueeze(0))
+    lw = torch.logsumexp(s, -1)
+    lse_m = torch.logsumexp(lse, 0).view(B, Lq, H).permute(0, 2, 1)
+    w = torch.exp(lse - torch.logsumexp(lse, 0, keepdim=True)).unsqueeze(-1)
+    got = (w * out).sum(0).view(B, Lq, H, Dh).permute(0, 2, 1, 3)
+    flops = 4.0 * Dh * Nc * rows * H
+    pk = peaks()
+    peak = pk.get("bf16_tflops", 1590.0)
+    ach = flops / (ms * 1e-3) / 1e12
+    print(json.dumps({
+        "bench": "ctx", "streams": B, "heads": H, "lq": Lq, "ctx": Nc, "splits": splits, "ms": ms,
+        "tflops": ach, "peak_tflops": peak, "frac": ach / peak, "peak_source": "measured" if pk else "fallback",
+        "exps_per_s": rows * H * Nc / (ms * 1e-3),
+        "max_rel_err_out": float((got - want).abs().max() / want.abs().max()),
+        "max_abs_err_lse": float((lse_m - lw).abs().max()), "status": int(status.item())}), flush=True)
+
+
+def bench_buffer(a):
+    lib = _lib.lib()
+    dev = torch.device("cuda")
+    g = torch.Generator(device=dev).manual_seed(1)
+    B, H, Dh, T = a.streams, a.heads, 32, a.max_buf
+    n_new = 2
+    rows = B * n_new
+    dt = torch.bfloat16 if a.dtype == "bf16" else torch.float32
+    esz = 2 if a.dtype == "bf16" else 4
+    code = _lib.dtype_code(dt)
+    q = torch.randn(rows, H, Dh, device=dev, generator=g).to(dt)
+    kv = torch.randn(a.layers, B, H, T, 2, Dh, device=dev, generator=g).to(dt)   # several "layers" > L2
+    o_part = torch.randn(1, rows, H, Dh, device=dev, generator=g)
+    lse_part = torch.randn(1, rows, H, device=dev, generator=g)
+    out = torch.empty(rows, H, Dh, device=dev)
+    st = _lib.stream_ptr()
+    state = {"l": 0}
+
+    def fn():
+        layer = kv[state["l"] % a.layers]
+        state["l"] += 1
+        _lib.check(lib.artab_buffer_attention_merge(code, _lib.ptr(q), _lib.ptr(layer), B, H, Dh, T, 0, n_new, a.len,
+                                                    _lib.ptr(o_part), _lib.ptr(lse_part), 1, rows, _lib.ptr(out), st))
+
+    ms = time_launches(fn, a.iters, a.warmup)
+    byts = float(B) * H * a.len * 2 * Dh * esz
+    # parity of the last launch
+    layer = kv[(state["l"] - 1) % a.layers].float()
+    qq = q.view(B, n_new, H, Dh).permute(0, 2, 1, 3).float()
+    kb, vb = layer[:, :, :a.len, 0], layer[:, :, :a.len, 1]
+    s = torch.matmul(qq, kb.transpose(-1, -2)) * Dh ** -0.5
+    ob, lb = torch.matmul(torch.softmax(s, -1), vb), torch.logsumexp(s, -1)
+    oc = o_part[0].view(B, n_new, H, Dh).permute(0, 2, 1, 3)
+    lc = lse_part[0].view(B, n_new, H).permute(0, 2, 1)
+    top = torch.maximum(lb, lc)
+    wb, wc = torch.exp(lb - top), torch.exp(lc - top)
+    want = (wb.unsqueeze(-1) * ob + wc.unsqueeze(-1) * oc) / (wb + wc).unsqueeze(-1)
+    got = out.view(B, n_new, H, Dh).permute(0, 2, 1, 3)
+    pk = peaks()
+    peak = pk.get("hbm_gbs", 6650.0)
+    ach = byts / (ms * 1e-3) / 1e9
+    print(json.dumps({
+        "bench": "buffer", "dtype": a.dtype, "streams": B, "heads": H, "len": a.len, "queries_per_stream": n_new,
+        "kv_bytes": byts, "working_set_mb": kv.numel() * esz / 2 ** 20, "ms": ms, "gbs": ach, "peak_gbs": peak,
+        "frac": ach / peak, "peak_source": "measured" if pk else "fallback",
+        "max_abs_err": float((got - want).abs().max())}), flush=True)
+
+
+def bench_append(a):
+    lib = _lib.lib()
+    dev = torch.device("cuda")
+    B, H, Dh, T = a.streams, a.heads, 32, a.max_buf
+    kv = torch.zeros(B, H, T, 2, Dh, device=dev, dtype=torch.bfloat16)
+    k = torch.randn(B, H, Dh, device=dev).bfloat16()
+    v = torch.randn(B, H, Dh, device=dev).bfloat16()
+    st = _lib.stream_ptr()
+    pos = {"p": 0}
+
+    def fn():
+        _lib.check(lib.artab_kv_append(_lib.BF16, _lib.ptr(kv), _lib.ptr(k), _lib.ptr(v), B, H, Dh, T, pos["p"] % T,
+                                       st))
+        pos["p"] += 1
+
+    ms = time_launches(fn, a.iters, a.warmup)
+    byts = 2.0 * 2 * B * H * Dh * 2   # read k,v + write both rows
+    pk = peaks()
+    peak = pk.get("hbm_gbs", 6650.0)
+    print(json.dumps({"bench": "append", "streams": B, "heads": H, "bytes": byts, "ms": ms,
+                      "gbs": byts / (ms * 1e-3) / 1e9, "peak_gbs": peak}), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("which", choices=["ctx", "buffer", "append"])
+    ap.add_argument("--streams", type=int, default=1024)
+    ap.add_argument("--heads", type=int, default=4)
+    ap.add_argument("--ctx", type=int, default=4096)
+    ap.add_argument("--lq", type=int, default=1)
+    ap.add_argument("--splits", type=int, default=0)
+    ap.add_argument("--len", type=int, default=63)
+    ap.add_argument("--max-buf", type=int, default=128)
+    ap.add_argument("--layers", type=int, default=6)
+    ap.add_argument("--dtype", default="bf16")
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    a = ap.parse_args()
+    {"ctx": bench_ctx, "buffer": bench_buffer, "append": bench_append}[a.which](a)
+
+
+if __name__ == "__main__":
+    main()
