@@ -186,6 +186,24 @@ ARTAB_API int artab_context_attention(int dtype, const void* q, const void* k_ct
                             int n_ctx, int n_ctx_pad, int n_splits, float* out, float* lse,
                             int32_t* status, void* stream);
 
+/* Context attention split over n_splits key ranges and merged, with NO caller scratch.
+ * (No counterpart in the reference: an addition for callers that cannot allocate.)
+ * Same result as artab_context_attention(n_splits) + artab_buffer_attention_merge without
+ * buffer keys, but the per-split partials live in a fixed 8 MiB device array inside the
+ * library image, so the caller passes inputs and the output only.  For hosts that must not
+ * allocate device memory at call time (a pre-sized serving arena, a plugin that is handed
+ * tensors but owns no allocator, a latency path where cudaMalloc would stall the device).
+ *   out [rows][H][Dh] fp32 (normalised, all splits merged).
+ * Limit: n_splits * rows * n_heads * (head_dim + 1) <= 2 097 152 floats, else ARTAB_ECAPACITY.
+ * The first call on each device looks the array's device address up (a host-side, one-off
+ * set-up step): make that first call outside any stream capture.  All calls on a device share
+ * the one array: calls whose kernels may overlap on the GPU (different streams) race on it;
+ * serialise them.  Every GPU that loads the library holds the 8 MiB until the process exits. */
+ARTAB_API int artab_context_attention_noalloc(int dtype, const void* q, const void* k_ctx, const void* v_ctx,
+                                              int rows, int rows_per_group, int n_groups, int n_heads,
+                                              int head_dim, int n_ctx, int n_ctx_pad, int n_splits, float* out,
+                                              void* stream);
+
 /* Private-buffer attention pass + log-sum-exp merge with the context partials.
  * One work item per (stream, head, item): up to two queries (a "target" row and a
  * "buffer" row, -1 = absent) attend to keys [0, len) of that stream-head's span in
