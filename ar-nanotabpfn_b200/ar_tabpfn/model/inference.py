@@ -144,7 +144,8 @@ class ARTabPFNPredictor:
 
     def _layout(self, n_ctx: int) -> None:
         """Allocate the layout-fixed caches: context K [L,G,H,Ncp,Dh], context V
-        (transposed in bf16) and the private buffers [L,B,H,T,2,Dh]."""
+        (in bf16 transposed and split hi | lo: [L,G,H,2Dh,Ncp]; the exposed
+        ``v_ctx_cache`` view is the hi part) and the private buffers [L,B,H,T,2,Dh]."""
         pm = self._packed(self._device)
         cdt = self._cache_dtype(self._dtype)
         B = self._batch
@@ -158,7 +159,7 @@ class ARTabPFNPredictor:
         st.buffer_len, st.max_rows, st.max_splits = 0, 0, _lib.MAX_SPLITS
         k_ctx = self._alloc("k_ctx", (L, G, H, Ncp, Dh), cdt)
         if cdt == torch.bfloat16:
-            v_ctx = self._alloc("v_ctx", (L, G, H, Dh, Ncp), cdt)
+            v_ctx = self._alloc("v_ctx", (L, G, H, 2 * Dh, Ncp), cdt)  # hi | lo parts
         else:
             v_ctx = self._alloc("v_ctx", (L, G, H, Ncp, Dh), cdt)
         k_ctx.zero_()
@@ -172,7 +173,8 @@ class ARTabPFNPredictor:
         # reference-shaped views on the layer modules (inference.py:113-118)
         for l, layer in enumerate(self.backbone.layers):
             kc = k_ctx[l, :, :, :n_ctx]
-            vc = v_ctx[l].transpose(-1, -2)[:, :, :n_ctx] if cdt == torch.bfloat16 else v_ctx[l, :, :, :n_ctx]
+            vc = (v_ctx[l, :, :, :Dh].transpose(-1, -2)[:, :, :n_ctx] if cdt == torch.bfloat16
+                  else v_ctx[l, :, :, :n_ctx])
             layer.k_ctx_cache = kc[0] if self.shared else kc
             layer.v_ctx_cache = vc[0] if self.shared else vc
             layer.k_buf_cache = kv[l, :, :, :, 0]

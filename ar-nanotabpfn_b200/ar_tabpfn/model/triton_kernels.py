@@ -46,7 +46,8 @@ def _unrows(o: Tensor, B: int, Lq: int) -> Tensor:
 
 def pack_context(k_ctx: Tensor, v_ctx: Tensor) -> Tuple[Tensor, Tensor, int, int]:
     """Lay [H,Nc,Dh] (or [G,H,Nc,Dh]) context K/V out as the kernels read it:
-    K [G,H,Ncp,Dh]; V the same in fp32, transposed [G,H,Dh,Ncp] in bf16."""
+    K [G,H,Ncp,Dh]; V the same in fp32; in bf16 transposed with a hi and a lo part,
+    [G,H,2*Dh,Ncp] (the lo part is zero for values that are already bf16)."""
     if k_ctx.dim() == 3:
         k_ctx, v_ctx = k_ctx.unsqueeze(0), v_ctx.unsqueeze(0)
     G, H, Nc, Dh = k_ctx.shape
@@ -54,8 +55,8 @@ def pack_context(k_ctx: Tensor, v_ctx: Tensor) -> Tuple[Tensor, Tensor, int, int
     k = torch.zeros(G, H, Ncp, Dh, device=k_ctx.device, dtype=k_ctx.dtype)
     k[:, :, :Nc] = k_ctx
     if k_ctx.dtype == torch.bfloat16:
-        v = torch.zeros(G, H, Dh, Ncp, device=k_ctx.device, dtype=k_ctx.dtype)
-        v[:, :, :, :Nc] = v_ctx.transpose(-1, -2)
+        v = torch.zeros(G, H, 2 * Dh, Ncp, device=k_ctx.device, dtype=k_ctx.dtype)
+        v[:, :, :Dh, :Nc] = v_ctx.transpose(-1, -2)
     else:
         v = torch.zeros(G, H, Ncp, Dh, device=k_ctx.device, dtype=k_ctx.dtype)
         v[:, :, :Nc] = v_ctx

@@ -98,12 +98,13 @@ int check_state(const artab_model* m, const artab_state* st) {
 }
 
 struct Layout {
-  size_t ctx_layer, buf_layer;  // elements per layer
+  size_t ctx_layer, vctx_layer, buf_layer;  // elements per layer
 };
 
 Layout layout_of(const artab_model* m, const artab_state* st) {
   Layout l;
   l.ctx_layer = (size_t)st->n_groups * m->n_heads * st->n_ctx_pad * m->head_dim;
+  l.vctx_layer = l.ctx_layer * (st->dtype == ARTAB_BF16 ? 2 : 1);  // bf16 V: hi and lo parts
   l.buf_layer = (size_t)st->n_streams * m->n_heads * st->max_buf * 2 * m->head_dim;
   return l;
 }
@@ -117,16 +118,26 @@ int plan_splits(int dtype, int head_dim, int rows, int rows_per_group, int n_gro
   const bool tc = use_tc(dtype, head_dim);
   const int tile_m = tc ? 128 : 16, tile_k = tc ? 128 : 64;
   const int rows_g = n_groups == 1 ? rows : rows_per_group;
-  const long ctas = (long)((rows_g + tile_m - 1) / tile_m) * n_heads * n_groups;
+  const long items = (long)((rows_g + tile_m - 1) / tile_m) * n_heads * n_groups;
   const int tiles = (n_ctx + tile_k - 1) / tile_k;
-  const long target = 2 * kSMs;
-  int s = 1;
-  if (ctas < target) s = (int)((target + ctas - 1) / ctas);
-  if (s > tiles) s = tiles;
-  if (s > max_splits) s = max_splits;
-  if (s < 1) s = 1;
-  const int tps = (tiles + s - 1) / s;
-  return (tiles + tps - 1) / tps;
+  // Resident CTA slots: two per SM for the tensor-core kernel (TMEM), about eight for the SIMT one.
+  const long slots = (long)kSMs * (tc ? 2 : 8);
+  // Cost model: waves x (key tiles per CTA + fixed per-CTA overhead in tile units); smallest wins.
+  int best = 1;
+  double best_cost = 1e30;
+  const int smax = tiles < max_splits ? tiles : max_splits;
+  for (int s = 1; s <= smax; ++s) {
+    const int tps = (tiles + s - 1) / s;
+    const int s_eff = (tiles + tps - 1) / tps;
+    if (s_eff != s) continue;
+    const long waves = (items * s + slots - 1) / slots;
+    const double cost = (double)waves * (tps + 1.5) + 0.05 * s;  // small bias against extra partials
+    if (cost < best_cost) {
+      best_cost = cost;
+      best = s;
+    }
+  }
+  return best;
 }
 
 int run_ctx(const artab_model* m, const artab_state* st, int layer, int rows, int rows_per_group, int n_splits,
@@ -137,7 +148,7 @@ int run_ctx(const artab_model* m, const artab_state* st, int layer, int rows, in
   c.dtype = st->dtype;
   c.q = st->q;
   c.k_ctx = off(st->k_ctx, lo.ctx_layer * layer, st->dtype);
-  c.v_ctx = off(st->v_ctx, lo.ctx_layer * layer, st->dtype);
+  c.v_ctx = off(st->v_ctx, lo.vctx_layer * layer, st->dtype);
   c.v_transposed = st->dtype == ARTAB_BF16;
   c.rows = rows;
   c.rows_per_group = rows_per_group;
@@ -190,7 +201,7 @@ DenseArgs dense_base(const artab_model* m, const artab_state* st, int rows) {
 void set_kv(const artab_model* m, const artab_state* st, int layer, KvDest& kv) {
   const Layout lo = layout_of(m, st);
   kv.k_ctx = off(st->k_ctx, lo.ctx_layer * layer, st->dtype);
-  kv.v_ctx = off(st->v_ctx, lo.ctx_layer * layer, st->dtype);
+  kv.v_ctx = off(st->v_ctx, lo.vctx_layer * layer, st->dtype);
   kv.n_ctx = st->n_ctx;
   kv.n_ctx_pad = st->n_ctx_pad;
   kv.kv_buf = st->kv_buf ? off(st->kv_buf, lo.buf_layer * layer, st->dtype) : nullptr;

@@ -42,7 +42,9 @@ __global__ void __launch_bounds__(kWarps * 32) ctx_attn_simt_kernel(const CtxAtt
 
   const T* Q = reinterpret_cast<const T*>(a.q);
   const T* Kc = reinterpret_cast<const T*>(a.k_ctx) + ((size_t)(g * a.n_heads + h) * a.n_ctx_pad) * DH;
-  const T* Vc = reinterpret_cast<const T*>(a.v_ctx) + ((size_t)(g * a.n_heads + h) * a.n_ctx_pad) * DH;
+  // transposed layout holds a hi and a lo part per head: [2*Dh][Ncp]
+  const T* Vc = reinterpret_cast<const T*>(a.v_ctx) +
+                ((size_t)(g * a.n_heads + h) * a.n_ctx_pad) * DH * (a.v_transposed ? 2 : 1);
 
   for (int i = threadIdx.x; i < kQB * DH; i += blockDim.x) {
     const int qi = i / DH, d = i - qi * DH;
@@ -69,7 +71,9 @@ __global__ void __launch_bounds__(kWarps * 32) ctx_attn_simt_kernel(const CtxAtt
     if (a.v_transposed) {
       for (int i = threadIdx.x; i < kKT * DH; i += blockDim.x) {
         const int d = i / kKT, key = i - d * kKT;
-        sV[key][d] = (kt + key) < a.n_ctx ? to_f32<T>(Vc[(size_t)d * a.n_ctx_pad + kt + key]) : 0.f;
+        sV[key][d] = (kt + key) < a.n_ctx ? to_f32<T>(Vc[(size_t)d * a.n_ctx_pad + kt + key]) +
+                                                 to_f32<T>(Vc[(size_t)(DH + d) * a.n_ctx_pad + kt + key])
+                                           : 0.f;
       }
     } else {
       for (int i = threadIdx.x; i < kKT * DH; i += blockDim.x) {

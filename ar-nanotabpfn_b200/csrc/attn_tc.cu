@@ -29,19 +29,22 @@ namespace {
 constexpr int BM = 128;       // query rows per tile
 constexpr int BN = 128;       // keys per tile
 constexpr int DH = 32;        // head dim this kernel is built for
-constexpr int NSTAGE = 4;     // K/V pipeline depth
-constexpr int kThreads = 192;
+constexpr int NSTAGE = 3;     // K/V pipeline depth
+constexpr int kThreads = 320; // warp 0 TMA, warp 1 MMA, warps 2-5 and 6-9 softmax (two warpgroups)
 constexpr uint32_t kTmemCols = 256;
-constexpr uint32_t kColS = 0;    // S: 128 fp32 columns; P (packed bf16) aliases columns [0, 64)
-constexpr uint32_t kColO = 128;  // O tile: 32 fp32 columns
+constexpr uint32_t kColS = 0;    // S: 128 fp32 columns
+constexpr uint32_t kColO = 128;  // O tile: 64 fp32 columns = P.V_hi | P.V_lo
+constexpr uint32_t kColP = 192;  // P: 128 bf16 = 64 packed columns (A operand of P.V)
 constexpr long long kWaitCycles = 2000000000LL;  // about one second
 
 struct __align__(1024) Smem {
   uint8_t q[BM * 64];               // [128 rows][32 bf16], 64-byte swizzle
   uint8_t k[NSTAGE][BN * 64];       // [128 keys][32 bf16], 64-byte swizzle
-  uint8_t v[NSTAGE][2][32 * 128];   // V^T: two boxes of [32 dims][64 keys], 128-byte swizzle
+  uint8_t v[NSTAGE][2][64 * 128];   // V^T hi|lo: two boxes of [64 rows][64 keys], 128-byte swizzle
   uint64_t q_full, s_full, p_full, o_full;
   uint64_t kv_full[NSTAGE], kv_empty[NSTAGE];
+  float xmax[2][2][BM];             // row maxima exchanged between the two softmax warpgroups
+  float xsum[BM];                   // row sum of the second warpgroup (epilogue)
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -167,28 +170,35 @@ struct TcParams {
   int32_t* status;
 };
 
-// Softmax of one 128 x 128 score tile for one row (thread).  MASKED: columns >= n_valid are -inf.
+// Softmax of this thread's half (64 columns) of one 128 x 128 score tile row.  The two
+// softmax warpgroups own columns [0,64) and [64,128) of the same rows and exchange their row
+// maxima through shared memory.  MASKED: columns >= n_valid are -inf.
 template <bool MASKED>
-__device__ __forceinline__ void softmax_tile(uint32_t t_row, float sc, int n_valid, float& m, float& l, float& alpha) {
+__device__ __forceinline__ void softmax_tile(Smem* sm, uint32_t t_row, int wg, int row, int parity, float sc,
+                                             int n_valid, float& m, float& l, float& alpha) {
   uint32_t r[32];
   float mx = -INFINITY;
-#pragma unroll 1  // one 32-column chunk in flight: keeps the register count low enough for two CTAs per SM
-  for (int c = 0; c < 4; ++c) {
-    tmem_ld32(t_row + kColS + 32 * c, r);
+  const int col0 = 64 * wg;
+#pragma unroll 1  // one 32-column chunk in flight keeps the register count low enough for two CTAs per SM
+  for (int c = 0; c < 2; ++c) {
+    tmem_ld32(t_row + kColS + col0 + 32 * c, r);
     tmem_wait_ld();
 #pragma unroll
     for (int i = 0; i < 32; ++i) {
       float s = __uint_as_float(r[i]);
-      if (MASKED && 32 * c + i >= n_valid) s = -INFINITY;
+      if (MASKED && col0 + 32 * c + i >= n_valid) s = -INFINITY;
       mx = fmaxf(mx, s);
     }
   }
-  const float m_new = fmaxf(m, mx * sc);  // at least one column of every tile is valid
+  sm->xmax[parity][wg][row] = mx;
+  asm volatile("bar.sync 2, 256;" ::: "memory");  // the two softmax warpgroups only
+  mx = fmaxf(mx, sm->xmax[parity][wg ^ 1][row]);
+  const float m_new = fmaxf(m, mx * sc);  // column 0 of every tile is valid, so mx is finite
   alpha = ex2_approx(m - m_new);          // m = -inf on the first tile gives 0
   float sum = 0.f;
 #pragma unroll 1
-  for (int c = 0; c < 4; ++c) {
-    tmem_ld32(t_row + kColS + 32 * c, r);
+  for (int c = 0; c < 2; ++c) {
+    tmem_ld32(t_row + kColS + col0 + 32 * c, r);
     tmem_wait_ld();
     uint32_t pk[16];
 #pragma unroll
@@ -196,14 +206,13 @@ __device__ __forceinline__ void softmax_tile(uint32_t t_row, float sc, int n_val
       float p0 = ex2_approx(fmaf(__uint_as_float(r[i]), sc, -m_new));
       float p1 = ex2_approx(fmaf(__uint_as_float(r[i + 1]), sc, -m_new));
       if (MASKED) {
-        if (32 * c + i >= n_valid) p0 = 0.f;
-        if (32 * c + i + 1 >= n_valid) p1 = 0.f;
+        if (col0 + 32 * c + i >= n_valid) p0 = 0.f;
+        if (col0 + 32 * c + i + 1 >= n_valid) p1 = 0.f;
       }
       sum += p0 + p1;
       pk[i >> 1] = pack_bf16(p0, p1);
     }
-    // P chunk c lands in columns [16c, 16c+16): S columns already consumed by this thread
-    tmem_st16(t_row + kColS + 16 * c, pk);
+    tmem_st16(t_row + kColP + 32 * wg + 16 * c, pk);
   }
   l = l * alpha + sum;
   m = m_new;
@@ -228,10 +237,11 @@ ctx_attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   const int tile_end = min(tiles, tile_begin + tps);
   const int nt = tile_end - tile_begin;
 
-  // softmax threads: TMEM lane (= tile row) owned by this thread
+  // softmax threads: TMEM lane (= tile row) owned by this thread; warpgroup 0 = warps 2-5, 1 = warps 6-9
   const int lane_base = 32 * (warp & 3);
   const int row = lane_base + lane;
-  const bool row_valid = warp >= 2 && (m0 + row) < rows_in_group;
+  const int wg = warp >= 6 ? 1 : 0;
+  const bool row_valid = warp >= 2 && warp < 6 && (m0 + row) < rows_in_group;  // warpgroup 0 stores
   const size_t out_row = ((size_t)split * p.rows + group_row0 + m0 + row) * p.n_heads + h;
 
   if (nt <= 0) {  // empty split: contributes nothing to the merge
@@ -247,7 +257,7 @@ ctx_attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   if (threadIdx.x == 0) {
     mbar_init(&sm->q_full, 1);
     mbar_init(&sm->s_full, 1);
-    mbar_init(&sm->p_full, 128);
+    mbar_init(&sm->p_full, 256);
     mbar_init(&sm->o_full, 1);
     for (int s = 0; s < NSTAGE; ++s) {
       mbar_init(&sm->kv_full[s], 1);
@@ -274,13 +284,13 @@ ctx_attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       mbar_expect_tx(&sm->q_full, BM * 64);
       tma_load_2d(sm->q, &tm_q, h * DH, (int)(group_row0 + m0), &sm->q_full);
       const int krow0 = (g * p.n_heads + h) * p.n_ctx_pad;
-      const int vrow0 = (g * p.n_heads + h) * DH;
+      const int vrow0 = (g * p.n_heads + h) * 2 * DH;
       int issued = 0;
       for (int j = 0; j < nt; ++j) {
         const int st = j % NSTAGE;
         if (j >= NSTAGE && !mbar_wait(&sm->kv_empty[st], ((j / NSTAGE) + 1) & 1, abort_flag)) break;
         const int key0 = (tile_begin + j) * BN;
-        mbar_expect_tx(&sm->kv_full[st], BN * 64 + 2 * 32 * 128);
+        mbar_expect_tx(&sm->kv_full[st], BN * 64 + 2 * 64 * 128);
         tma_load_2d(sm->k[st], &tm_k, 0, krow0 + key0, &sm->kv_full[st]);
         tma_load_2d(sm->v[st][0], &tm_v, key0, vrow0, &sm->kv_full[st]);
         tma_load_2d(sm->v[st][1], &tm_v, key0 + 64, vrow0, &sm->kv_full[st]);
@@ -303,7 +313,7 @@ ctx_attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     // ------------------------------- MMA issuer -------------------------------
     if (lane == 0) {
       constexpr uint32_t idesc_qk = make_idesc(BM, BN);
-      constexpr uint32_t idesc_pv = make_idesc(BM, DH);
+      constexpr uint32_t idesc_pv = make_idesc(BM, 2 * DH);
       bool ok = mbar_wait(&sm->q_full, 0, abort_flag);
       const uint32_t q_addr = smem_u32(sm->q);
       for (int j = 0; ok && j < nt; ++j) {
@@ -318,14 +328,14 @@ ctx_attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
           umma_ss(tmem + kColS, make_desc(q_addr + 32 * ks, 512, kLayoutSw64),
                   make_desc(k_addr + 32 * ks, 512, kLayoutSw64), idesc_qk, ks);
         umma_commit(&sm->s_full);
-        // softmax writes P (and has folded the previous O tile) -> O = P . V
+        // softmax writes P (and has folded the previous O tile) -> O = P . [V_hi | V_lo]
         ok = mbar_wait(&sm->p_full, j & 1, abort_flag);
         if (!ok) break;
         tc_fence_after();
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks) {
           const uint32_t v_addr = smem_u32(sm->v[st][ks >> 2]) + 32 * (ks & 3);
-          umma_ts(tmem + kColO, tmem + kColS + 8 * ks, make_desc(v_addr, 1024, kLayoutSw128), idesc_pv, ks);
+          umma_ts(tmem + kColO, tmem + kColP + 8 * ks, make_desc(v_addr, 1024, kLayoutSw128), idesc_pv, ks);
         }
         umma_commit(&sm->o_full);
         umma_commit(&sm->kv_empty[st]);
@@ -341,43 +351,56 @@ ctx_attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     for (int d = 0; d < DH; ++d) o[d] = 0.f;
     uint32_t r[32];
     bool ok = true;
+    // On an abort the loop still runs every iteration (waits return at once, results are void):
+    // both warpgroups must execute the same number of bar.sync instructions.
     for (int j = 0; j < nt; ++j) {
-      ok = mbar_wait(&sm->s_full, j & 1, abort_flag);
-      if (!ok) break;
+      ok = mbar_wait(&sm->s_full, j & 1, abort_flag) && ok;
       tc_fence_after();
       const int n_valid = p.n_ctx - (tile_begin + j) * BN;
       if (n_valid >= BN)
-        softmax_tile<false>(t_row, sc, BN, m, l, alpha);
+        softmax_tile<false>(sm, t_row, wg, row, j & 1, sc, BN, m, l, alpha);
       else
-        softmax_tile<true>(t_row, sc, n_valid, m, l, alpha);
-      // fold the previous tile's O (its MMA completed before this tile's S) and rescale; this
-      // read must precede the arrival below, which lets the next P.V overwrite the O columns
-      if (j > 0) {
-        ok = mbar_wait(&sm->o_full, (j - 1) & 1, abort_flag);  // already complete: keeps the phase in step
-        if (!ok) break;
-        tmem_ld32(t_row + kColO, r);
-        tmem_wait_ld();
+        softmax_tile<true>(sm, t_row, wg, row, j & 1, sc, n_valid, m, l, alpha);
+      // warpgroup 0 folds the previous tile's O (its MMA completed before this tile's S) and
+      // rescales; the read must precede the arrival below, which lets the next P.V overwrite O
+      if (wg == 0 && j > 0) {
+        ok = mbar_wait(&sm->o_full, (j - 1) & 1, abort_flag) && ok;  // already complete: keeps the phase in step
+#pragma unroll 1
+        for (int hl = 0; hl < 2; ++hl) {  // hi and lo halves of V
+          tmem_ld32(t_row + kColO + 32 * hl, r);
+          tmem_wait_ld();
 #pragma unroll
-        for (int d = 0; d < DH; ++d) o[d] = (o[d] + __uint_as_float(r[d])) * alpha;
+          for (int d = 0; d < DH; ++d) o[d] += __uint_as_float(r[d]);
+        }
+#pragma unroll
+        for (int d = 0; d < DH; ++d) o[d] *= alpha;
       }
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(&sm->p_full);
     }
-    if (ok) ok = mbar_wait(&sm->o_full, (nt - 1) & 1, abort_flag);
-    if (ok) {
-      tc_fence_after();
-      tmem_ld32(t_row + kColO, r);
-      tmem_wait_ld();
-      if (row_valid) {
-        const float inv = 1.0f / l;
-        float4* dst = reinterpret_cast<float4*>(p.out + out_row * DH);
+    if (wg == 1) sm->xsum[row] = l;
+    asm volatile("bar.sync 2, 256;" ::: "memory");
+    if (wg == 0) {
+      l += sm->xsum[row];
+      if (ok) ok = mbar_wait(&sm->o_full, (nt - 1) & 1, abort_flag);
+      if (ok) {
+        tc_fence_after();
+#pragma unroll 1
+        for (int hl = 0; hl < 2; ++hl) {
+          tmem_ld32(t_row + kColO + 32 * hl, r);
+          tmem_wait_ld();
 #pragma unroll
-        for (int d = 0; d < DH; d += 4)
-          dst[d >> 2] = make_float4((o[d] + __uint_as_float(r[d])) * inv, (o[d + 1] + __uint_as_float(r[d + 1])) * inv,
-                                    (o[d + 2] + __uint_as_float(r[d + 2])) * inv,
-                                    (o[d + 3] + __uint_as_float(r[d + 3])) * inv);
-        p.lse[out_row] = (m + log2f(l)) * kLn2;
+          for (int d = 0; d < DH; ++d) o[d] += __uint_as_float(r[d]);
+        }
+        if (row_valid) {
+          const float inv = 1.0f / l;
+          float4* dst = reinterpret_cast<float4*>(p.out + out_row * DH);
+#pragma unroll
+          for (int d = 0; d < DH; d += 4)
+            dst[d >> 2] = make_float4(o[d] * inv, o[d + 1] * inv, o[d + 2] * inv, o[d + 3] * inv);
+          p.lse[out_row] = (m + log2f(l)) * kLn2;
+        }
       }
     }
   }
@@ -445,7 +468,7 @@ int launch_ctx_attn_tc(const CtxAttnArgs& a, cudaStream_t s) {
   const uint64_t gh = (uint64_t)a.n_groups * a.n_heads;
   rc = make_map_2d(&tk, a.k_ctx, DH, gh * a.n_ctx_pad, DH * 2, DH, BN, CU_TENSOR_MAP_SWIZZLE_64B, "k_ctx");
   if (rc) return rc;
-  rc = make_map_2d(&tv, a.v_ctx, (uint64_t)a.n_ctx_pad, gh * DH, (uint64_t)a.n_ctx_pad * 2, 64, DH,
+  rc = make_map_2d(&tv, a.v_ctx, (uint64_t)a.n_ctx_pad, gh * 2 * DH, (uint64_t)a.n_ctx_pad * 2, 64, 2 * DH,
                    CU_TENSOR_MAP_SWIZZLE_128B, "v_ctx");
   if (rc) return rc;
 

@@ -263,9 +263,11 @@ __device__ __forceinline__ void scatter_kv(const KvDest& kv, long row, int c, fl
     const long g = row / kv.n_ctx, i = row - g * kv.n_ctx;
     const size_t base = ((size_t)(g * kv.n_heads + h) * kv.n_ctx_pad);
     reinterpret_cast<T*>(kv.k_ctx)[(base + i) * kv.head_dim + d] = from_f32<T>(kval);
-    if (kv.dtype == ARTAB_BF16) {  // transposed [.., Dh][Ncp]
-      reinterpret_cast<T*>(kv.v_ctx)[((size_t)(g * kv.n_heads + h) * kv.head_dim + d) * kv.n_ctx_pad + i] =
-          from_f32<T>(vval);
+    if (kv.dtype == ARTAB_BF16) {  // transposed, split into a bf16 hi and lo part: [.., 2*Dh][Ncp]
+      T* vb = reinterpret_cast<T*>(kv.v_ctx) + ((size_t)(g * kv.n_heads + h) * 2 * kv.head_dim) * kv.n_ctx_pad + i;
+      const T hi = from_f32<T>(vval);
+      vb[(size_t)d * kv.n_ctx_pad] = hi;
+      vb[(size_t)(kv.head_dim + d) * kv.n_ctx_pad] = from_f32<T>(vval - to_f32<T>(hi));
     } else {
       reinterpret_cast<T*>(kv.v_ctx)[(base + i) * kv.head_dim + d] = from_f32<T>(vval);
     }

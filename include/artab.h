@@ -97,8 +97,9 @@ typedef struct artab_model {
 /* the caller; layout fixed at allocation, nothing is re-allocated per step).   */
 /*                                                                             */
 /*   k_ctx  [L][G][H][Ncp][Dh]                       context keys               */
-/*   v_ctx  fp32: [L][G][H][Ncp][Dh]; bf16: [L][G][H][Dh][Ncp] (transposed so    */
-/*          that both tensor-core B operands are K-major)                       */
+/*   v_ctx  fp32: [L][G][H][Ncp][Dh]; bf16: [L][G][H][2*Dh][Ncp]: transposed (so  */
+/*          that both tensor-core B operands are K-major) and split into a bf16  */
+/*          hi part (rows 0..Dh-1) and lo part (rows Dh..2Dh-1), v = hi + lo      */
 /*   kv_buf [L][B][H][T][2][Dh]   private buffer K (slot 0) and V (slot 1) of    */
 /*          every stream; one stream-head's history is one contiguous span      */
 /*   G = 1: one context shared by all streams ("triton_shared_context");        */
@@ -174,7 +175,7 @@ ARTAB_API int artab_teacher_forcing(const artab_model* m, artab_state* st, const
 /* ------------------------------ single operators -------------------------- */
 
 /* Shared-context attention with LSE output.
- *   q [rows][H][Dh] (dtype), k_ctx [G][H][Ncp][Dh], v_ctx (layout per dtype, see above),
+ *   q [rows][H][Dh] (dtype), k_ctx [G][H][Ncp][Dh], v_ctx (layout per dtype, see artab_state),
  *   rows_per_group: rows r belong to context group r / rows_per_group (ignored when G = 1);
  *   out [rows][H][Dh] fp32 (normalised), lse [rows][H] fp32 (natural log).
  *   n_splits >= 1 splits the key axis; out/lse then hold n_splits partials

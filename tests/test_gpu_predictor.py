@@ -8,7 +8,7 @@ from util import build_model, load_golden
 
 pytestmark = pytest.mark.gpu
 
-BF16_LOGDENS_ATOL = 4e-3  # TODO tighten to 2e-3 once the context V cache is split hi/lo
+BF16_LOGDENS_ATOL = 2e-3
 
 
 def fp64_joint_density(fx, shared):
