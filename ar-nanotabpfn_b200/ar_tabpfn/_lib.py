@@ -21,15 +21,16 @@ _fp = C.c_void_p  # every device pointer travels as void*
 
 class LayerWeights(C.Structure):
     _fields_ = [(n, _fp) for n in ("wf_t", "ln1_g", "ln1_b", "wqkv_t", "wo_t", "ln2_g", "ln2_b", "w1_t", "b1",
-                                   "w2_t", "b2", "ln3_g", "ln3_b")]
+                                   "w2_t", "b2", "ln3_g", "ln3_b", "tc_wo", "tc_w1", "tc_w2", "tc_wf", "tc_wqkv")] + \
+               [("tc_lo", C.c_int32), ("tc_reserved", C.c_int32)]
 
 
 class Model(C.Structure):
     _fields_ = [(n, C.c_int32) for n in ("d_model", "n_heads", "head_dim", "d_ff", "n_layers", "n_comp",
                                           "n_ar_tokens", "reserved")] + \
                [(n, _fp) for n in ("wx", "bx", "wy", "by", "marker", "ar_tokens", "lnf_g", "lnf_b", "wa_t", "ba",
-                                   "wb_t", "bb", "mean_bias", "std_bias", "weight_bias")] + \
-               [("layers", C.POINTER(LayerWeights))]
+                                   "wb_t", "bb", "mean_bias", "std_bias", "weight_bias", "tc_wa", "tc_wb")] + \
+               [("tc_head_lo", C.c_int32), ("tc_reserved", C.c_int32), ("layers", C.POINTER(LayerWeights))]
 
 
 class State(C.Structure):

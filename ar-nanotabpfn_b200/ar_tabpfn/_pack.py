@@ -18,6 +18,50 @@ from . import _lib
 _ALIGN = 64  # floats
 
 
+def _split_bf16(w: torch.Tensor):
+    """fp64 matrix -> (hi, lo) bf16 parts with hi + lo ~= w to 16 mantissa bits."""
+    hi = w.to(torch.float32).to(torch.bfloat16)
+    lo = (w - hi.to(torch.float64)).to(torch.float32).to(torch.bfloat16)
+    return hi, lo
+
+
+def _swizzle_block(blk: torch.Tensor) -> torch.Tensor:
+    """[rows][64] bf16 -> the 128-byte-swizzled K-major shared-memory image of that block:
+    16-byte chunk c of row r is stored at chunk position c ^ (r % 8)."""
+    rows = blk.shape[0]
+    chunks = blk.reshape(rows, 8, 8)
+    pos = torch.arange(8, device=blk.device)[None, :] ^ (torch.arange(rows, device=blk.device)[:, None] % 8)
+    out = torch.empty_like(chunks)
+    out.scatter_(1, pos[:, :, None].expand(rows, 8, 8), chunks)
+    return out.reshape(-1)
+
+
+def tile_weight(w: torch.Tensor, mode: str, force_lo: bool = False):
+    """Tile an nn.Linear weight [N][K] (fp64) for the tensor-core chain.
+
+    The result is the exact byte stream the kernel's weight ring consumes: a sequence of
+    slabs, each a stack of swizzled [rows][64 k] blocks, hi part then (optionally) lo part.
+      mode "full":   one slab per 64-wide k-chunk holding all N rows            (N = d_model)
+      mode "ntile":  one slab per 64-row output tile holding all its k-chunks   (hidden GEMMs)
+    Returns (flat bf16 tensor, has_lo)."""
+    N, K = w.shape
+    assert K % 64 == 0
+    hi, lo = _split_bf16(w)
+    has_lo = force_lo or bool((lo != 0).any())
+    slabs = []
+    if mode == "full":
+        for kc in range(K // 64):
+            for part in ((hi, lo) if has_lo else (hi,)):
+                slabs.append(_swizzle_block(part[:, kc * 64:(kc + 1) * 64].contiguous()))
+    else:
+        assert N % 64 == 0
+        for j in range(N // 64):
+            for part in ((hi, lo) if has_lo else (hi,)):
+                for kc in range(K // 64):
+                    slabs.append(_swizzle_block(part[j * 64:(j + 1) * 64, kc * 64:(kc + 1) * 64].contiguous()))
+    return torch.cat(slabs), has_lo
+
+
 class PackedModel:
     def __init__(self, embedder, backbone, head, ar_tokens, device: torch.device):
         layers = list(backbone.layers)
@@ -79,7 +123,8 @@ class PackedModel:
         self._layers = (_lib.LayerWeights * self.n_layers)()
         for i in range(self.n_layers):
             for f, _ in _lib.LayerWeights._fields_:
-                setattr(self._layers[i], f, P(f"{i}.{f}"))
+                if not f.startswith("tc_"):
+                    setattr(self._layers[i], f, P(f"{i}.{f}"))
         m = _lib.Model()
         m.d_model, m.n_heads, m.head_dim, m.d_ff = self.d_model, self.n_heads, self.head_dim, self.d_ff
         m.n_layers, m.n_comp, m.n_ar_tokens = self.n_layers, self.n_comp, self.n_ar
@@ -88,6 +133,62 @@ class PackedModel:
             setattr(m, f, P(f))
         m.layers = C.cast(self._layers, C.POINTER(_lib.LayerWeights))
         self.struct = m
+        self._pack_tensor_core(embedder, backbone, head, device)
+
+    def _pack_tensor_core(self, embedder, backbone, head, device):
+        """bf16 hi/lo tiles for the tcgen05 per-token chain (d_model in {64,128,192}, d_ff % 64 == 0,
+        3K <= 16).  Other shapes keep the fp32 FMA chain (the tc_* pointers stay NULL)."""
+        D, Dff = self.d_model, self.d_ff
+        self.tc_flat = None
+        if D not in (64, 128, 192) or Dff % 64 != 0 or 3 * self.n_comp > 16:
+            return
+        f64 = lambda t: t.detach().to(device=device, dtype=torch.float64)
+        items = []
+
+        def add(name, w, mode, force_lo=False):
+            flat, has_lo = tile_weight(w, mode, force_lo)
+            items.append((name, flat))
+            return has_lo
+
+        layer_lo = []
+        for i, l in enumerate(backbone.layers):
+            r = l.attn_rows
+            bits = 0
+            bits |= 1 * add(f"{i}.tc_wo", f64(r.out_proj.weight), "full")
+            bits |= 2 * add(f"{i}.tc_w1", f64(l.ff[0].weight), "ntile")
+            bits |= 4 * add(f"{i}.tc_w2", f64(l.ff[2].weight), "full")
+            wf = f64(l.attn_features.out_proj.weight) @ f64(l.attn_features.v_proj.weight)
+            bits |= 8 * add(f"{i}.tc_wf", wf, "full")
+            # q, k, v must agree on the lo part: they share one flag
+            qkv_lo = any(bool((_split_bf16(f64(p.weight))[1] != 0).any()) for p in (r.q_proj, r.k_proj, r.v_proj))
+            for nm, p in (("q", r.q_proj), ("k", r.k_proj), ("v", r.v_proj)):
+                add(f"{i}.tc_w{nm}", f64(p.weight), "full", force_lo=qkv_lo)
+            bits |= 16 * qkv_lo
+            layer_lo.append(bits)
+        head_bits = 1 * add("tc_wa", f64(head.head[0].weight), "ntile")
+        wb = torch.zeros(16, Dff, dtype=torch.float64, device=device)
+        wb[: 3 * self.n_comp] = f64(head.head[2].weight)
+        head_bits |= 2 * add("tc_wb", wb, "full")
+        offs, tot = {}, 0
+        for name, t in items:
+            offs[name] = tot
+            tot += (t.numel() + 511) // 512 * 512          # 1 KiB alignment of every matrix
+        flat = torch.zeros(tot, dtype=torch.bfloat16, device=device)
+        for name, t in items:
+            flat[offs[name]:offs[name] + t.numel()] = t
+        self.tc_flat = flat
+        base = flat.data_ptr()
+        for i in range(self.n_layers):
+            lw = self._layers[i]
+            lw.tc_wo = base + 2 * offs[f"{i}.tc_wo"]
+            lw.tc_w1 = base + 2 * offs[f"{i}.tc_w1"]
+            lw.tc_w2 = base + 2 * offs[f"{i}.tc_w2"]
+            lw.tc_wf = base + 2 * offs[f"{i}.tc_wf"]
+            lw.tc_wqkv = base + 2 * offs[f"{i}.tc_wq"]
+            lw.tc_lo = layer_lo[i]
+        self.struct.tc_wa = base + 2 * offs["tc_wa"]
+        self.struct.tc_wb = base + 2 * offs["tc_wb"]
+        self.struct.tc_head_lo = head_bits
 
     @property
     def ref(self):

@@ -175,6 +175,9 @@ void fill_head(const artab_model* m, DenseArgs& d) {
   d.mean_bias = m->mean_bias;
   d.std_bias = m->std_bias;
   d.weight_bias = m->weight_bias;
+  d.tc_wa = m->tc_wa;
+  d.tc_wb = m->tc_wb;
+  d.tc_head_lo = m->tc_head_lo;
 }
 
 DenseArgs dense_base(const artab_model* m, const artab_state* st, int rows) {

@@ -41,9 +41,13 @@ struct DenseArgs {
   float* ld_out;
   int32_t* comp_out;
   int32_t* status;     // device status word (bounded waits), may be null
+  const void *tc_wa, *tc_wb;  // tensor-core tiles of the head matrices (null: fp32 chain)
+  int tc_head_lo;
 };
 
 int launch_embed(const EmbedArgs& a, cudaStream_t s);
-int launch_dense(const DenseArgs& a, cudaStream_t s);
+int launch_dense(const DenseArgs& a, cudaStream_t s);     // picks the tensor-core chain when it applies
+int launch_dense_tc(const DenseArgs& a, cudaStream_t s);  // tcgen05 chain (bf16 mode)
+bool dense_tc_applicable(const DenseArgs& a);
 
 }  // namespace artab

@@ -8,6 +8,7 @@
 // plain fp32 FMA: this is the path that has to agree with the fp32 CPU
 // reference to 1e-5 on the log density, so no TF32 / bf16 operand rounding.
 #include "dense.cuh"
+#include "kv_scatter.cuh"
 
 namespace artab {
 
@@ -256,33 +257,6 @@ __device__ __forceinline__ void ln_rows(float* dst, int ldd, const float* a, int
   sync_compute(T);
 }
 
-template <typename T>
-__device__ __forceinline__ void scatter_kv(const KvDest& kv, long row, int c, float kval, float vval) {
-  const int h = c / kv.head_dim, d = c - h * kv.head_dim;
-  if (kv.mode == KV_PREFILL) {
-    const long g = row / kv.n_ctx, i = row - g * kv.n_ctx;
-    const size_t base = ((size_t)(g * kv.n_heads + h) * kv.n_ctx_pad);
-    reinterpret_cast<T*>(kv.k_ctx)[(base + i) * kv.head_dim + d] = from_f32<T>(kval);
-    if (kv.dtype == ARTAB_BF16) {  // transposed, split into a bf16 hi and lo part: [.., 2*Dh][Ncp]
-      T* vb = reinterpret_cast<T*>(kv.v_ctx) + ((size_t)(g * kv.n_heads + h) * 2 * kv.head_dim) * kv.n_ctx_pad + i;
-      const T hi = from_f32<T>(vval);
-      vb[(size_t)d * kv.n_ctx_pad] = hi;
-      vb[(size_t)(kv.head_dim + d) * kv.n_ctx_pad] = from_f32<T>(vval - to_f32<T>(hi));
-    } else {
-      reinterpret_cast<T*>(kv.v_ctx)[(base + i) * kv.head_dim + d] = from_f32<T>(vval);
-    }
-  } else {
-    const long b = row / kv.tokens_per_stream;
-    const int j = (int)(row - b * kv.tokens_per_stream);
-    if (j >= kv.n_kv_tokens) return;
-    const int pos = kv.pos0 + j;
-    T* p = reinterpret_cast<T*>(kv.kv_buf) +
-           (((size_t)(b * kv.n_heads + h) * kv.max_buf + pos) * 2) * kv.head_dim + d;
-    p[0] = from_f32<T>(kval);
-    p[kv.head_dim] = from_f32<T>(vval);
-  }
-}
-
 // One warp per head row: mixture parameters from raw[3K], then sample or log-pdf.
 __device__ __forceinline__ void head_row(const DenseArgs& a, const float* raw, long row) {
   const int lane = threadIdx.x & 31;
@@ -451,10 +425,13 @@ __global__ void __launch_bounds__(288) dense_chain_kernel(const DenseArgs a) {
         reinterpret_cast<float*>(a.q_out)[(size_t)row0 * D + i] = qv;
       if (a.kv.mode != KV_NONE) {
         const float kv_k = s_h[r * wide + D + c], kv_v = s_h[r * wide + 2 * D + c];
-        if (bf)
-          scatter_kv<__nv_bfloat16>(a.kv, row0 + r, c, kv_k, kv_v);
-        else
-          scatter_kv<float>(a.kv, row0 + r, c, kv_k, kv_v);
+        if (bf) {
+          scatter_k<__nv_bfloat16>(a.kv, row0 + r, c, kv_k);
+          scatter_v<__nv_bfloat16>(a.kv, row0 + r, c, kv_v);
+        } else {
+          scatter_k<float>(a.kv, row0 + r, c, kv_k);
+          scatter_v<float>(a.kv, row0 + r, c, kv_v);
+        }
       }
     }
   }
@@ -531,6 +508,7 @@ int launch_embed(const EmbedArgs& a, cudaStream_t s) {
 
 int launch_dense(const DenseArgs& a, cudaStream_t s) {
   if (a.rows <= 0) return ARTAB_OK;
+  if (dense_tc_applicable(a)) return launch_dense_tc(a, s);
   ARTAB_REQUIRE(a.D % 32 == 0 && a.Dff % 4 == 0 && a.D >= 32, ARTAB_EINVAL,
                 "dense chain: d_model must be a multiple of 32 and d_ff a multiple of 4 (got %d, %d)", a.D, a.Dff);
   ARTAB_REQUIRE(3 * a.n_comp <= a.D && a.n_comp <= 32, ARTAB_EINVAL, "dense chain: need 3*K <= d_model and K <= 32");

@@ -1,0 +1,799 @@
+// Per-token layer chain on the 5th-generation tensor cores (bf16 mode).
+//
+// One CTA owns 128 token rows and walks the same chain as the fp32 kernel
+// (out-proj + LN2 + MLP + LN3 [+ final LN + mixture head] [+ next layer's
+// feature fold + LN1 + QKV + KV scatter]).  Every GEMM is tcgen05.mma with the
+// accumulator in tensor memory:
+//   * activations are split into a bf16 hi and lo part (x = hi + lo, 16 mantissa
+//     bits) so that the products keep near-fp32 accuracy: rounding activations to
+//     plain bf16 moves the log density by 1.5e-2, far outside the 2e-3 bar;
+//   * the D-wide activation operand lives in TMEM (written by the epilogue threads
+//     with tcgen05.st, read as the A operand), the 64-wide hidden tile of the MLP
+//     goes through shared memory (swizzled K-major, written by the epilogue);
+//   * weights are bf16 hi(/lo) tiles pre-swizzled on the host into the exact
+//     shared-memory image, streamed by a producer warp with plain bulk copies
+//     through a 6-slot ring (full / empty mbarriers).
+// Warp 0: weight producer.  Warp 1: MMA issuer, owns the 512 TMEM columns.
+// Warps 2-9: 256 epilogue threads, two per row (each owns half of the columns);
+// LayerNorm statistics are exchanged through shared memory.
+// All mbarrier waits are bounded; on expiry the CTA flags an abort, stops
+// producing results, drains and frees TMEM.
+#include "dense.cuh"
+#include "kv_scatter.cuh"
+
+namespace artab {
+
+namespace {
+
+constexpr int BM = 128;          // token rows per CTA
+constexpr int HT = 64;           // hidden units per MLP tile
+constexpr int NSLOT = 6;         // weight ring depth
+constexpr int kThreads = 320;
+constexpr uint32_t kTmemCols = 512;
+constexpr uint32_t kAccA = 0;    // wide accumulator (<= 192 columns)
+constexpr uint32_t kAxHi = 192;  // activation operand, hi part (<= 96 packed columns)
+constexpr uint32_t kAxLo = 288;  // activation operand, lo part
+constexpr uint32_t kAccH = 384;  // two hidden-tile accumulators of 64 columns
+constexpr long long kWaitCycles = 2000000000LL;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint64_t* b, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(b)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* b) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(b)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint64_t* b, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(b)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* b, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_try(b, parity)) return true;
+  const long long t0 = clock64();
+  for (;;) {
+    if (mbar_try(b, parity)) return true;
+    if (*abort_flag) return false;
+    if (clock64() - t0 > kWaitCycles) {
+      *abort_flag = 1;
+      return false;
+    }
+  }
+}
+
+constexpr uint64_t kLayoutSw128 = 2;
+__device__ __forceinline__ uint64_t make_desc(uint32_t saddr) {  // K-major, 128-byte swizzle, 8-row groups 1 KiB apart
+  uint64_t d = (uint64_t)((saddr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)1 << 16;
+  d |= (uint64_t)(1024 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= kLayoutSw128 << 61;
+  return d;
+}
+__device__ __forceinline__ uint32_t make_idesc(int N) {  // M 128, fp32 accumulate, bf16 x bf16, K-major both
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+}
+__device__ __forceinline__ void umma_ss(uint32_t d_tmem, uint64_t a, uint64_t b, uint32_t idesc, uint32_t acc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a), "l"(b), "r"(idesc), "r"(acc)
+      : "memory");
+}
+__device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b, uint32_t idesc, uint32_t acc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b), "r"(idesc), "r"(acc)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,"
+      "%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t* r) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+        "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+// x -> (hi, lo) bf16 with hi + lo = x to 16 mantissa bits, for two neighbouring columns at once
+__device__ __forceinline__ void split2(float a, float b, uint32_t& hi, uint32_t& lo) {
+  const __nv_bfloat16 ah = __float2bfloat16_rn(a), bh = __float2bfloat16_rn(b);
+  hi = (uint32_t)__bfloat16_as_ushort(ah) | ((uint32_t)__bfloat16_as_ushort(bh) << 16);
+  lo = pack_bf16(a - __bfloat162float(ah), b - __bfloat162float(bh));
+}
+
+// erf by Abramowitz-Stegun 7.1.26 (|error| < 1.5e-7), exp on the MUFU pipe
+__device__ __forceinline__ float gelu_fast(float x) {
+  const float z = fabsf(x) * 0.70710678118654752f;
+  float t;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(t) : "f"(fmaf(0.3275911f, z, 1.0f)));
+  float poly = fmaf(1.061405429f, t, -1.453152027f);
+  poly = fmaf(poly, t, 1.421413741f);
+  poly = fmaf(poly, t, -0.284496736f);
+  poly = fmaf(poly, t, 0.254829592f);
+  poly *= t;
+  float e;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(-z * z * 1.4426950408889634f));
+  const float erf_abs = fmaf(-poly, e, 1.0f);
+  return 0.5f * x * (1.0f + copysignf(erf_abs, x));
+}
+
+#ifdef DENSE_TC_TIMING
+__device__ long long g_dbg[64];
+#define TSTAMP(i) do { if (blockIdx.x == 0 && threadIdx.x == 64) g_dbg[i] = clock64(); } while (0)
+#else
+#define TSTAMP(i)
+#endif
+
+struct __align__(1024) Smem {
+  uint8_t ring[NSLOT][192 * 128];     // weight slabs (d_model * 128 bytes each)
+  uint8_t ah[2][2][BM * 128];         // hidden tile operand [buffer][hi, lo][128 rows x 64 bf16], swizzled
+  float xs[2][2][BM];                 // LayerNorm partial sums exchanged between the two column halves
+  uint64_t w_full[NSLOT], w_empty[NSLOT];
+  uint64_t ep_done, acc_full, h_full[2], ah_ready[2], ah_free[2];
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+struct Ctx {
+  Smem* sm;
+  volatile int* abort_flag;
+  uint32_t tmem;
+};
+
+// ------------------------------------------------------------------ producer
+struct Producer {
+  Smem* sm;
+  int issued;
+  bool ok;
+  __device__ void slab(const uint8_t* src, uint32_t bytes) {
+    if (!ok) return;
+    const int buf = issued % NSLOT;
+    if (issued >= NSLOT && !mbar_wait(&sm->w_empty[buf], ((issued / NSLOT) + 1) & 1, &sm->abort_flag)) {
+      ok = false;
+      return;
+    }
+    uint64_t* bar = &sm->w_full[buf];
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+                 : "memory");
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(smem_u32(sm->ring[buf])), "l"(src), "r"(bytes), "r"(smem_u32(bar))
+                 : "memory");
+    ++issued;
+  }
+  // all slabs of a matrix consumed in order ("full" layout: one k-chunk group after the other)
+  __device__ void matrix(const void* w, int groups, bool has_lo, uint32_t slab_bytes) {
+    const uint8_t* p = reinterpret_cast<const uint8_t*>(w);
+    const int n = groups * (has_lo ? 2 : 1);
+    for (int i = 0; i < n; ++i) slab(p + (size_t)i * slab_bytes, slab_bytes);
+  }
+  // two-GEMM MLP: hidden tiles of w1 interleaved with the k-chunks of w2, one tile of look-ahead
+  __device__ void mlp(const void* w1, bool lo1, uint32_t bytes1, const void* w2, bool lo2, uint32_t bytes2, int nt) {
+    const uint8_t* p1 = reinterpret_cast<const uint8_t*>(w1);
+    const uint8_t* p2 = reinterpret_cast<const uint8_t*>(w2);
+    const int s1 = lo1 ? 2 : 1, s2 = lo2 ? 2 : 1;
+    for (int j = 0; j < nt; ++j) {
+      for (int i = 0; i < s1; ++i) slab(p1 + (size_t)(j * s1 + i) * bytes1, bytes1);
+      if (j >= 1)
+        for (int i = 0; i < s2; ++i) slab(p2 + (size_t)((j - 1) * s2 + i) * bytes2, bytes2);
+    }
+    for (int i = 0; i < s2; ++i) slab(p2 + (size_t)((nt - 1) * s2 + i) * bytes2, bytes2);
+  }
+};
+
+// ---------------------------------------------------------------- MMA issuer
+struct Issuer {
+  Smem* sm;
+  uint32_t tmem;
+  int consumed;     // ring slabs consumed
+  int ep_phase;     // completed waits on ep_done
+  int ah_count[2];  // completed waits on ah_ready[b]
+  bool ok;
+
+  __device__ uint32_t slab_wait() {
+    const int buf = consumed % NSLOT;
+    ok = ok && mbar_wait(&sm->w_full[buf], (consumed / NSLOT) & 1, &sm->abort_flag);
+    tc_fence_after();
+    return smem_u32(sm->ring[buf]);
+  }
+  __device__ void slab_release() {
+    umma_commit(&sm->w_empty[consumed % NSLOT]);
+    ++consumed;
+  }
+  __device__ void wait_epilogue() {
+    ok = ok && mbar_wait(&sm->ep_done, ep_phase & 1, &sm->abort_flag);
+    ++ep_phase;
+    tc_fence_after();
+  }
+  // ACC[acc_col] = A_x . W^T with W streamed as `nkc` slabs of [n_out rows][64 k]
+  __device__ void gemm_full_ts(uint32_t acc_col, int n_out, int nkc, bool has_lo) {
+    const uint32_t idesc = make_idesc(n_out);
+    for (int kc = 0; kc < nkc; ++kc) {
+      const uint32_t hi = slab_wait();
+#pragma unroll
+      for (int ks = 0; ks < 4; ++ks)
+        umma_ts(tmem + acc_col, tmem + kAxHi + kc * 32 + ks * 8, make_desc(hi + 32 * ks), idesc, (kc | ks) != 0);
+#pragma unroll
+      for (int ks = 0; ks < 4; ++ks)
+        umma_ts(tmem + acc_col, tmem + kAxLo + kc * 32 + ks * 8, make_desc(hi + 32 * ks), idesc, 1);
+      slab_release();
+      if (has_lo) {
+        const uint32_t lo = slab_wait();
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks)
+          umma_ts(tmem + acc_col, tmem + kAxHi + kc * 32 + ks * 8, make_desc(lo + 32 * ks), idesc, 1);
+        slab_release();
+      }
+    }
+  }
+  // ACC[acc_col] (64 columns) = A_x . W_tile^T, the slab holds the tile's nkc blocks of [64 rows][64 k]
+  __device__ void gemm_tile_ts(uint32_t acc_col, int nkc, bool has_lo) {
+    const uint32_t idesc = make_idesc(HT);
+    const uint32_t hi = slab_wait();
+    for (int kc = 0; kc < nkc; ++kc)
+#pragma unroll
+      for (int ks = 0; ks < 4; ++ks)
+        umma_ts(tmem + acc_col, tmem + kAxHi + kc * 32 + ks * 8, make_desc(hi + kc * (HT * 128) + 32 * ks), idesc,
+                (kc | ks) != 0);
+    for (int kc = 0; kc < nkc; ++kc)
+#pragma unroll
+      for (int ks = 0; ks < 4; ++ks)
+        umma_ts(tmem + acc_col, tmem + kAxLo + kc * 32 + ks * 8, make_desc(hi + kc * (HT * 128) + 32 * ks), idesc, 1);
+    slab_release();
+    if (has_lo) {
+      const uint32_t lo = slab_wait();
+      for (int kc = 0; kc < nkc; ++kc)
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks)
+          umma_ts(tmem + acc_col, tmem + kAxHi + kc * 32 + ks * 8, make_desc(lo + kc * (HT * 128) + 32 * ks), idesc, 1);
+      slab_release();
+    }
+  }
+  // ACC[acc_col] (+)= A_h[b] . W_chunk^T  (K = 64, A from shared memory)
+  __device__ void gemm_chunk_ss(uint32_t acc_col, int n_out, int b, bool has_lo, bool accumulate) {
+    const uint32_t idesc = make_idesc(n_out);
+    const uint32_t a_hi = smem_u32(sm->ah[b][0]), a_lo = smem_u32(sm->ah[b][1]);
+    const uint32_t hi = slab_wait();
+#pragma unroll
+    for (int ks = 0; ks < 4; ++ks)
+      umma_ss(tmem + acc_col, make_desc(a_hi + 32 * ks), make_desc(hi + 32 * ks), idesc, accumulate || ks != 0);
+#pragma unroll
+    for (int ks = 0; ks < 4; ++ks) umma_ss(tmem + acc_col, make_desc(a_lo + 32 * ks), make_desc(hi + 32 * ks), idesc, 1);
+    slab_release();
+    if (has_lo) {
+      const uint32_t lo = slab_wait();
+#pragma unroll
+      for (int ks = 0; ks < 4; ++ks) umma_ss(tmem + acc_col, make_desc(a_hi + 32 * ks), make_desc(lo + 32 * ks), idesc, 1);
+      slab_release();
+    }
+  }
+  // hidden = act(A_x . W1^T) tile by tile, ACC_A = hidden . W2^T; one tile of look-ahead
+  __device__ void mlp(int nkc, bool lo1, bool lo2, int nt, int n_out) {
+    for (int j = 0; j < nt; ++j) {
+      gemm_tile_ts(kAccH + 64 * (j & 1), nkc, lo1);
+      umma_commit(&sm->h_full[j & 1]);
+      if (j >= 1) second(j - 1, lo2, n_out);
+    }
+    second(nt - 1, lo2, n_out);
+    umma_commit(&sm->acc_full);
+  }
+  __device__ void second(int j, bool lo2, int n_out) {
+    const int b = j & 1;
+    ok = ok && mbar_wait(&sm->ah_ready[b], ah_count[b] & 1, &sm->abort_flag);
+    ++ah_count[b];
+    tc_fence_after();
+    gemm_chunk_ss(kAccA, n_out, b, lo2, j > 0);
+    umma_commit(&sm->ah_free[b]);
+  }
+};
+
+// ------------------------------------------------------------------ epilogue
+template <int D>
+struct Epilogue {
+  static constexpr int HALF = D / 2;       // columns owned by one thread
+  static constexpr int NCH = HALF / 32;    // 32-column chunks
+  Smem* sm;
+  uint32_t t_row;                          // TMEM address of this thread's lane
+  int row, wg, col0;
+  int acc_phase, xs_phase;
+  int h_count[2], free_count[2];
+  bool ok;
+
+  __device__ void sync_halves() { asm volatile("bar.sync 3, 256;" ::: "memory"); }
+
+  __device__ void wait_acc() {
+    ok = mbar_wait(&sm->acc_full, acc_phase & 1, &sm->abort_flag) && ok;
+    ++acc_phase;
+    tc_fence_after();
+  }
+  // v[i] += ACC_A[col0 + i]
+  __device__ void add_acc(float* v) {
+    uint32_t r[32];
+#pragma unroll
+    for (int c = 0; c < NCH; ++c) {
+      tmem_ld32(t_row + kAccA + col0 + 32 * c, r);
+      tmem_wait_ld();
+#pragma unroll
+      for (int i = 0; i < 32; ++i) v[32 * c + i] += __uint_as_float(r[i]);
+    }
+  }
+  // A_x <- split(v) for this thread's columns, then tell the MMA warp
+  __device__ void publish_ax(const float* v) {
+#pragma unroll
+    for (int c = 0; c < NCH; ++c) {
+      uint32_t hi[16], lo[16];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) split2(v[32 * c + 2 * i], v[32 * c + 2 * i + 1], hi[i], lo[i]);
+      tmem_st16(t_row + kAxHi + (col0 >> 1) + 16 * c, hi);
+      tmem_st16(t_row + kAxLo + (col0 >> 1) + 16 * c, lo);
+    }
+    done();
+  }
+  __device__ void done() {
+    tmem_wait_st();
+    tc_fence_before();
+    mbar_arrive(&sm->ep_done);
+  }
+  // LayerNorm over the full row (two threads, one per column half)
+  __device__ void layer_norm(float* v, const float* __restrict__ gamma, const float* __restrict__ beta) {
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < HALF; ++i) s += v[i];
+    const int ph = xs_phase & 1;
+    ++xs_phase;
+    sm->xs[ph][wg][row] = s;
+    sync_halves();
+    const float mean = (wg == 0 ? s + sm->xs[ph][1][row] : sm->xs[ph][0][row] + s) / (float)D;
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < HALF; ++i) {
+      const float d = v[i] - mean;
+      ss = fmaf(d, d, ss);
+    }
+    const int ph2 = xs_phase & 1;
+    ++xs_phase;
+    sm->xs[ph2][wg][row] = ss;
+    sync_halves();
+    const float var = (wg == 0 ? ss + sm->xs[ph2][1][row] : sm->xs[ph2][0][row] + ss) / (float)D;
+    const float rstd = 1.0f / sqrtf(var + 1e-5f);
+#pragma unroll
+    for (int i = 0; i < HALF; ++i)
+      v[i] = (v[i] - mean) * rstd * __ldg(gamma + col0 + i) + __ldg(beta + col0 + i);
+  }
+  // hidden tile j: act(ACC_H + bias) -> split -> swizzled shared-memory operand
+  __device__ void hidden_tile(int j, const float* __restrict__ bias) {
+    const int b = j & 1;
+    ok = mbar_wait(&sm->h_full[b], h_count[b] & 1, &sm->abort_flag) && ok;
+    ++h_count[b];
+    tc_fence_after();
+    uint32_t r[32];
+    tmem_ld32(t_row + kAccH + 64 * b + 32 * wg, r);
+    tmem_wait_ld();
+    uint32_t hi[16], lo[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const float x0 = gelu_fast(__uint_as_float(r[2 * i]) + __ldg(bias + j * HT + 32 * wg + 2 * i));
+      const float x1 = gelu_fast(__uint_as_float(r[2 * i + 1]) + __ldg(bias + j * HT + 32 * wg + 2 * i + 1));
+      split2(x0, x1, hi[i], lo[i]);
+    }
+    if (j >= 2) {  // the MMA that read this buffer two tiles ago must be complete
+      ok = mbar_wait(&sm->ah_free[b], free_count[b] & 1, &sm->abort_flag) && ok;
+      ++free_count[b];
+    }
+    // row r, 16-byte chunk c of the 128-byte row lives at chunk position c ^ (r % 8)
+    uint8_t* base_hi = sm->ah[b][0] + row * 128;
+    uint8_t* base_lo = sm->ah[b][1] + row * 128;
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      const int pos = ((4 * wg + c) ^ (row & 7)) * 16;
+      *reinterpret_cast<uint4*>(base_hi + pos) = make_uint4(hi[4 * c], hi[4 * c + 1], hi[4 * c + 2], hi[4 * c + 3]);
+      *reinterpret_cast<uint4*>(base_lo + pos) = make_uint4(lo[4 * c], lo[4 * c + 1], lo[4 * c + 2], lo[4 * c + 3]);
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic writes -> visible to the MMA's reads
+    tc_fence_before();
+    mbar_arrive(&sm->ah_ready[b]);
+  }
+  // After an MLP: consume the ah_free completions of its last tile(s), which no hidden_tile waited
+  // for, so that the parity bookkeeping is exact when a second MLP runs in the same launch.
+  __device__ void drain_free(int nt) {
+    for (int j = nt >= 2 ? nt - 2 : 0; j < nt; ++j) {
+      ok = mbar_wait(&sm->ah_free[j & 1], free_count[j & 1] & 1, &sm->abort_flag) && ok;
+      ++free_count[j & 1];
+    }
+  }
+};
+
+// Mixture head for one row from raw[3K] (one thread): sample or log-pdf.
+__device__ __forceinline__ void head_row_thread(const DenseArgs& a, const float* raw, long row) {
+  const int K = a.n_comp;
+  const long b = row / a.head_tps;
+  const int j = (int)(row - b * a.head_tps);
+  if (j < a.head_first) return;
+  const long oidx = b * a.out_stride + a.out_col + (j - a.head_first);
+  float mean[8], stdv[8], lw[8];
+  float mx = -INFINITY;
+  for (int k = 0; k < K; ++k) {
+    mean[k] = raw[3 * k] + __ldg(a.mean_bias + k);
+    const float sr = raw[3 * k + 1] + __ldg(a.std_bias + k);
+    const float sp = sr > 20.f ? sr : log1pf(expf(sr));
+    stdv[k] = fminf(sp, 2.0f) + 1e-3f;
+    lw[k] = raw[3 * k + 2] + __ldg(a.weight_bias + k);
+    mx = fmaxf(mx, lw[k]);
+  }
+  float se = 0.f;
+  for (int k = 0; k < K; ++k) se += expf(lw[k] - mx);
+  const float lse = mx + logf(se);
+  float y;
+  if (a.head_mode == 1) {
+    int best = 0;
+    float bv = -1.f;
+    for (int k = 0; k < K; ++k) {
+      const float ratio = expf(lw[k] - lse) / __ldg(a.expo + b * K + k);
+      if (ratio > bv) {
+        bv = ratio;
+        best = k;
+      }
+    }
+    y = mean[best] + stdv[best] * __ldg(a.normal + b);
+    a.y_out[oidx] = y;
+    if (a.comp_out) a.comp_out[oidx] = best;
+  } else {
+    y = __ldg(a.y_in + oidx);
+  }
+  if (a.ld_out) {
+    float lp[8], m2 = -INFINITY;
+    for (int k = 0; k < K; ++k) {
+      const float zz = (y - mean[k]) / stdv[k];
+      lp[k] = -0.5f * (1.8378770664093453f + 2.0f * logf(stdv[k]) + zz * zz) + (lw[k] - lse);
+      m2 = fmaxf(m2, lp[k]);
+    }
+    float s2 = 0.f;
+    for (int k = 0; k < K; ++k) s2 += expf(lp[k] - m2);
+    a.ld_out[oidx] = m2 + logf(s2);
+  }
+}
+
+template <int D>
+__global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const DenseArgs a) {
+  extern __shared__ uint8_t smem_raw[];
+  Smem* sm = reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  constexpr int NKC = D / 64;
+  constexpr uint32_t kSlab = D * 128;
+  const int nt = a.Dff / HT;
+  const long row0 = (long)blockIdx.x * BM;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < NSLOT; ++i) {
+      mbar_init(&sm->w_full[i], 1);
+      mbar_init(&sm->w_empty[i], 1);
+    }
+    mbar_init(&sm->ep_done, 256);
+    mbar_init(&sm->acc_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&sm->h_full[i], 1);
+      mbar_init(&sm->ah_ready[i], 256);
+      mbar_init(&sm->ah_free[i], 1);
+    }
+    sm->abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm->tmem_base)),
+                 "r"(kTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = sm->tmem_base;
+
+  const int lo_post = a.post_w.tc_lo, lo_pre = a.pre_w.tc_lo;
+
+  if (warp == 0) {
+    // ------------------------------ weight producer ------------------------------
+    if (lane == 0) {
+      Producer p{sm, 0, true};
+      if (a.do_post) {
+        p.matrix(a.post_w.tc_wo, NKC, lo_post & 1, kSlab);
+        p.mlp(a.post_w.tc_w1, lo_post & 2, kSlab, a.post_w.tc_w2, lo_post & 4, kSlab, nt);
+      }
+      if (a.do_head) {
+        p.mlp(a.tc_wa, a.tc_head_lo & 1, kSlab, a.tc_wb, a.tc_head_lo & 2, 16 * 128, nt);
+      } else if (a.do_pre) {
+        p.matrix(a.pre_w.tc_wf, NKC, lo_pre & 8, kSlab);
+        p.matrix(a.pre_w.tc_wqkv, 3 * NKC, lo_pre & 16, kSlab);
+      }
+    }
+  } else if (warp == 1) {
+    // --------------------------------- MMA issuer ---------------------------------
+    if (lane == 0) {
+      Issuer m{sm, tmem, 0, 0, {0, 0}, true};
+      if (a.do_post) {
+        m.wait_epilogue();                               // A_x = attention output
+        m.gemm_full_ts(kAccA, D, NKC, lo_post & 1);
+        umma_commit(&sm->acc_full);
+        m.wait_epilogue();                               // A_x = x2 (and ACC_A drained)
+        m.mlp(NKC, lo_post & 2, lo_post & 4, nt, D);
+      }
+      if (a.do_head) {
+        m.wait_epilogue();                               // A_x = z
+        m.mlp(NKC, a.tc_head_lo & 1, a.tc_head_lo & 2, nt, 16);
+      } else if (a.do_pre) {
+        m.wait_epilogue();                               // A_x = layer input
+        m.gemm_full_ts(kAccA, D, NKC, lo_pre & 8);
+        umma_commit(&sm->acc_full);
+        m.wait_epilogue();                               // A_x = x1
+        for (int t = 0; t < 3; ++t) {
+          if (t > 0) m.wait_epilogue();                  // previous projection drained from ACC_A
+          m.gemm_full_ts(kAccA, D, NKC, lo_pre & 16);
+          umma_commit(&sm->acc_full);
+        }
+      }
+    }
+  } else {
+    // ---------------------------------- epilogue ----------------------------------
+    Epilogue<D> e;
+    constexpr int HALF = Epilogue<D>::HALF;
+    e.sm = sm;
+    e.row = 32 * (warp & 3) + lane;
+    e.wg = warp >= 6 ? 1 : 0;
+    e.col0 = e.wg * HALF;
+    e.t_row = tmem + ((uint32_t)(32 * (warp & 3)) << 16);
+    e.acc_phase = e.xs_phase = 0;
+    e.h_count[0] = e.h_count[1] = e.free_count[0] = e.free_count[1] = 0;
+    e.ok = true;
+    const long grow = row0 + e.row;
+    const bool valid = grow < a.rows;
+    const size_t goff = (size_t)grow * D + e.col0;
+    float v[HALF];
+
+    auto load_row = [&](const float* src) {
+#pragma unroll
+      for (int i = 0; i < HALF; i += 4) {
+        const float4 t = valid ? *reinterpret_cast<const float4*>(src + goff + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+        v[i] = t.x; v[i + 1] = t.y; v[i + 2] = t.z; v[i + 3] = t.w;
+      }
+    };
+    auto store_row = [&](float* dst) {
+      if (!valid) return;
+#pragma unroll
+      for (int i = 0; i < HALF; i += 4)
+        *reinterpret_cast<float4*>(dst + goff + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+    };
+
+    TSTAMP(0);
+    if (a.do_post) {
+      load_row(a.attn);
+      TSTAMP(1);
+      e.publish_ax(v);
+      load_row(a.x1_in);                         // residual
+      TSTAMP(2);
+      e.wait_acc();
+      TSTAMP(3);
+      e.add_acc(v);
+      e.layer_norm(v, a.post_w.ln2_g, a.post_w.ln2_b);   // v = x2
+      TSTAMP(4);
+      e.publish_ax(v);
+      TSTAMP(5);
+      for (int j = 0; j < nt; ++j) { e.hidden_tile(j, a.post_w.b1); TSTAMP(6 + j); }
+      e.wait_acc();
+      TSTAMP(20);
+      e.drain_free(nt);
+#pragma unroll
+      for (int i = 0; i < HALF; ++i) v[i] += __ldg(a.post_w.b2 + e.col0 + i);
+      e.add_acc(v);
+      e.layer_norm(v, a.post_w.ln3_g, a.post_w.ln3_b);   // v = x3
+      TSTAMP(21);
+      if (a.x_out) store_row(a.x_out);
+    } else {
+      load_row(a.x_in);
+    }
+    if (a.do_final) {
+      e.layer_norm(v, a.lnf_g, a.lnf_b);                 // v = z
+      if (a.z_out) store_row(a.z_out);
+    }
+    if (a.do_head) {
+      e.publish_ax(v);
+      for (int j = 0; j < nt; ++j) e.hidden_tile(j, a.ba);
+      e.wait_acc();
+      e.drain_free(nt);
+      if (e.wg == 0) {
+        uint32_t r[16];
+        tmem_ld16(e.t_row + kAccA, r);
+        tmem_wait_ld();
+        float raw[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) raw[i] = __uint_as_float(r[i]) + (i < 3 * a.n_comp ? __ldg(a.bb + i) : 0.f);
+        if (valid && e.ok) head_row_thread(a, raw, grow);
+      }
+    } else if (a.do_pre) {
+      e.publish_ax(v);
+      TSTAMP(22);
+      e.wait_acc();
+      TSTAMP(23);
+      e.add_acc(v);
+      e.layer_norm(v, a.pre_w.ln1_g, a.pre_w.ln1_b);     // v = x1
+      store_row(a.x1_out);
+      e.publish_ax(v);
+      TSTAMP(24);
+      // q, k, v projections, one accumulator round each.  Destinations of this row's K / V are
+      // resolved once (no per-element division): context cache rows during prefill, the private
+      // buffer slot (in-place append) otherwise.
+      const int Dh = a.kv.head_dim;
+      const int dh_shift = Dh == 16 ? 4 : (Dh == 32 ? 5 : 6);
+      __nv_bfloat16* k_dst = nullptr;   // element (h, d) at k_dst + h * k_hstride + d
+      __nv_bfloat16* v_dst = nullptr;   // buffer / fp-layout V: v_dst + h * k_hstride + d
+      __nv_bfloat16* vt_dst = nullptr;  // transposed hi|lo context V: vt_dst + (h * 2 * Dh + d) * Ncp
+      size_t k_hstride = 0;
+      if (valid && a.kv.mode == KV_PREFILL) {
+        const long g = grow / a.kv.n_ctx, i = grow - g * a.kv.n_ctx;
+        k_hstride = (size_t)a.kv.n_ctx_pad * Dh;
+        k_dst = reinterpret_cast<__nv_bfloat16*>(a.kv.k_ctx) + ((size_t)g * a.kv.n_heads * a.kv.n_ctx_pad + i) * Dh;
+        vt_dst = reinterpret_cast<__nv_bfloat16*>(a.kv.v_ctx) + (size_t)g * a.kv.n_heads * 2 * Dh * a.kv.n_ctx_pad + i;
+      } else if (valid && (a.kv.mode == KV_DECODE || a.kv.mode == KV_TF)) {
+        const long b = grow / a.kv.tokens_per_stream;
+        const int j = (int)(grow - b * a.kv.tokens_per_stream);
+        if (j < a.kv.n_kv_tokens) {
+          k_hstride = (size_t)a.kv.max_buf * 2 * Dh;
+          k_dst = reinterpret_cast<__nv_bfloat16*>(a.kv.kv_buf) +
+                  ((size_t)b * a.kv.n_heads * a.kv.max_buf + a.kv.pos0 + j) * 2 * Dh;
+          v_dst = k_dst + Dh;
+        }
+      }
+      for (int t = 0; t < 3; ++t) {
+        e.wait_acc();
+        uint32_t r[32];
+#pragma unroll
+        for (int c = 0; c < Epilogue<D>::NCH; ++c) {
+          tmem_ld32(e.t_row + kAccA + e.col0 + 32 * c, r);
+          tmem_wait_ld();
+          const int cbase = e.col0 + 32 * c;
+          if (t == 0 || (t == 1 && k_dst) || (t == 2 && v_dst)) {
+            uint32_t pk[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) pk[i] = pack_bf16(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
+            if (t == 0) {
+              if (valid) {
+                uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(a.q_out) + goff + 32 * c);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) dst[i] = make_uint4(pk[4 * i], pk[4 * i + 1], pk[4 * i + 2], pk[4 * i + 3]);
+              }
+            } else {
+              __nv_bfloat16* base = t == 1 ? k_dst : v_dst;
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {  // 8 columns = 16 bytes, never straddles a head (Dh % 8 == 0)
+                const int col = cbase + 8 * i;
+                const int h = col >> dh_shift, d = col & (Dh - 1);
+                *reinterpret_cast<uint4*>(base + (size_t)h * k_hstride + d) =
+                    make_uint4(pk[4 * i], pk[4 * i + 1], pk[4 * i + 2], pk[4 * i + 3]);
+              }
+            }
+          } else if (t == 2 && vt_dst) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              const int col = cbase + i;
+              const int h = col >> dh_shift, d = col & (Dh - 1);
+              const float val = __uint_as_float(r[i]);
+              const __nv_bfloat16 hi = __float2bfloat16_rn(val);
+              __nv_bfloat16* p = vt_dst + ((size_t)h * 2 * Dh + d) * a.kv.n_ctx_pad;
+              p[0] = hi;
+              p[(size_t)Dh * a.kv.n_ctx_pad] = __float2bfloat16_rn(val - __bfloat162float(hi));
+            }
+          }
+        }
+        if (t < 2) {  // accumulator drained: the next projection may overwrite it
+          tc_fence_before();
+          mbar_arrive(&sm->ep_done);
+        }
+        TSTAMP(25 + t);
+      }
+    }
+    if (!e.ok && threadIdx.x == 64 && a.status) atomicExch(a.status, 3);
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
+  }
+}
+
+}  // namespace
+
+#ifdef DENSE_TC_TIMING
+extern "C" ARTAB_API int artab_debug_read(long long* out) {
+  return (int)cudaMemcpyFromSymbol(out, g_dbg, sizeof(long long) * 64);
+}
+#endif
+
+bool dense_tc_applicable(const DenseArgs& a) {
+  if (a.kv.dtype != ARTAB_BF16) return false;
+  if (!(a.D == 64 || a.D == 128 || a.D == 192) || a.Dff % HT != 0 || 3 * a.n_comp > 16 || a.n_comp > 8) return false;
+  if (a.do_post && !(a.post_w.tc_wo && a.post_w.tc_w1 && a.post_w.tc_w2)) return false;
+  if (a.do_pre && !(a.pre_w.tc_wf && a.pre_w.tc_wqkv)) return false;
+  if (a.do_head && !(a.tc_wa && a.tc_wb)) return false;
+  if (!a.do_post && !a.do_pre && !a.do_head) return false;
+  return true;
+}
+
+int launch_dense_tc(const DenseArgs& a, cudaStream_t s) {
+  if (a.rows <= 0) return ARTAB_OK;
+  ARTAB_REQUIRE(dense_tc_applicable(a), ARTAB_EINVAL, "tensor-core dense chain: unsupported shape or missing tiles");
+  const size_t smem = sizeof(Smem) + 1024;
+  const int grid = (a.rows + BM - 1) / BM;
+  cudaError_t e = cudaSuccess;
+  static bool configured[3] = {false, false, false};
+  prof_begin(PROF_DENSE, s);
+  switch (a.D) {
+    case 64:
+      if (!configured[0]) {
+        e = cudaFuncSetAttribute(dense_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        configured[0] = e == cudaSuccess;
+      }
+      if (e == cudaSuccess) dense_tc_kernel<64><<<grid, kThreads, smem, s>>>(a);
+      break;
+    case 128:
+      if (!configured[1]) {
+        e = cudaFuncSetAttribute(dense_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        configured[1] = e == cudaSuccess;
+      }
+      if (e == cudaSuccess) dense_tc_kernel<128><<<grid, kThreads, smem, s>>>(a);
+      break;
+    default:
+      if (!configured[2]) {
+        e = cudaFuncSetAttribute(dense_tc_kernel<192>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        configured[2] = e == cudaSuccess;
+      }
+      if (e == cudaSuccess) dense_tc_kernel<192><<<grid, kThreads, smem, s>>>(a);
+      break;
+  }
+  prof_end(s);
+  ARTAB_REQUIRE(e == cudaSuccess, ARTAB_ELAUNCH, "dense_tc_kernel: shared memory refused: %s", cudaGetErrorString(e));
+  count_launch();
+  return check_launch("dense_tc_kernel");
+}
+
+}  // namespace artab

@@ -70,6 +70,19 @@ typedef struct artab_layer_weights {
   const float* b2;      /* [D] */
   const float* ln3_g;
   const float* ln3_b;
+  /* Optional bf16 copies for the tensor-core chain (NULL: the fp32 FMA chain runs).  Each is
+   * the byte stream the kernel's weight ring consumes: slabs of d_model*128 bytes made of
+   * [rows][64 k] blocks in the 128-byte-swizzled K-major shared-memory image, a bf16 "hi"
+   * slab followed by a "lo" slab (w = hi + lo) when the matching tc_lo bit is set.
+   *   tc_wo, tc_wf, tc_wqkv (q, k, v one after the other): one slab per 64-wide k-chunk, all rows;
+   *   tc_w1: one slab per 64-row output tile (all its k-chunks); tc_w2: one slab per k-chunk. */
+  const void* tc_wo;
+  const void* tc_w1;
+  const void* tc_w2;
+  const void* tc_wf;
+  const void* tc_wqkv;
+  int32_t tc_lo;        /* bit 0 wo, 1 w1, 2 w2, 3 wf, 4 wqkv: the matrix carries lo slabs */
+  int32_t tc_reserved;
 } artab_layer_weights;
 
 typedef struct artab_model {
@@ -89,6 +102,10 @@ typedef struct artab_model {
   const float* mean_bias;    /* [K] */
   const float* std_bias;     /* [K] */
   const float* weight_bias;  /* [K] */
+  const void* tc_wa;         /* head.head.0 tiled like tc_w1 (NULL: fp32 chain) */
+  const void* tc_wb;         /* head.head.2 padded to 16 rows, tiled like tc_w2 */
+  int32_t tc_head_lo;        /* bit 0 wa, bit 1 wb */
+  int32_t tc_reserved;
   const artab_layer_weights* layers; /* HOST pointer to n_layers entries */
 } artab_model;
 
