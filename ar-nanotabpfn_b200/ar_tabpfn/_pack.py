@@ -42,7 +42,7 @@ def tile_weight(w: torch.Tensor, mode: str, force_lo: bool = False):
     The result is the exact byte stream the kernel's weight ring consumes: a sequence of
     slabs, each a stack of swizzled [rows][64 k] blocks, hi part then (optionally) lo part.
       mode "full":   one slab per 64-wide k-chunk holding all N rows            (N = d_model)
-      mode "ntile":  one slab per 64-row output tile holding all its k-chunks   (hidden GEMMs)
+      mode "ntile":  per 128-row output tile one 16 KB slab per k-chunk         (hidden GEMMs)
     Returns (flat bf16 tensor, has_lo)."""
     N, K = w.shape
     assert K % 64 == 0
@@ -54,11 +54,11 @@ def tile_weight(w: torch.Tensor, mode: str, force_lo: bool = False):
             for part in ((hi, lo) if has_lo else (hi,)):
                 slabs.append(_swizzle_block(part[:, kc * 64:(kc + 1) * 64].contiguous()))
     else:
-        assert N % 64 == 0
-        for j in range(N // 64):
+        assert N % 128 == 0
+        for j in range(N // 128):
             for part in ((hi, lo) if has_lo else (hi,)):
                 for kc in range(K // 64):
-                    slabs.append(_swizzle_block(part[j * 64:(j + 1) * 64, kc * 64:(kc + 1) * 64].contiguous()))
+                    slabs.append(_swizzle_block(part[j * 128:(j + 1) * 128, kc * 64:(kc + 1) * 64].contiguous()))
     return torch.cat(slabs), has_lo
 
 
@@ -136,11 +136,11 @@ class PackedModel:
         self._pack_tensor_core(embedder, backbone, head, device)
 
     def _pack_tensor_core(self, embedder, backbone, head, device):
-        """bf16 hi/lo tiles for the tcgen05 per-token chain (d_model in {64,128,192}, d_ff % 64 == 0,
+        """bf16 hi/lo tiles for the tcgen05 per-token chain (d_model in {64,128,192}, d_ff % 128 == 0,
         3K <= 16).  Other shapes keep the fp32 FMA chain (the tc_* pointers stay NULL)."""
         D, Dff = self.d_model, self.d_ff
         self.tc_flat = None
-        if D not in (64, 128, 192) or Dff % 64 != 0 or 3 * self.n_comp > 16:
+        if D not in (64, 128, 192) or Dff % 128 != 0 or Dff > 1024 or 3 * self.n_comp > 16:
             return
         f64 = lambda t: t.detach().to(device=device, dtype=torch.float64)
         items = []

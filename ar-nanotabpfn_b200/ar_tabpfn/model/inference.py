@@ -132,6 +132,7 @@ class ARTabPFNPredictor:
         if rows <= st.max_rows:
             return
         D, H, Dh = pm.d_model, pm.n_heads, pm.head_dim
+        rows = (rows + 127) // 128 * 128   # whole 128-row tiles: the tensor-core chain reads padded tiles
         cdt = torch.bfloat16 if st.dtype == _lib.BF16 else torch.float32
         st.x = self._alloc("x", (rows, D), torch.float32).data_ptr()
         st.x1 = self._alloc("x1", (rows, D), torch.float32).data_ptr()

@@ -140,6 +140,25 @@ int plan_splits(int dtype, int head_dim, int rows, int rows_per_group, int n_gro
   return best;
 }
 
+// The tensor-core chain reads attn / x1 in the lane-major layout (workspaces padded to 128 rows).
+bool chain_on_tc(const artab_model* m, const artab_state* st) {
+  if (st->dtype != ARTAB_BF16 || !m->tc_wa || !m->tc_wb) return false;
+  for (int l = 0; l < m->n_layers; ++l)
+    if (!m->layers[l].tc_wo || !m->layers[l].tc_w1 || !m->layers[l].tc_w2 || !m->layers[l].tc_wf ||
+        !m->layers[l].tc_wqkv)
+      return false;
+  DenseArgs probe;
+  memset(&probe, 0, sizeof(probe));
+  probe.D = m->d_model;
+  probe.Dff = m->d_ff;
+  probe.n_comp = m->n_comp;
+  probe.kv.dtype = st->dtype;
+  probe.do_head = 1;
+  probe.tc_wa = m->tc_wa;
+  probe.tc_wb = m->tc_wb;
+  return dense_tc_applicable(probe);
+}
+
 int run_ctx(const artab_model* m, const artab_state* st, int layer, int rows, int rows_per_group, int n_splits,
             float* out, float* lse, cudaStream_t s) {
   const Layout lo = layout_of(m, st);
@@ -160,6 +179,7 @@ int run_ctx(const artab_model* m, const artab_state* st, int layer, int rows, in
   c.n_splits = n_splits;
   c.scale = 1.0f / sqrtf((float)m->head_dim);
   c.out = out;
+  c.out_lane_major = out == st->attn && chain_on_tc(m, st);
   c.lse = lse;
   c.status = st->status;
   return use_tc(st->dtype, m->head_dim) ? launch_ctx_attn_tc(c, s) : launch_ctx_attn_simt(c, s);
@@ -197,6 +217,7 @@ DenseArgs dense_base(const artab_model* m, const artab_state* st, int rows) {
   d.kv.n_heads = m->n_heads;
   d.kv.head_dim = m->head_dim;
   d.status = st->status;
+  d.lane_major = chain_on_tc(m, st);
   fill_head(m, d);
   return d;
 }
@@ -279,6 +300,7 @@ BufMergeArgs buf_base(const artab_model* m, const artab_state* st, int rows) {
   b.rows = rows;
   b.scale = 1.0f / sqrtf((float)m->head_dim);
   b.out = st->attn;
+  b.out_lane_major = chain_on_tc(m, st);
   return b;
 }
 

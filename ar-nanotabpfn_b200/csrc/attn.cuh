@@ -13,6 +13,7 @@ struct CtxAttnArgs {
   int rows, rows_per_group, n_groups, n_heads, head_dim, n_ctx, n_ctx_pad, n_splits;
   float scale;
   float* out;         // [splits][rows][H][Dh]
+  int out_lane_major; // n_splits == 1 only: write the [rows][H*Dh] result in the lane-major layout
   float* lse;         // [splits][rows][H]
   int32_t* status;    // device status word (bounded waits), may be null for SIMT
 };
@@ -29,6 +30,7 @@ struct BufMergeArgs {
   int n_splits, rows;
   float scale;
   float* out;  // [rows][H][Dh]
+  int out_lane_major;  // write out in the lane-major layout instead
 };
 
 int launch_ctx_attn_simt(const CtxAttnArgs& a, cudaStream_t s);

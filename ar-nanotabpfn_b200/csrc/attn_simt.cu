@@ -137,7 +137,12 @@ __global__ void __launch_bounds__(kWarps * 32) ctx_attn_simt_kernel(const CtxAtt
     const float inv = l[qq] > 0.f ? 1.0f / l[qq] : 0.f;
     if (DH >= 32 || lane < DH) {
 #pragma unroll
-      for (int e = 0; e < NDL; ++e) a.out[ro * DH + lane + 32 * e] = acc[qq][e] * inv;
+      for (int e = 0; e < NDL; ++e) {
+        const size_t idx = a.out_lane_major
+                               ? lane_major_index(group_row0 + r, h * DH + lane + 32 * e, a.n_heads * DH)
+                               : ro * DH + lane + 32 * e;
+        a.out[idx] = acc[qq][e] * inv;
+      }
     }
     if (lane == 0) a.lse[ro] = l[qq] > 0.f ? (m[qq] + log2f(l[qq])) * kLn2 : -INFINITY;
   }
@@ -297,10 +302,12 @@ __global__ void __launch_bounds__(128) buf_merge_kernel(const BufMergeArgs a) {
     }
     if (grp == 0) {
       const float inv = wsum > 0.f ? 1.0f / wsum : 0.f;
-      float* dst = a.out + ((size_t)r * a.n_heads + h) * DH + sub * VEC;
 #pragma unroll
-      for (int e = 0; e < VEC; e += 4)
-        *reinterpret_cast<float4*>(dst + e) = make_float4(o[e] * inv, o[e + 1] * inv, o[e + 2] * inv, o[e + 3] * inv);
+      for (int e = 0; e < VEC; e += 4) {
+        float* dst = a.out + (a.out_lane_major ? lane_major_index(r, h * DH + sub * VEC + e, a.n_heads * DH)
+                                               : ((size_t)r * a.n_heads + h) * DH + sub * VEC + e);
+        *reinterpret_cast<float4*>(dst) = make_float4(o[e] * inv, o[e + 1] * inv, o[e + 2] * inv, o[e + 3] * inv);
+      }
     }
   }
 }

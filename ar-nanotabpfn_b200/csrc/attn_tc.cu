@@ -165,6 +165,7 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 struct TcParams {
   int rows, rows_per_group, n_groups, n_heads, n_ctx, n_ctx_pad, n_splits;
   float scale_log2e;
+  int out_lane_major;
   float* out;
   float* lse;
   int32_t* status;
@@ -395,10 +396,12 @@ ctx_attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         }
         if (row_valid) {
           const float inv = 1.0f / l;
-          float4* dst = reinterpret_cast<float4*>(p.out + out_row * DH);
 #pragma unroll
-          for (int d = 0; d < DH; d += 4)
-            dst[d >> 2] = make_float4(o[d] * inv, o[d + 1] * inv, o[d + 2] * inv, o[d + 3] * inv);
+          for (int d = 0; d < DH; d += 4) {
+            float* dst = p.out + (p.out_lane_major ? lane_major_index(group_row0 + m0 + row, h * DH + d, p.n_heads * DH)
+                                                   : out_row * DH + d);
+            *reinterpret_cast<float4*>(dst) = make_float4(o[d] * inv, o[d + 1] * inv, o[d + 2] * inv, o[d + 3] * inv);
+          }
           p.lse[out_row] = (m + log2f(l)) * kLn2;
         }
       }
@@ -491,6 +494,7 @@ int launch_ctx_attn_tc(const CtxAttnArgs& a, cudaStream_t s) {
   p.n_ctx_pad = a.n_ctx_pad;
   p.n_splits = a.n_splits;
   p.scale_log2e = a.scale * kLog2e;
+  p.out_lane_major = a.out_lane_major && a.n_splits == 1;
   p.out = a.out;
   p.lse = a.lse;
   p.status = a.status;

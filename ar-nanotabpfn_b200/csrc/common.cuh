@@ -84,6 +84,13 @@ __device__ __forceinline__ float warp_max(float v) {
   return v;
 }
 
+// "Lane-major" layout of a [rows][D] fp32 workspace: 32-row tiles, inside a tile the float4 column
+// groups are outermost and the 32 rows innermost, so that 32 threads owning 32 consecutive rows
+// (tensor-memory lanes) read or write one contiguous 512-byte span per float4.
+__host__ __device__ __forceinline__ size_t lane_major_index(long row, int col, int D) {
+  return ((size_t)(row >> 5) * (D >> 2) + (col >> 2)) * 128 + (size_t)(row & 31) * 4 + (col & 3);
+}
+
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 

@@ -25,6 +25,7 @@ struct DenseArgs {
   int rows, D, Dff, n_comp;
   int do_post, do_final, do_head, do_pre;
   artab_layer_weights post_w, pre_w;
+  int lane_major;      // tensor-core chain: attn and the x1 workspace use the lane-major layout
   const float* attn;   // [rows][D]  post input
   const float* x1_in;  // [rows][D]  post residual input
   const float* x_in;   // [rows][D]  chain input when !do_post

@@ -14,8 +14,8 @@
 //     shared-memory image, streamed by a producer warp with plain bulk copies
 //     through a 6-slot ring (full / empty mbarriers).
 // Warp 0: weight producer.  Warp 1: MMA issuer, owns the 512 TMEM columns.
-// Warps 2-9: 256 epilogue threads, two per row (each owns half of the columns);
-// LayerNorm statistics are exchanged through shared memory.
+// Warps 2-17: 512 epilogue threads, four per row (each owns a quarter of the
+// columns); LayerNorm statistics are exchanged through shared memory.
 // All mbarrier waits are bounded; on expiry the CTA flags an abort, stops
 // producing results, drains and frees TMEM.
 #include "dense.cuh"
@@ -26,14 +26,16 @@ namespace artab {
 namespace {
 
 constexpr int BM = 128;          // token rows per CTA
-constexpr int HT = 64;           // hidden units per MLP tile
+constexpr int HT = 128;          // hidden units per MLP tile
 constexpr int NSLOT = 6;         // weight ring depth
-constexpr int kThreads = 320;
+constexpr int NWG = 4;           // epilogue threads per row (column groups)
+constexpr int kEpi = 128 * NWG;  // epilogue threads
+constexpr int kThreads = 64 + kEpi;
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kAccA = 0;    // wide accumulator (<= 192 columns)
 constexpr uint32_t kAxHi = 192;  // activation operand, hi part (<= 96 packed columns)
 constexpr uint32_t kAxLo = 288;  // activation operand, lo part
-constexpr uint32_t kAccH = 384;  // two hidden-tile accumulators of 64 columns
+constexpr uint32_t kAccH = 384;  // hidden-tile accumulator, 128 columns
 constexpr long long kWaitCycles = 2000000000LL;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -99,18 +101,6 @@ __device__ __forceinline__ void umma_commit(uint64_t* bar) {
 }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,"
-      "%29,%30,%31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr)
-      : "memory");
-}
 __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* r) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
@@ -120,13 +110,10 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* r) {
       : "r"(taddr)
       : "memory");
 }
-__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t* r) {
-  asm volatile(
-      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
-      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
-      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
-        "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
-      : "memory");
+__device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t* r) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"r"(taddr), "r"(r[0]),
+               "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+               : "memory");
 }
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
@@ -167,10 +154,12 @@ __device__ long long g_dbg[64];
 
 struct __align__(1024) Smem {
   uint8_t ring[NSLOT][192 * 128];     // weight slabs (d_model * 128 bytes each)
-  uint8_t ah[2][2][BM * 128];         // hidden tile operand [buffer][hi, lo][128 rows x 64 bf16], swizzled
-  float xs[2][2][BM];                 // LayerNorm partial sums exchanged between the two column halves
+  uint8_t ah[2][2][BM * 128];         // hidden tile operand [hi, lo][k-chunk][128 rows x 64 bf16], swizzled
+  float xs[2][NWG][BM];               // LayerNorm partial sums exchanged between the column groups
+  float bias_h[1024];                 // hidden bias of the current MLP (b1 / head.0 bias), d_ff <= 1024
+  float vec[8][192];                  // ln2 g,b | b2 | ln3 g,b | (ln1 | final) g,b | spare
   uint64_t w_full[NSLOT], w_empty[NSLOT];
-  uint64_t ep_done, acc_full, h_full[2], ah_ready[2], ah_free[2];
+  uint64_t ep_done, acc_full, h_full, acch_free, ah_ready, ah_free;
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -207,11 +196,13 @@ struct Producer {
     const int n = groups * (has_lo ? 2 : 1);
     for (int i = 0; i < n; ++i) slab(p + (size_t)i * slab_bytes, slab_bytes);
   }
-  // two-GEMM MLP: hidden tiles of w1 interleaved with the k-chunks of w2, one tile of look-ahead
-  __device__ void mlp(const void* w1, bool lo1, uint32_t bytes1, const void* w2, bool lo2, uint32_t bytes2, int nt) {
+  // two-GEMM MLP: per 128-wide hidden tile the first matrix contributes nkc slabs of 16 KB per part
+  // and the second matrix two k-chunk slabs per part; tiles of the second trail by one
+  __device__ void mlp(const void* w1, bool lo1, int nkc, const void* w2, bool lo2, uint32_t bytes2, int nt) {
     const uint8_t* p1 = reinterpret_cast<const uint8_t*>(w1);
     const uint8_t* p2 = reinterpret_cast<const uint8_t*>(w2);
-    const int s1 = lo1 ? 2 : 1, s2 = lo2 ? 2 : 1;
+    const int s1 = nkc * (lo1 ? 2 : 1), s2 = 2 * (lo2 ? 2 : 1);
+    const uint32_t bytes1 = HT * 128;
     for (int j = 0; j < nt; ++j) {
       for (int i = 0; i < s1; ++i) slab(p1 + (size_t)(j * s1 + i) * bytes1, bytes1);
       if (j >= 1)
@@ -227,7 +218,8 @@ struct Issuer {
   uint32_t tmem;
   int consumed;     // ring slabs consumed
   int ep_phase;     // completed waits on ep_done
-  int ah_count[2];  // completed waits on ah_ready[b]
+  int ah_count;     // completed waits on ah_ready
+  int hfree_count;  // completed waits on acch_free
   bool ok;
 
   __device__ uint32_t slab_wait() {
@@ -266,106 +258,118 @@ struct Issuer {
       }
     }
   }
-  // ACC[acc_col] (64 columns) = A_x . W_tile^T, the slab holds the tile's nkc blocks of [64 rows][64 k]
-  __device__ void gemm_tile_ts(uint32_t acc_col, int nkc, bool has_lo) {
+  // ACC_H (128 columns) = A_x . W_tile^T; the tile arrives as nkc slabs of [128 rows][64 k] per part,
+  // ordered hi part (all k-chunks) then lo part
+  __device__ void gemm_tile_ts(int nkc, bool has_lo) {
     const uint32_t idesc = make_idesc(HT);
-    const uint32_t hi = slab_wait();
-    for (int kc = 0; kc < nkc; ++kc)
+    for (int kc = 0; kc < nkc; ++kc) {
+      const uint32_t hi = slab_wait();
 #pragma unroll
       for (int ks = 0; ks < 4; ++ks)
-        umma_ts(tmem + acc_col, tmem + kAxHi + kc * 32 + ks * 8, make_desc(hi + kc * (HT * 128) + 32 * ks), idesc,
-                (kc | ks) != 0);
-    for (int kc = 0; kc < nkc; ++kc)
+        umma_ts(tmem + kAccH, tmem + kAxHi + kc * 32 + ks * 8, make_desc(hi + 32 * ks), idesc, (kc | ks) != 0);
 #pragma unroll
       for (int ks = 0; ks < 4; ++ks)
-        umma_ts(tmem + acc_col, tmem + kAxLo + kc * 32 + ks * 8, make_desc(hi + kc * (HT * 128) + 32 * ks), idesc, 1);
-    slab_release();
+        umma_ts(tmem + kAccH, tmem + kAxLo + kc * 32 + ks * 8, make_desc(hi + 32 * ks), idesc, 1);
+      slab_release();
+    }
     if (has_lo) {
-      const uint32_t lo = slab_wait();
-      for (int kc = 0; kc < nkc; ++kc)
+      for (int kc = 0; kc < nkc; ++kc) {
+        const uint32_t lo = slab_wait();
 #pragma unroll
         for (int ks = 0; ks < 4; ++ks)
-          umma_ts(tmem + acc_col, tmem + kAxHi + kc * 32 + ks * 8, make_desc(lo + kc * (HT * 128) + 32 * ks), idesc, 1);
-      slab_release();
+          umma_ts(tmem + kAccH, tmem + kAxHi + kc * 32 + ks * 8, make_desc(lo + 32 * ks), idesc, 1);
+        slab_release();
+      }
     }
   }
-  // ACC[acc_col] (+)= A_h[b] . W_chunk^T  (K = 64, A from shared memory)
-  __device__ void gemm_chunk_ss(uint32_t acc_col, int n_out, int b, bool has_lo, bool accumulate) {
+  // ACC_A (+)= A_h . W_chunks^T for the two 64-wide k-chunks of one hidden tile (A from shared memory)
+  __device__ void gemm_chunks_ss(int n_out, bool has_lo, bool accumulate) {
     const uint32_t idesc = make_idesc(n_out);
-    const uint32_t a_hi = smem_u32(sm->ah[b][0]), a_lo = smem_u32(sm->ah[b][1]);
-    const uint32_t hi = slab_wait();
+    for (int kc = 0; kc < 2; ++kc) {
+      const uint32_t a_hi = smem_u32(sm->ah[0][kc]), a_lo = smem_u32(sm->ah[1][kc]);
+      const uint32_t hi = slab_wait();
 #pragma unroll
-    for (int ks = 0; ks < 4; ++ks)
-      umma_ss(tmem + acc_col, make_desc(a_hi + 32 * ks), make_desc(hi + 32 * ks), idesc, accumulate || ks != 0);
+      for (int ks = 0; ks < 4; ++ks)
+        umma_ss(tmem + kAccA, make_desc(a_hi + 32 * ks), make_desc(hi + 32 * ks), idesc, accumulate || (kc | ks) != 0);
 #pragma unroll
-    for (int ks = 0; ks < 4; ++ks) umma_ss(tmem + acc_col, make_desc(a_lo + 32 * ks), make_desc(hi + 32 * ks), idesc, 1);
-    slab_release();
-    if (has_lo) {
-      const uint32_t lo = slab_wait();
-#pragma unroll
-      for (int ks = 0; ks < 4; ++ks) umma_ss(tmem + acc_col, make_desc(a_hi + 32 * ks), make_desc(lo + 32 * ks), idesc, 1);
+      for (int ks = 0; ks < 4; ++ks) umma_ss(tmem + kAccA, make_desc(a_lo + 32 * ks), make_desc(hi + 32 * ks), idesc, 1);
       slab_release();
+      if (has_lo) {
+        const uint32_t lo = slab_wait();
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks) umma_ss(tmem + kAccA, make_desc(a_hi + 32 * ks), make_desc(lo + 32 * ks), idesc, 1);
+        slab_release();
+      }
     }
   }
-  // hidden = act(A_x . W1^T) tile by tile, ACC_A = hidden . W2^T; one tile of look-ahead
+  // hidden = act(A_x . W1^T) tile by tile into ACC_H, ACC_A = hidden . W2^T.  The epilogue frees
+  // ACC_H as soon as it has pulled a tile into registers, so tile j+1 is computed while tile j is
+  // still being activated; the second GEMM of tile j follows the first GEMM of tile j+1.
   __device__ void mlp(int nkc, bool lo1, bool lo2, int nt, int n_out) {
     for (int j = 0; j < nt; ++j) {
-      gemm_tile_ts(kAccH + 64 * (j & 1), nkc, lo1);
-      umma_commit(&sm->h_full[j & 1]);
+      if (j >= 1) wait_hidden_free();
+      gemm_tile_ts(nkc, lo1);
+      umma_commit(&sm->h_full);
       if (j >= 1) second(j - 1, lo2, n_out);
     }
+    wait_hidden_free();  // keeps the phase count exact for a second MLP in the same launch
     second(nt - 1, lo2, n_out);
     umma_commit(&sm->acc_full);
   }
-  __device__ void second(int j, bool lo2, int n_out) {
-    const int b = j & 1;
-    ok = ok && mbar_wait(&sm->ah_ready[b], ah_count[b] & 1, &sm->abort_flag);
-    ++ah_count[b];
+  __device__ void wait_hidden_free() {
+    ok = ok && mbar_wait(&sm->acch_free, hfree_count & 1, &sm->abort_flag);
+    ++hfree_count;
     tc_fence_after();
-    gemm_chunk_ss(kAccA, n_out, b, lo2, j > 0);
-    umma_commit(&sm->ah_free[b]);
+  }
+  __device__ void second(int j, bool lo2, int n_out) {
+    ok = ok && mbar_wait(&sm->ah_ready, ah_count & 1, &sm->abort_flag);
+    ++ah_count;
+    tc_fence_after();
+    gemm_chunks_ss(n_out, lo2, j > 0);
+    umma_commit(&sm->ah_free);
   }
 };
 
 // ------------------------------------------------------------------ epilogue
 template <int D>
 struct Epilogue {
-  static constexpr int HALF = D / 2;       // columns owned by one thread
-  static constexpr int NCH = HALF / 32;    // 32-column chunks
+  static constexpr int PART = D / NWG;     // columns owned by one thread
+  static constexpr int NCH = PART / 16;    // 16-column chunks
+  static constexpr int HPART = HT / NWG;   // hidden-tile columns owned by one thread (16)
   Smem* sm;
   uint32_t t_row;                          // TMEM address of this thread's lane
   int row, wg, col0;
   int acc_phase, xs_phase;
-  int h_count[2], free_count[2];
+  int h_count, free_count;
   bool ok;
 
-  __device__ void sync_halves() { asm volatile("bar.sync 3, 256;" ::: "memory"); }
+  __device__ void sync_groups() { asm volatile("bar.sync 3, %0;" ::"n"(kEpi) : "memory"); }
 
   __device__ void wait_acc() {
     ok = mbar_wait(&sm->acc_full, acc_phase & 1, &sm->abort_flag) && ok;
     ++acc_phase;
     tc_fence_after();
   }
-  // v[i] += ACC_A[col0 + i]
+  // v[i] += ACC_A[col0 + i]   (16 columns at a time: keeps the live register set small)
   __device__ void add_acc(float* v) {
-    uint32_t r[32];
+    uint32_t r[16];
 #pragma unroll
     for (int c = 0; c < NCH; ++c) {
-      tmem_ld32(t_row + kAccA + col0 + 32 * c, r);
+      tmem_ld16(t_row + kAccA + col0 + 16 * c, r);
       tmem_wait_ld();
 #pragma unroll
-      for (int i = 0; i < 32; ++i) v[32 * c + i] += __uint_as_float(r[i]);
+      for (int i = 0; i < 16; ++i) v[16 * c + i] += __uint_as_float(r[i]);
     }
   }
   // A_x <- split(v) for this thread's columns, then tell the MMA warp
   __device__ void publish_ax(const float* v) {
 #pragma unroll
     for (int c = 0; c < NCH; ++c) {
-      uint32_t hi[16], lo[16];
+      uint32_t hi[8], lo[8];
 #pragma unroll
-      for (int i = 0; i < 16; ++i) split2(v[32 * c + 2 * i], v[32 * c + 2 * i + 1], hi[i], lo[i]);
-      tmem_st16(t_row + kAxHi + (col0 >> 1) + 16 * c, hi);
-      tmem_st16(t_row + kAxLo + (col0 >> 1) + 16 * c, lo);
+      for (int i = 0; i < 8; ++i) split2(v[16 * c + 2 * i], v[16 * c + 2 * i + 1], hi[i], lo[i]);
+      tmem_st8(t_row + kAxHi + (col0 >> 1) + 8 * c, hi);
+      tmem_st8(t_row + kAxLo + (col0 >> 1) + 8 * c, lo);
     }
     done();
   }
@@ -374,72 +378,79 @@ struct Epilogue {
     tc_fence_before();
     mbar_arrive(&sm->ep_done);
   }
-  // LayerNorm over the full row (two threads, one per column half)
-  __device__ void layer_norm(float* v, const float* __restrict__ gamma, const float* __restrict__ beta) {
-    float s = 0.f;
-#pragma unroll
-    for (int i = 0; i < HALF; ++i) s += v[i];
+  // sum of one value per column group of this row, added in a fixed order (deterministic)
+  __device__ float row_total(float part) {
     const int ph = xs_phase & 1;
     ++xs_phase;
-    sm->xs[ph][wg][row] = s;
-    sync_halves();
-    const float mean = (wg == 0 ? s + sm->xs[ph][1][row] : sm->xs[ph][0][row] + s) / (float)D;
+    sm->xs[ph][wg][row] = part;
+    sync_groups();
+    float tot = 0.f;
+#pragma unroll
+    for (int g = 0; g < NWG; ++g) tot += sm->xs[ph][g][row];
+    return tot;
+  }
+  // LayerNorm over the full row (NWG threads, one per column group)
+  __device__ void layer_norm(float* v, const float* gamma, const float* beta) {
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < PART; ++i) s += v[i];
+    const float mean = row_total(s) / (float)D;
     float ss = 0.f;
 #pragma unroll
-    for (int i = 0; i < HALF; ++i) {
+    for (int i = 0; i < PART; ++i) {
       const float d = v[i] - mean;
       ss = fmaf(d, d, ss);
     }
-    const int ph2 = xs_phase & 1;
-    ++xs_phase;
-    sm->xs[ph2][wg][row] = ss;
-    sync_halves();
-    const float var = (wg == 0 ? ss + sm->xs[ph2][1][row] : sm->xs[ph2][0][row] + ss) / (float)D;
+    const float var = row_total(ss) / (float)D;
     const float rstd = 1.0f / sqrtf(var + 1e-5f);
 #pragma unroll
-    for (int i = 0; i < HALF; ++i)
-      v[i] = (v[i] - mean) * rstd * __ldg(gamma + col0 + i) + __ldg(beta + col0 + i);
+    for (int i = 0; i < PART; ++i) v[i] = (v[i] - mean) * rstd * gamma[col0 + i] + beta[col0 + i];
   }
   // hidden tile j: act(ACC_H + bias) -> split -> swizzled shared-memory operand
-  __device__ void hidden_tile(int j, const float* __restrict__ bias) {
-    const int b = j & 1;
-    ok = mbar_wait(&sm->h_full[b], h_count[b] & 1, &sm->abort_flag) && ok;
-    ++h_count[b];
+  __device__ void hidden_tile(int j, const float* bias) {
+    ok = mbar_wait(&sm->h_full, h_count & 1, &sm->abort_flag) && ok;
+    ++h_count;
     tc_fence_after();
-    uint32_t r[32];
-    tmem_ld32(t_row + kAccH + 64 * b + 32 * wg, r);
+    uint32_t r[2][16];
+#pragma unroll
+    for (int c = 0; c < 2; ++c) tmem_ld16(t_row + kAccH + HPART * wg + 16 * c, r[c]);
     tmem_wait_ld();
-    uint32_t hi[16], lo[16];
+    tc_fence_before();
+    mbar_arrive(&sm->acch_free);  // the accumulator is in registers: the next tile's GEMM may overwrite it
+    // this thread's 32 hidden columns sit in k-chunk wg / 2, 16-byte chunks 4 * (wg % 2) .. + 3 of the
+    // 128-byte row; chunk c of row r lives at chunk position c ^ (r % 8)
+    uint8_t* base_hi = sm->ah[0][wg >> 1] + row * 128;
+    uint8_t* base_lo = sm->ah[1][wg >> 1] + row * 128;
 #pragma unroll
-    for (int i = 0; i < 16; ++i) {
-      const float x0 = gelu_fast(__uint_as_float(r[2 * i]) + __ldg(bias + j * HT + 32 * wg + 2 * i));
-      const float x1 = gelu_fast(__uint_as_float(r[2 * i + 1]) + __ldg(bias + j * HT + 32 * wg + 2 * i + 1));
-      split2(x0, x1, hi[i], lo[i]);
-    }
-    if (j >= 2) {  // the MMA that read this buffer two tiles ago must be complete
-      ok = mbar_wait(&sm->ah_free[b], free_count[b] & 1, &sm->abort_flag) && ok;
-      ++free_count[b];
-    }
-    // row r, 16-byte chunk c of the 128-byte row lives at chunk position c ^ (r % 8)
-    uint8_t* base_hi = sm->ah[b][0] + row * 128;
-    uint8_t* base_lo = sm->ah[b][1] + row * 128;
+    for (int half = 0; half < 2; ++half) {
+      uint32_t hi[8], lo[8];
 #pragma unroll
-    for (int c = 0; c < 4; ++c) {
-      const int pos = ((4 * wg + c) ^ (row & 7)) * 16;
-      *reinterpret_cast<uint4*>(base_hi + pos) = make_uint4(hi[4 * c], hi[4 * c + 1], hi[4 * c + 2], hi[4 * c + 3]);
-      *reinterpret_cast<uint4*>(base_lo + pos) = make_uint4(lo[4 * c], lo[4 * c + 1], lo[4 * c + 2], lo[4 * c + 3]);
+      for (int i = 0; i < 8; ++i) {
+        const float2 bb = *reinterpret_cast<const float2*>(bias + j * HT + HPART * wg + 16 * half + 2 * i);
+        const float x0 = gelu_fast(__uint_as_float(r[half][2 * i]) + bb.x);
+        const float x1 = gelu_fast(__uint_as_float(r[half][2 * i + 1]) + bb.y);
+        split2(x0, x1, hi[i], lo[i]);
+      }
+      if (half == 0 && j >= 1) {  // the previous tile's second GEMM must have finished reading the buffer
+        ok = mbar_wait(&sm->ah_free, free_count & 1, &sm->abort_flag) && ok;
+        ++free_count;
+      }
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        const int pos = ((4 * (wg & 1) + 2 * half + c) ^ (row & 7)) * 16;
+        *reinterpret_cast<uint4*>(base_hi + pos) = make_uint4(hi[4 * c], hi[4 * c + 1], hi[4 * c + 2], hi[4 * c + 3]);
+        *reinterpret_cast<uint4*>(base_lo + pos) = make_uint4(lo[4 * c], lo[4 * c + 1], lo[4 * c + 2], lo[4 * c + 3]);
+      }
     }
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic writes -> visible to the MMA's reads
     tc_fence_before();
-    mbar_arrive(&sm->ah_ready[b]);
+    mbar_arrive(&sm->ah_ready);
   }
-  // After an MLP: consume the ah_free completions of its last tile(s), which no hidden_tile waited
-  // for, so that the parity bookkeeping is exact when a second MLP runs in the same launch.
-  __device__ void drain_free(int nt) {
-    for (int j = nt >= 2 ? nt - 2 : 0; j < nt; ++j) {
-      ok = mbar_wait(&sm->ah_free[j & 1], free_count[j & 1] & 1, &sm->abort_flag) && ok;
-      ++free_count[j & 1];
-    }
+  // After an MLP: consume the ah_free completion of its last tile, which no hidden_tile waited for,
+  // so that the parity bookkeeping is exact when a second MLP runs in the same launch.
+  __device__ void drain_free() {
+    ok = mbar_wait(&sm->ah_free, free_count & 1, &sm->abort_flag) && ok;
+    ++free_count;
   }
 };
 
@@ -508,13 +519,12 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const DenseArgs a
       mbar_init(&sm->w_full[i], 1);
       mbar_init(&sm->w_empty[i], 1);
     }
-    mbar_init(&sm->ep_done, 256);
+    mbar_init(&sm->ep_done, kEpi);
     mbar_init(&sm->acc_full, 1);
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(&sm->h_full[i], 1);
-      mbar_init(&sm->ah_ready[i], 256);
-      mbar_init(&sm->ah_free[i], 1);
-    }
+    mbar_init(&sm->h_full, 1);
+    mbar_init(&sm->acch_free, kEpi);
+    mbar_init(&sm->ah_ready, kEpi);
+    mbar_init(&sm->ah_free, 1);
     sm->abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -524,6 +534,25 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const DenseArgs a
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
+  // small per-column vectors -> shared memory (read by every epilogue thread, many times)
+  for (int i = threadIdx.x; i < D; i += kThreads) {
+    if (a.do_post) {
+      sm->vec[0][i] = a.post_w.ln2_g[i];
+      sm->vec[1][i] = a.post_w.ln2_b[i];
+      sm->vec[2][i] = a.post_w.b2[i];
+      sm->vec[3][i] = a.post_w.ln3_g[i];
+      sm->vec[4][i] = a.post_w.ln3_b[i];
+    }
+    if (a.do_final) {
+      sm->vec[5][i] = a.lnf_g[i];
+      sm->vec[6][i] = a.lnf_b[i];
+    } else if (a.do_pre) {
+      sm->vec[5][i] = a.pre_w.ln1_g[i];
+      sm->vec[6][i] = a.pre_w.ln1_b[i];
+    }
+  }
+  if (a.do_post)
+    for (int i = threadIdx.x; i < a.Dff; i += kThreads) sm->bias_h[i] = a.post_w.b1[i];
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -537,10 +566,10 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const DenseArgs a
       Producer p{sm, 0, true};
       if (a.do_post) {
         p.matrix(a.post_w.tc_wo, NKC, lo_post & 1, kSlab);
-        p.mlp(a.post_w.tc_w1, lo_post & 2, kSlab, a.post_w.tc_w2, lo_post & 4, kSlab, nt);
+        p.mlp(a.post_w.tc_w1, lo_post & 2, NKC, a.post_w.tc_w2, lo_post & 4, kSlab, nt);
       }
       if (a.do_head) {
-        p.mlp(a.tc_wa, a.tc_head_lo & 1, kSlab, a.tc_wb, a.tc_head_lo & 2, 16 * 128, nt);
+        p.mlp(a.tc_wa, a.tc_head_lo & 1, NKC, a.tc_wb, a.tc_head_lo & 2, 16 * 128, nt);
       } else if (a.do_pre) {
         p.matrix(a.pre_w.tc_wf, NKC, lo_pre & 8, kSlab);
         p.matrix(a.pre_w.tc_wqkv, 3 * NKC, lo_pre & 16, kSlab);
@@ -549,7 +578,7 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const DenseArgs a
   } else if (warp == 1) {
     // --------------------------------- MMA issuer ---------------------------------
     if (lane == 0) {
-      Issuer m{sm, tmem, 0, 0, {0, 0}, true};
+      Issuer m{sm, tmem, 0, 0, 0, 0, true};
       if (a.do_post) {
         m.wait_epilogue();                               // A_x = attention output
         m.gemm_full_ts(kAccA, D, NKC, lo_post & 1);
@@ -575,23 +604,39 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const DenseArgs a
   } else {
     // ---------------------------------- epilogue ----------------------------------
     Epilogue<D> e;
-    constexpr int HALF = Epilogue<D>::HALF;
+    constexpr int PART = Epilogue<D>::PART;
     e.sm = sm;
     e.row = 32 * (warp & 3) + lane;
-    e.wg = warp >= 6 ? 1 : 0;
-    e.col0 = e.wg * HALF;
+    e.wg = (warp - 2) >> 2;
+    e.col0 = e.wg * PART;
     e.t_row = tmem + ((uint32_t)(32 * (warp & 3)) << 16);
     e.acc_phase = e.xs_phase = 0;
-    e.h_count[0] = e.h_count[1] = e.free_count[0] = e.free_count[1] = 0;
+    e.h_count = e.free_count = 0;
     e.ok = true;
     const long grow = row0 + e.row;
     const bool valid = grow < a.rows;
     const size_t goff = (size_t)grow * D + e.col0;
-    float v[HALF];
+    float v[PART];
 
+    // lane-major workspaces (attn, x1): a warp's 32 rows form one contiguous 512-byte span per float4;
+    // the workspaces are padded to whole 128-row tiles, so no row guard is needed
+    const size_t lm0 = lane_major_index(grow, e.col0, D);
+    auto load_lm = [&](const float* src) {
+#pragma unroll
+      for (int i = 0; i < PART; i += 4) {
+        const float4 t = *reinterpret_cast<const float4*>(src + lm0 + (size_t)(i >> 2) * 128);
+        v[i] = t.x; v[i + 1] = t.y; v[i + 2] = t.z; v[i + 3] = t.w;
+      }
+    };
+    auto store_lm = [&](float* dst) {
+#pragma unroll
+      for (int i = 0; i < PART; i += 4)
+        *reinterpret_cast<float4*>(dst + lm0 + (size_t)(i >> 2) * 128) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+    };
+    // row-major workspace (x, z): each thread touches its own contiguous slice
     auto load_row = [&](const float* src) {
 #pragma unroll
-      for (int i = 0; i < HALF; i += 4) {
+      for (int i = 0; i < PART; i += 4) {
         const float4 t = valid ? *reinterpret_cast<const float4*>(src + goff + i) : make_float4(0.f, 0.f, 0.f, 0.f);
         v[i] = t.x; v[i + 1] = t.y; v[i + 2] = t.z; v[i + 3] = t.w;
       }
@@ -599,46 +644,53 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const DenseArgs a
     auto store_row = [&](float* dst) {
       if (!valid) return;
 #pragma unroll
-      for (int i = 0; i < HALF; i += 4)
+      for (int i = 0; i < PART; i += 4)
         *reinterpret_cast<float4*>(dst + goff + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
     };
 
-    TSTAMP(0);
     if (a.do_post) {
-      load_row(a.attn);
+      load_lm(a.attn);
       TSTAMP(1);
       e.publish_ax(v);
-      load_row(a.x1_in);                         // residual
+      load_lm(a.x1_in);                          // residual
       TSTAMP(2);
       e.wait_acc();
       TSTAMP(3);
       e.add_acc(v);
-      e.layer_norm(v, a.post_w.ln2_g, a.post_w.ln2_b);   // v = x2
+      e.layer_norm(v, sm->vec[0], sm->vec[1]);   // v = x2
       TSTAMP(4);
       e.publish_ax(v);
+      // x2 is the residual of the last LayerNorm; it waits in this thread's own slice of the x1
+      // workspace (free until the next layer writes it) so that the MLP epilogue has the registers
+      store_lm(a.x1_out);
       TSTAMP(5);
-      for (int j = 0; j < nt; ++j) { e.hidden_tile(j, a.post_w.b1); TSTAMP(6 + j); }
+      for (int j = 0; j < nt; ++j) { e.hidden_tile(j, sm->bias_h); TSTAMP(6 + j); }
+      load_lm(a.x1_out);
       e.wait_acc();
       TSTAMP(20);
-      e.drain_free(nt);
+      e.drain_free();
 #pragma unroll
-      for (int i = 0; i < HALF; ++i) v[i] += __ldg(a.post_w.b2 + e.col0 + i);
+      for (int i = 0; i < PART; ++i) v[i] += sm->vec[2][e.col0 + i];
       e.add_acc(v);
-      e.layer_norm(v, a.post_w.ln3_g, a.post_w.ln3_b);   // v = x3
+      e.layer_norm(v, sm->vec[3], sm->vec[4]);   // v = x3
       TSTAMP(21);
       if (a.x_out) store_row(a.x_out);
     } else {
       load_row(a.x_in);
     }
     if (a.do_final) {
-      e.layer_norm(v, a.lnf_g, a.lnf_b);                 // v = z
+      e.layer_norm(v, sm->vec[5], sm->vec[6]);                 // v = z
       if (a.z_out) store_row(a.z_out);
     }
     if (a.do_head) {
+      // the hidden bias buffer now takes the head's first-layer bias (every thread is past the MLP)
+      e.sync_groups();
+      for (int i = threadIdx.x - 64; i < a.Dff; i += kEpi) sm->bias_h[i] = a.ba[i];
+      e.sync_groups();
       e.publish_ax(v);
-      for (int j = 0; j < nt; ++j) e.hidden_tile(j, a.ba);
+      for (int j = 0; j < nt; ++j) e.hidden_tile(j, sm->bias_h);
       e.wait_acc();
-      e.drain_free(nt);
+      e.drain_free();
       if (e.wg == 0) {
         uint32_t r[16];
         tmem_ld16(e.t_row + kAccA, r);
@@ -654,8 +706,8 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const DenseArgs a
       e.wait_acc();
       TSTAMP(23);
       e.add_acc(v);
-      e.layer_norm(v, a.pre_w.ln1_g, a.pre_w.ln1_b);     // v = x1
-      store_row(a.x1_out);
+      e.layer_norm(v, sm->vec[5], sm->vec[6]);     // v = x1
+      store_lm(a.x1_out);
       e.publish_ax(v);
       TSTAMP(24);
       // q, k, v projections, one accumulator round each.  Destinations of this row's K / V are
@@ -684,26 +736,26 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const DenseArgs a
       }
       for (int t = 0; t < 3; ++t) {
         e.wait_acc();
-        uint32_t r[32];
+        uint32_t r[16];
 #pragma unroll
         for (int c = 0; c < Epilogue<D>::NCH; ++c) {
-          tmem_ld32(e.t_row + kAccA + e.col0 + 32 * c, r);
+          tmem_ld16(e.t_row + kAccA + e.col0 + 16 * c, r);
           tmem_wait_ld();
-          const int cbase = e.col0 + 32 * c;
+          const int cbase = e.col0 + 16 * c;
           if (t == 0 || (t == 1 && k_dst) || (t == 2 && v_dst)) {
-            uint32_t pk[16];
+            uint32_t pk[8];
 #pragma unroll
-            for (int i = 0; i < 16; ++i) pk[i] = pack_bf16(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
+            for (int i = 0; i < 8; ++i) pk[i] = pack_bf16(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
             if (t == 0) {
               if (valid) {
-                uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(a.q_out) + goff + 32 * c);
-#pragma unroll
-                for (int i = 0; i < 4; ++i) dst[i] = make_uint4(pk[4 * i], pk[4 * i + 1], pk[4 * i + 2], pk[4 * i + 3]);
+                uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(a.q_out) + goff + 16 * c);
+                dst[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                dst[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
               }
             } else {
               __nv_bfloat16* base = t == 1 ? k_dst : v_dst;
 #pragma unroll
-              for (int i = 0; i < 4; ++i) {  // 8 columns = 16 bytes, never straddles a head (Dh % 8 == 0)
+              for (int i = 0; i < 2; ++i) {  // 8 columns = 16 bytes, never straddles a head (Dh % 8 == 0)
                 const int col = cbase + 8 * i;
                 const int h = col >> dh_shift, d = col & (Dh - 1);
                 *reinterpret_cast<uint4*>(base + (size_t)h * k_hstride + d) =
@@ -712,7 +764,7 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const DenseArgs a
             }
           } else if (t == 2 && vt_dst) {
 #pragma unroll
-            for (int i = 0; i < 32; ++i) {
+            for (int i = 0; i < 16; ++i) {
               const int col = cbase + i;
               const int h = col >> dh_shift, d = col & (Dh - 1);
               const float val = __uint_as_float(r[i]);
@@ -751,7 +803,7 @@ extern "C" ARTAB_API int artab_debug_read(long long* out) {
 
 bool dense_tc_applicable(const DenseArgs& a) {
   if (a.kv.dtype != ARTAB_BF16) return false;
-  if (!(a.D == 64 || a.D == 128 || a.D == 192) || a.Dff % HT != 0 || 3 * a.n_comp > 16 || a.n_comp > 8) return false;
+  if (!(a.D == 64 || a.D == 128 || a.D == 192) || a.Dff % HT != 0 || a.Dff > 1024 || 3 * a.n_comp > 16 || a.n_comp > 8) return false;
   if (a.do_post && !(a.post_w.tc_wo && a.post_w.tc_w1 && a.post_w.tc_w2)) return false;
   if (a.do_pre && !(a.pre_w.tc_wf && a.pre_w.tc_wqkv)) return false;
   if (a.do_head && !(a.tc_wa && a.tc_wb)) return false;

@@ -75,7 +75,8 @@ typedef struct artab_layer_weights {
    * [rows][64 k] blocks in the 128-byte-swizzled K-major shared-memory image, a bf16 "hi"
    * slab followed by a "lo" slab (w = hi + lo) when the matching tc_lo bit is set.
    *   tc_wo, tc_wf, tc_wqkv (q, k, v one after the other): one slab per 64-wide k-chunk, all rows;
-   *   tc_w1: one slab per 64-row output tile (all its k-chunks); tc_w2: one slab per k-chunk. */
+   *   tc_w1: per 128-row output tile one 16 KB slab per k-chunk (hi part first, then lo);
+ *   tc_w2: one slab per 64-wide k-chunk, all rows. */
   const void* tc_wo;
   const void* tc_w1;
   const void* tc_w2;
