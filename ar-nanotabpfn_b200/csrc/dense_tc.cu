@@ -78,6 +78,10 @@ __device__ __forceinline__ uint64_t make_desc(uint32_t saddr) {  // K-major, 128
   d |= kLayoutSw128 << 61;
   return d;
 }
+// The issuing thread shares its scheduler with four busy epilogue warps, so every instruction it
+// spends between two MMAs costs about five cycles: descriptors are built once per slab and
+// stepped with a single add (the start-address field counts 16-byte units).
+__device__ __forceinline__ uint64_t desc_step(uint64_t d, int bytes) { return d + (uint64_t)(bytes >> 4); }
 __device__ __forceinline__ uint32_t make_idesc(int N) {  // M 128, fp32 accumulate, bf16 x bf16, K-major both
   return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
 }
@@ -148,8 +152,10 @@ __device__ __forceinline__ float gelu_fast(float x) {
 #ifdef DENSE_TC_TIMING
 __device__ long long g_dbg[64];
 #define TSTAMP(i) do { if (blockIdx.x == 0 && threadIdx.x == 64) g_dbg[i] = clock64(); } while (0)
+#define MSTAMP(i) do { if (blockIdx.x == 0) g_dbg[i] = clock64(); } while (0)
 #else
 #define TSTAMP(i)
+#define MSTAMP(i)
 #endif
 
 struct __align__(1024) Smem {
@@ -183,6 +189,7 @@ struct Producer {
       return;
     }
     uint64_t* bar = &sm->w_full[buf];
+    if (issued == 20) MSTAMP(54);
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
                  : "memory");
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
@@ -224,7 +231,10 @@ struct Issuer {
 
   __device__ uint32_t slab_wait() {
     const int buf = consumed % NSLOT;
+    if (consumed == 20) MSTAMP(55);
+    if (consumed == 14) MSTAMP(57);
     ok = ok && mbar_wait(&sm->w_full[buf], (consumed / NSLOT) & 1, &sm->abort_flag);
+    if (consumed == 20) MSTAMP(56);
     tc_fence_after();
     return smem_u32(sm->ring[buf]);
   }
@@ -240,20 +250,19 @@ struct Issuer {
   // ACC[acc_col] = A_x . W^T with W streamed as `nkc` slabs of [n_out rows][64 k]
   __device__ void gemm_full_ts(uint32_t acc_col, int n_out, int nkc, bool has_lo) {
     const uint32_t idesc = make_idesc(n_out);
-    for (int kc = 0; kc < nkc; ++kc) {
-      const uint32_t hi = slab_wait();
+    const uint32_t acc = tmem + acc_col;
+    uint32_t ahi = tmem + kAxHi, alo = tmem + kAxLo;
+    for (int kc = 0; kc < nkc; ++kc, ahi += 32, alo += 32) {
+      const uint64_t bd = make_desc(slab_wait());
 #pragma unroll
-      for (int ks = 0; ks < 4; ++ks)
-        umma_ts(tmem + acc_col, tmem + kAxHi + kc * 32 + ks * 8, make_desc(hi + 32 * ks), idesc, (kc | ks) != 0);
+      for (int ks = 0; ks < 4; ++ks) umma_ts(acc, ahi + ks * 8, desc_step(bd, 32 * ks), idesc, (kc | ks) != 0);
 #pragma unroll
-      for (int ks = 0; ks < 4; ++ks)
-        umma_ts(tmem + acc_col, tmem + kAxLo + kc * 32 + ks * 8, make_desc(hi + 32 * ks), idesc, 1);
+      for (int ks = 0; ks < 4; ++ks) umma_ts(acc, alo + ks * 8, desc_step(bd, 32 * ks), idesc, 1);
       slab_release();
       if (has_lo) {
-        const uint32_t lo = slab_wait();
+        const uint64_t ld = make_desc(slab_wait());
 #pragma unroll
-        for (int ks = 0; ks < 4; ++ks)
-          umma_ts(tmem + acc_col, tmem + kAxHi + kc * 32 + ks * 8, make_desc(lo + 32 * ks), idesc, 1);
+        for (int ks = 0; ks < 4; ++ks) umma_ts(acc, ahi + ks * 8, desc_step(ld, 32 * ks), idesc, 1);
         slab_release();
       }
     }
@@ -262,22 +271,22 @@ struct Issuer {
   // ordered hi part (all k-chunks) then lo part
   __device__ void gemm_tile_ts(int nkc, bool has_lo) {
     const uint32_t idesc = make_idesc(HT);
-    for (int kc = 0; kc < nkc; ++kc) {
-      const uint32_t hi = slab_wait();
+    const uint32_t acc = tmem + kAccH;
+    uint32_t ahi = tmem + kAxHi, alo = tmem + kAxLo;
+    for (int kc = 0; kc < nkc; ++kc, ahi += 32, alo += 32) {
+      const uint64_t bd = make_desc(slab_wait());
 #pragma unroll
-      for (int ks = 0; ks < 4; ++ks)
-        umma_ts(tmem + kAccH, tmem + kAxHi + kc * 32 + ks * 8, make_desc(hi + 32 * ks), idesc, (kc | ks) != 0);
+      for (int ks = 0; ks < 4; ++ks) umma_ts(acc, ahi + ks * 8, desc_step(bd, 32 * ks), idesc, (kc | ks) != 0);
 #pragma unroll
-      for (int ks = 0; ks < 4; ++ks)
-        umma_ts(tmem + kAccH, tmem + kAxLo + kc * 32 + ks * 8, make_desc(hi + 32 * ks), idesc, 1);
+      for (int ks = 0; ks < 4; ++ks) umma_ts(acc, alo + ks * 8, desc_step(bd, 32 * ks), idesc, 1);
       slab_release();
     }
     if (has_lo) {
-      for (int kc = 0; kc < nkc; ++kc) {
-        const uint32_t lo = slab_wait();
+      ahi = tmem + kAxHi;
+      for (int kc = 0; kc < nkc; ++kc, ahi += 32) {
+        const uint64_t ld = make_desc(slab_wait());
 #pragma unroll
-        for (int ks = 0; ks < 4; ++ks)
-          umma_ts(tmem + kAccH, tmem + kAxHi + kc * 32 + ks * 8, make_desc(lo + 32 * ks), idesc, 1);
+        for (int ks = 0; ks < 4; ++ks) umma_ts(acc, ahi + ks * 8, desc_step(ld, 32 * ks), idesc, 1);
         slab_release();
       }
     }
@@ -285,19 +294,20 @@ struct Issuer {
   // ACC_A (+)= A_h . W_chunks^T for the two 64-wide k-chunks of one hidden tile (A from shared memory)
   __device__ void gemm_chunks_ss(int n_out, bool has_lo, bool accumulate) {
     const uint32_t idesc = make_idesc(n_out);
+    const uint32_t acc = tmem + kAccA;
     for (int kc = 0; kc < 2; ++kc) {
-      const uint32_t a_hi = smem_u32(sm->ah[0][kc]), a_lo = smem_u32(sm->ah[1][kc]);
-      const uint32_t hi = slab_wait();
+      const uint64_t a_hi = make_desc(smem_u32(sm->ah[0][kc])), a_lo = make_desc(smem_u32(sm->ah[1][kc]));
+      const uint64_t bd = make_desc(slab_wait());
 #pragma unroll
       for (int ks = 0; ks < 4; ++ks)
-        umma_ss(tmem + kAccA, make_desc(a_hi + 32 * ks), make_desc(hi + 32 * ks), idesc, accumulate || (kc | ks) != 0);
+        umma_ss(acc, desc_step(a_hi, 32 * ks), desc_step(bd, 32 * ks), idesc, accumulate || (kc | ks) != 0);
 #pragma unroll
-      for (int ks = 0; ks < 4; ++ks) umma_ss(tmem + kAccA, make_desc(a_lo + 32 * ks), make_desc(hi + 32 * ks), idesc, 1);
+      for (int ks = 0; ks < 4; ++ks) umma_ss(acc, desc_step(a_lo, 32 * ks), desc_step(bd, 32 * ks), idesc, 1);
       slab_release();
       if (has_lo) {
-        const uint32_t lo = slab_wait();
+        const uint64_t ld = make_desc(slab_wait());
 #pragma unroll
-        for (int ks = 0; ks < 4; ++ks) umma_ss(tmem + kAccA, make_desc(a_hi + 32 * ks), make_desc(lo + 32 * ks), idesc, 1);
+        for (int ks = 0; ks < 4; ++ks) umma_ss(acc, desc_step(a_hi, 32 * ks), desc_step(ld, 32 * ks), idesc, 1);
         slab_release();
       }
     }
@@ -307,10 +317,14 @@ struct Issuer {
   // still being activated; the second GEMM of tile j follows the first GEMM of tile j+1.
   __device__ void mlp(int nkc, bool lo1, bool lo2, int nt, int n_out) {
     for (int j = 0; j < nt; ++j) {
+      if (j == 3) MSTAMP(48);
       if (j >= 1) wait_hidden_free();
+      if (j == 3) MSTAMP(49);
       gemm_tile_ts(nkc, lo1);
+      if (j == 3) MSTAMP(50);
       umma_commit(&sm->h_full);
       if (j >= 1) second(j - 1, lo2, n_out);
+      if (j == 3) MSTAMP(53);
     }
     wait_hidden_free();  // keeps the phase count exact for a second MLP in the same launch
     second(nt - 1, lo2, n_out);
@@ -325,7 +339,9 @@ struct Issuer {
     ok = ok && mbar_wait(&sm->ah_ready, ah_count & 1, &sm->abort_flag);
     ++ah_count;
     tc_fence_after();
+    if (j == 2) MSTAMP(51);
     gemm_chunks_ss(n_out, lo2, j > 0);
+    if (j == 2) MSTAMP(52);
     umma_commit(&sm->ah_free);
   }
 };
@@ -734,50 +750,92 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const DenseArgs a
           v_dst = k_dst + Dh;
         }
       }
+      // Staging tile for coalesced stores: [128 rows][D bf16] with 16 bytes of padding per row
+      // (conflict-free 16-byte accesses), in the hidden-operand buffer, which is idle in this phase.
+      constexpr int kStageRow = D * 2 + 16;
+      uint8_t* stage = &sm->ah[0][0][0];
+      const bool direct = a.kv.mode == KV_PREFILL;   // context cache: direct stores are already coalesced
+      const int tid_e = threadIdx.x - 64;
       for (int t = 0; t < 3; ++t) {
         e.wait_acc();
-        uint32_t r[16];
+        uint32_t r[Epilogue<D>::NCH][16];
 #pragma unroll
-        for (int c = 0; c < Epilogue<D>::NCH; ++c) {
-          tmem_ld16(e.t_row + kAccA + e.col0 + 16 * c, r);
-          tmem_wait_ld();
-          const int cbase = e.col0 + 16 * c;
-          if (t == 0 || (t == 1 && k_dst) || (t == 2 && v_dst)) {
-            uint32_t pk[8];
-#pragma unroll
-            for (int i = 0; i < 8; ++i) pk[i] = pack_bf16(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
-            if (t == 0) {
-              if (valid) {
-                uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(a.q_out) + goff + 16 * c);
-                dst[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-                dst[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
-              }
-            } else {
-              __nv_bfloat16* base = t == 1 ? k_dst : v_dst;
-#pragma unroll
-              for (int i = 0; i < 2; ++i) {  // 8 columns = 16 bytes, never straddles a head (Dh % 8 == 0)
-                const int col = cbase + 8 * i;
-                const int h = col >> dh_shift, d = col & (Dh - 1);
-                *reinterpret_cast<uint4*>(base + (size_t)h * k_hstride + d) =
-                    make_uint4(pk[4 * i], pk[4 * i + 1], pk[4 * i + 2], pk[4 * i + 3]);
-              }
-            }
-          } else if (t == 2 && vt_dst) {
-#pragma unroll
-            for (int i = 0; i < 16; ++i) {
-              const int col = cbase + i;
-              const int h = col >> dh_shift, d = col & (Dh - 1);
-              const float val = __uint_as_float(r[i]);
-              const __nv_bfloat16 hi = __float2bfloat16_rn(val);
-              __nv_bfloat16* p = vt_dst + ((size_t)h * 2 * Dh + d) * a.kv.n_ctx_pad;
-              p[0] = hi;
-              p[(size_t)Dh * a.kv.n_ctx_pad] = __float2bfloat16_rn(val - __bfloat162float(hi));
-            }
-          }
-        }
-        if (t < 2) {  // accumulator drained: the next projection may overwrite it
+        for (int c = 0; c < Epilogue<D>::NCH; ++c) tmem_ld16(e.t_row + kAccA + e.col0 + 16 * c, r[c]);
+        tmem_wait_ld();
+        if (t < 2) {  // the accumulator is in registers: the next projection may overwrite it
           tc_fence_before();
           mbar_arrive(&sm->ep_done);
+        }
+        if (t == 0 || !direct) {
+          // bf16 -> staging tile
+#pragma unroll
+          for (int c = 0; c < Epilogue<D>::NCH; ++c) {
+            uint32_t pk[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+              pk[i] = pack_bf16(__uint_as_float(r[c][2 * i]), __uint_as_float(r[c][2 * i + 1]));
+            uint4* dst = reinterpret_cast<uint4*>(stage + (size_t)e.row * kStageRow + (e.col0 + 16 * c) * 2);
+            dst[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+            dst[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+          }
+          e.sync_groups();
+          constexpr int kChunksPerRow = D / 8;  // 16-byte chunks
+          if (t == 0) {
+            // q rows of this tile are one contiguous block of global memory
+            __nv_bfloat16* qdst = reinterpret_cast<__nv_bfloat16*>(a.q_out) + (size_t)row0 * D;
+            const int n_rows = (int)min((long)BM, (long)a.rows - row0);
+            for (int idx = tid_e; idx < n_rows * kChunksPerRow; idx += kEpi) {
+              const int rr = idx / kChunksPerRow, ch = idx - rr * kChunksPerRow;
+              *reinterpret_cast<uint4*>(qdst + (size_t)idx * 8) =
+                  *reinterpret_cast<const uint4*>(stage + (size_t)rr * kStageRow + ch * 16);
+            }
+          } else if (a.kv.mode == KV_DECODE || a.kv.mode == KV_TF) {
+            // K (t = 1) or V (t = 2) of the buffer tokens: 16-byte chunks, Dh / 8 lanes per (row, head)
+            const int cph = Dh >> 3;  // chunks per head
+            for (int idx = tid_e; idx < BM * kChunksPerRow; idx += kEpi) {
+              const int rr = idx / kChunksPerRow, ch = idx - rr * kChunksPerRow;
+              const long gr = row0 + rr;
+              if (gr >= a.rows) continue;
+              const long bb = gr / a.kv.tokens_per_stream;
+              const int jj = (int)(gr - bb * a.kv.tokens_per_stream);
+              if (jj >= a.kv.n_kv_tokens) continue;
+              const int hh = ch / cph, cc = ch - hh * cph;
+              __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(a.kv.kv_buf) +
+                                   (((size_t)(bb * a.kv.n_heads + hh) * a.kv.max_buf + a.kv.pos0 + jj) * 2 + (t - 1)) * Dh +
+                                   cc * 8;
+              *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(stage + (size_t)rr * kStageRow + ch * 16);
+            }
+          }
+          e.sync_groups();  // the staging tile is reused by the next projection
+        } else {
+          // prefill: context K rows and the transposed hi|lo context V, written straight from registers
+#pragma unroll
+          for (int c = 0; c < Epilogue<D>::NCH; ++c) {
+            const int cbase = e.col0 + 16 * c;
+            if (t == 1 && k_dst) {
+#pragma unroll
+              for (int i = 0; i < 2; ++i) {
+                const int col = cbase + 8 * i;
+                const int h = col >> dh_shift, d = col & (Dh - 1);
+                *reinterpret_cast<uint4*>(k_dst + (size_t)h * k_hstride + d) = make_uint4(
+                    pack_bf16(__uint_as_float(r[c][8 * i]), __uint_as_float(r[c][8 * i + 1])),
+                    pack_bf16(__uint_as_float(r[c][8 * i + 2]), __uint_as_float(r[c][8 * i + 3])),
+                    pack_bf16(__uint_as_float(r[c][8 * i + 4]), __uint_as_float(r[c][8 * i + 5])),
+                    pack_bf16(__uint_as_float(r[c][8 * i + 6]), __uint_as_float(r[c][8 * i + 7])));
+              }
+            } else if (t == 2 && vt_dst) {
+#pragma unroll
+              for (int i = 0; i < 16; ++i) {
+                const int col = cbase + i;
+                const int h = col >> dh_shift, d = col & (Dh - 1);
+                const float val = __uint_as_float(r[c][i]);
+                const __nv_bfloat16 hi = __float2bfloat16_rn(val);
+                __nv_bfloat16* p = vt_dst + ((size_t)h * 2 * Dh + d) * a.kv.n_ctx_pad;
+                p[0] = hi;
+                p[(size_t)Dh * a.kv.n_ctx_pad] = __float2bfloat16_rn(val - __bfloat162float(hi));
+              }
+            }
+          }
         }
         TSTAMP(25 + t);
       }
