@@ -148,6 +148,12 @@ __global__ void __launch_bounds__(kWarps * 32) ctx_attn_simt_kernel(const CtxAtt
   }
 }
 
+__device__ __forceinline__ float fast_exp2(float x) {  // MUFU ex2: relative error 2^-22, exp2(-inf) = 0
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 // ---------------------------------------------------------------------------
 // Private-buffer pass + merge.  One warp per (stream, head[, item]).
 // Each key's K row and V row are adjacent in memory ([.., T][2][Dh]), so a warp
@@ -208,41 +214,75 @@ __global__ void __launch_bounds__(128) buf_merge_kernel(const BufMergeArgs a) {
     for (int e = 0; e < VEC; ++e) acc[w][e] = 0.f;
 
   const T* kv = reinterpret_cast<const T*>(a.kv_buf) + ((size_t)(b * a.n_heads + h) * a.max_buf) * 2 * DH;
-#pragma unroll 2
-  for (int key0 = 0; key0 < len; key0 += KPI) {
-    const int key = key0 + grp;
-    const bool valid = key < len;
-    float kf[VEC], vf[VEC];
-    if (valid) {
-      const T* p = kv + (size_t)key * 2 * DH + sub * VEC;
-      Vec16<T>::load(p, kf);
-      Vec16<T>::load(p + DH, vf);
-    } else {
+  // Keys are walked in chunks of CH warp iterations: all 2*CH 16-byte loads of a chunk are issued
+  // before the first is used, so a warp has CH KiB in flight and pays one memory round trip per
+  // chunk instead of one per iteration.
+  constexpr int CH = 4;
+  for (int key0 = 0; key0 < len; key0 += KPI * CH) {
+    uint4 kr[CH], vr[CH];
 #pragma unroll
-      for (int e = 0; e < VEC; ++e) kf[e] = vf[e] = 0.f;
-    }
-    float s[2] = {0.f, 0.f};
-#pragma unroll
-    for (int e = 0; e < VEC; ++e) {
-      s[0] = fmaf(q[0][e], kf[e], s[0]);
-      s[1] = fmaf(q[1][e], kf[e], s[1]);
-    }
-#pragma unroll
-    for (int o = 1; o < LPK; o <<= 1) {
-      s[0] += __shfl_xor_sync(0xffffffffu, s[0], o);
-      s[1] += __shfl_xor_sync(0xffffffffu, s[1], o);
-    }
-    if (valid) {
-#pragma unroll
-      for (int w = 0; w < 2; ++w) {
-        const float mn = fmaxf(m[w], s[w]);
-        const float alpha = exp2f(m[w] - mn);
-        const float p = exp2f(s[w] - mn);
-        l[w] = l[w] * alpha + p;
-        m[w] = mn;
-#pragma unroll
-        for (int e = 0; e < VEC; ++e) acc[w][e] = fmaf(p, vf[e], acc[w][e] * alpha);
+    for (int c = 0; c < CH; ++c) {
+      const int key = key0 + c * KPI + grp;
+      if (key < len) {
+        const uint4* p = reinterpret_cast<const uint4*>(kv + (size_t)key * 2 * DH + sub * VEC);
+        kr[c] = __ldg(p);
+        vr[c] = __ldg(p + LPK);  // the V row follows the K row: DH elements = LPK 16-byte slices
+      } else {
+        kr[c] = make_uint4(0u, 0u, 0u, 0u);
+        vr[c] = kr[c];
       }
+    }
+    // scores of the chunk first, then ONE running-max update and rescale for all CH keys
+    float sc0[CH], sc1[CH];
+#pragma unroll
+    for (int c = 0; c < CH; ++c) {
+      float kf[VEC];
+      Vec16<T>::unpack(kr[c], kf);
+      float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) {
+        s0 = fmaf(q[0][e], kf[e], s0);
+        s1 = fmaf(q[1][e], kf[e], s1);
+      }
+#pragma unroll
+      for (int o = 1; o < LPK; o <<= 1) {
+        s0 += __shfl_xor_sync(0xffffffffu, s0, o);
+        s1 += __shfl_xor_sync(0xffffffffu, s1, o);
+      }
+      const bool valid = key0 + c * KPI + grp < len;
+      sc0[c] = valid ? s0 : -INFINITY;
+      sc1[c] = valid ? s1 : -INFINITY;
+    }
+    if (key0 + grp < len) {  // this lane group has at least one key in the chunk
+      float mn0 = m[0], mn1 = m[1];
+#pragma unroll
+      for (int c = 0; c < CH; ++c) {
+        mn0 = fmaxf(mn0, sc0[c]);
+        mn1 = fmaxf(mn1, sc1[c]);
+      }
+      const float a0 = fast_exp2(m[0] - mn0), a1 = fast_exp2(m[1] - mn1);
+      l[0] *= a0;
+      l[1] *= a1;
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) {
+        acc[0][e] *= a0;
+        acc[1][e] *= a1;
+      }
+#pragma unroll
+      for (int c = 0; c < CH; ++c) {
+        float vf[VEC];
+        Vec16<T>::unpack(vr[c], vf);
+        const float p0 = fast_exp2(sc0[c] - mn0), p1 = fast_exp2(sc1[c] - mn1);  // masked keys: exp2(-inf) = 0
+        l[0] += p0;
+        l[1] += p1;
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) {
+          acc[0][e] = fmaf(p0, vf[e], acc[0][e]);
+          acc[1][e] = fmaf(p1, vf[e], acc[1][e]);
+        }
+      }
+      m[0] = mn0;
+      m[1] = mn1;
     }
   }
   // fold the KPI per-group partial softmaxes together
@@ -253,8 +293,8 @@ __global__ void __launch_bounds__(128) buf_merge_kernel(const BufMergeArgs a) {
       const float mo = __shfl_xor_sync(0xffffffffu, m[w], o);
       const float lo = __shfl_xor_sync(0xffffffffu, l[w], o);
       const float mn = fmaxf(m[w], mo);
-      const float a1 = mn == -INFINITY ? 0.f : exp2f(m[w] - mn);
-      const float a2 = mn == -INFINITY ? 0.f : exp2f(mo - mn);
+      const float a1 = mn == -INFINITY ? 0.f : fast_exp2(m[w] - mn);
+      const float a2 = mn == -INFINITY ? 0.f : fast_exp2(mo - mn);
       l[w] = l[w] * a1 + lo * a2;
       m[w] = mn;
 #pragma unroll

@@ -54,16 +54,21 @@ struct Vec16;
 template <>
 struct Vec16<float> {
   static constexpr int N = 4;
+  __device__ static __forceinline__ void unpack(const uint4& v, float* out) {
+    out[0] = __uint_as_float(v.x); out[1] = __uint_as_float(v.y);
+    out[2] = __uint_as_float(v.z); out[3] = __uint_as_float(v.w);
+  }
   __device__ static __forceinline__ void load(const float* p, float* out) {
-    float4 v = *reinterpret_cast<const float4*>(p);
-    out[0] = v.x; out[1] = v.y; out[2] = v.z; out[3] = v.w;
+    unpack(*reinterpret_cast<const uint4*>(p), out);
   }
 };
 template <>
 struct Vec16<__nv_bfloat16> {
   static constexpr int N = 8;
   __device__ static __forceinline__ void load(const __nv_bfloat16* p, float* out) {
-    uint4 v = *reinterpret_cast<const uint4*>(p);
+    unpack(*reinterpret_cast<const uint4*>(p), out);
+  }
+  __device__ static __forceinline__ void unpack(const uint4& v, float* out) {
     const uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
