@@ -93,6 +93,7 @@ int check_state(const artab_model* m, const artab_state* st) {
   ARTAB_REQUIRE(st->k_ctx && st->v_ctx && st->x && st->x1 && st->attn && st->q && st->o_part && st->lse_part,
                 ARTAB_EINVAL, "state: null buffer");
   ARTAB_REQUIRE(st->max_splits >= 1, ARTAB_EINVAL, "state: max_splits < 1");
+  ARTAB_REQUIRE(st->max_rows % 128 == 0, ARTAB_EINVAL, "state: max_rows must be a multiple of 128");
   (void)m;
   return ARTAB_OK;
 }

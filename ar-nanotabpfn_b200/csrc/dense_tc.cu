@@ -443,8 +443,13 @@ struct Epilogue {
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
         const float2 bb = *reinterpret_cast<const float2*>(bias + j * HT + HPART * wg + 16 * half + 2 * i);
+#ifdef EXP_NOGELU
+        const float x0 = __uint_as_float(r[half][2 * i]) + bb.x;
+        const float x1 = __uint_as_float(r[half][2 * i + 1]) + bb.y;
+#else
         const float x0 = gelu_fast(__uint_as_float(r[half][2 * i]) + bb.x);
         const float x1 = gelu_fast(__uint_as_float(r[half][2 * i + 1]) + bb.y);
+#endif
         split2(x0, x1, hi[i], lo[i]);
       }
       if (half == 0 && j >= 1) {  // the previous tile's second GEMM must have finished reading the buffer

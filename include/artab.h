@@ -138,6 +138,8 @@ typedef struct artab_state {
   void* k_ctx;
   void* v_ctx;
   void* kv_buf;
+  /* max_rows must be a multiple of 128 (the tensor-core chain reads whole 128-row tiles).  In bf16
+   * mode x1 and attn are library-private scratch in a lane-major tile layout; x stays row-major. */
   float* x;             /* [max_rows][D] layer input / output (residual stream) */
   float* x1;            /* [max_rows][D] post-norm1 activations */
   float* attn;          /* [max_rows][D] merged attention output */
