@@ -27,10 +27,10 @@ namespace {
 
 constexpr int BM = 128;          // token rows per CTA
 constexpr int HT = 128;          // hidden units per MLP tile
-constexpr int NSLOT = 6;         // weight ring depth
+constexpr int NSLOT = 3;         // depth of each of the two weight rings
 constexpr int NWG = 4;           // epilogue threads per row (column groups)
 constexpr int kEpi = 128 * NWG;  // epilogue threads
-constexpr int kThreads = 64 + kEpi;
+constexpr int kThreads = 64 + kEpi + 64;  // + second MMA issuer warp and its weight producer warp
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kAccA = 0;    // wide accumulator (<= 192 columns)
 constexpr uint32_t kAxHi = 192;  // activation operand, hi part (<= 96 packed columns)
@@ -128,25 +128,26 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 }
 // x -> (hi, lo) bf16 with hi + lo = x to 16 mantissa bits, for two neighbouring columns at once
 __device__ __forceinline__ void split2(float a, float b, uint32_t& hi, uint32_t& lo) {
-  const __nv_bfloat16 ah = __float2bfloat16_rn(a), bh = __float2bfloat16_rn(b);
-  hi = (uint32_t)__bfloat16_as_ushort(ah) | ((uint32_t)__bfloat16_as_ushort(bh) << 16);
-  lo = pack_bf16(a - __bfloat162float(ah), b - __bfloat162float(bh));
+  hi = pack_bf16(a, b);
+  lo = pack_bf16(a - __uint_as_float(hi << 16), b - __uint_as_float(hi & 0xffff0000u));
 }
 
-// erf by Abramowitz-Stegun 7.1.26 (|error| < 1.5e-7), exp on the MUFU pipe
+// GELU with erf(z) = 1 - 2^q(z) for z >= 0, q a degree-8 polynomial fitted to log2(erfc) on [0, 4]
+// (|erf error| < 4e-6, below the 2^-17 of the hi + lo operand split): one MUFU op per element.
 __device__ __forceinline__ float gelu_fast(float x) {
-  const float z = fabsf(x) * 0.70710678118654752f;
-  float t;
-  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(t) : "f"(fmaf(0.3275911f, z, 1.0f)));
-  float poly = fmaf(1.061405429f, t, -1.453152027f);
-  poly = fmaf(poly, t, 1.421413741f);
-  poly = fmaf(poly, t, -0.284496736f);
-  poly = fmaf(poly, t, 0.254829592f);
-  poly *= t;
+  const float z = fminf(fabsf(x) * 0.70710678118654752f, 6.0f);
+  float q = fmaf(-1.2271906e-06f, z, -2.4917551e-06f);
+  q = fmaf(q, z, 0.00038366718f);
+  q = fmaf(q, z, -0.0049292254f);
+  q = fmaf(q, z, 0.03347154f);
+  q = fmaf(q, z, -0.15211754f);
+  q = fmaf(q, z, -0.9171586f);
+  q = fmaf(q, z, -1.6280657f);
+  q *= z;
   float e;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(-z * z * 1.4426950408889634f));
-  const float erf_abs = fmaf(-poly, e, 1.0f);
-  return 0.5f * x * (1.0f + copysignf(erf_abs, x));
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(q));
+  const float h = 0.5f * x;
+  return fmaf(copysignf(1.0f - e, x), h, h);  // 0.5 x (1 + erf)
 }
 
 #ifdef DENSE_TC_TIMING
@@ -159,12 +160,12 @@ __device__ long long g_dbg[64];
 #endif
 
 struct __align__(1024) Smem {
-  uint8_t ring[NSLOT][192 * 128];     // weight slabs (d_model * 128 bytes each)
+  uint8_t ring[2][NSLOT][192 * 128];  // two weight rings (first / second MLP GEMM), slabs <= d_model * 128 bytes
   uint8_t ah[2][2][BM * 128];         // hidden tile operand [hi, lo][k-chunk][128 rows x 64 bf16], swizzled
   float xs[2][NWG][BM];               // LayerNorm partial sums exchanged between the column groups
   float bias_h[1024];                 // hidden bias of the current MLP (b1 / head.0 bias), d_ff <= 1024
   float vec[8][192];                  // ln2 g,b | b2 | ln3 g,b | (ln1 | final) g,b | spare
-  uint64_t w_full[NSLOT], w_empty[NSLOT];
+  uint64_t w_full[2][NSLOT], w_empty[2][NSLOT];
   uint64_t ep_done, acc_full, h_full, acch_free, ah_ready, ah_free;
   uint32_t tmem_base;
   int abort_flag;
@@ -179,21 +180,21 @@ struct Ctx {
 // ------------------------------------------------------------------ producer
 struct Producer {
   Smem* sm;
+  int ring;   // which weight ring this thread feeds
   int issued;
   bool ok;
   __device__ void slab(const uint8_t* src, uint32_t bytes) {
     if (!ok) return;
     const int buf = issued % NSLOT;
-    if (issued >= NSLOT && !mbar_wait(&sm->w_empty[buf], ((issued / NSLOT) + 1) & 1, &sm->abort_flag)) {
+    if (issued >= NSLOT && !mbar_wait(&sm->w_empty[ring][buf], ((issued / NSLOT) + 1) & 1, &sm->abort_flag)) {
       ok = false;
       return;
     }
-    uint64_t* bar = &sm->w_full[buf];
-    if (issued == 20) MSTAMP(54);
+    uint64_t* bar = &sm->w_full[ring][buf];
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
                  : "memory");
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                 ::"r"(smem_u32(sm->ring[buf])), "l"(src), "r"(bytes), "r"(smem_u32(bar))
+                 ::"r"(smem_u32(sm->ring[ring][buf])), "l"(src), "r"(bytes), "r"(smem_u32(bar))
                  : "memory");
     ++issued;
   }
@@ -203,19 +204,17 @@ struct Producer {
     const int n = groups * (has_lo ? 2 : 1);
     for (int i = 0; i < n; ++i) slab(p + (size_t)i * slab_bytes, slab_bytes);
   }
-  // two-GEMM MLP: per 128-wide hidden tile the first matrix contributes nkc slabs of 16 KB per part
-  // and the second matrix two k-chunk slabs per part; tiles of the second trail by one
-  __device__ void mlp(const void* w1, bool lo1, int nkc, const void* w2, bool lo2, uint32_t bytes2, int nt) {
-    const uint8_t* p1 = reinterpret_cast<const uint8_t*>(w1);
-    const uint8_t* p2 = reinterpret_cast<const uint8_t*>(w2);
-    const int s1 = nkc * (lo1 ? 2 : 1), s2 = 2 * (lo2 ? 2 : 1);
-    const uint32_t bytes1 = HT * 128;
-    for (int j = 0; j < nt; ++j) {
-      for (int i = 0; i < s1; ++i) slab(p1 + (size_t)(j * s1 + i) * bytes1, bytes1);
-      if (j >= 1)
-        for (int i = 0; i < s2; ++i) slab(p2 + (size_t)((j - 1) * s2 + i) * bytes2, bytes2);
-    }
-    for (int i = 0; i < s2; ++i) slab(p2 + (size_t)((nt - 1) * s2 + i) * bytes2, bytes2);
+  // first GEMM of an MLP: per 128-wide hidden tile nkc slabs of 16 KB per part
+  __device__ void mlp_first(const void* w1, bool lo1, int nkc, int nt) {
+    const uint8_t* p = reinterpret_cast<const uint8_t*>(w1);
+    const int n = nt * nkc * (lo1 ? 2 : 1);  // tile-major: hi k-chunks then lo k-chunks of every tile
+    for (int i = 0; i < n; ++i) slab(p + (size_t)i * (HT * 128), HT * 128);
+  }
+  // second GEMM of an MLP: per hidden tile two k-chunk slabs per part
+  __device__ void mlp_second(const void* w2, bool lo2, uint32_t bytes2, int nt) {
+    const uint8_t* p = reinterpret_cast<const uint8_t*>(w2);
+    const int n = nt * 2 * (lo2 ? 2 : 1);
+    for (int i = 0; i < n; ++i) slab(p + (size_t)i * bytes2, bytes2);
   }
 };
 
@@ -223,6 +222,7 @@ struct Producer {
 struct Issuer {
   Smem* sm;
   uint32_t tmem;
+  int ring;         // which weight ring this thread drains
   int consumed;     // ring slabs consumed
   int ep_phase;     // completed waits on ep_done
   int ah_count;     // completed waits on ah_ready
@@ -231,15 +231,12 @@ struct Issuer {
 
   __device__ uint32_t slab_wait() {
     const int buf = consumed % NSLOT;
-    if (consumed == 20) MSTAMP(55);
-    if (consumed == 14) MSTAMP(57);
-    ok = ok && mbar_wait(&sm->w_full[buf], (consumed / NSLOT) & 1, &sm->abort_flag);
-    if (consumed == 20) MSTAMP(56);
+    ok = ok && mbar_wait(&sm->w_full[ring][buf], (consumed / NSLOT) & 1, &sm->abort_flag);
     tc_fence_after();
-    return smem_u32(sm->ring[buf]);
+    return smem_u32(sm->ring[ring][buf]);
   }
   __device__ void slab_release() {
-    umma_commit(&sm->w_empty[consumed % NSLOT]);
+    umma_commit(&sm->w_empty[ring][consumed % NSLOT]);
     ++consumed;
   }
   __device__ void wait_epilogue() {
@@ -312,37 +309,33 @@ struct Issuer {
       }
     }
   }
-  // hidden = act(A_x . W1^T) tile by tile into ACC_H, ACC_A = hidden . W2^T.  The epilogue frees
-  // ACC_H as soon as it has pulled a tile into registers, so tile j+1 is computed while tile j is
-  // still being activated; the second GEMM of tile j follows the first GEMM of tile j+1.
-  __device__ void mlp(int nkc, bool lo1, bool lo2, int nt, int n_out) {
+  // First MLP GEMM (issuer A): hidden tile j = A_x . W1_j^T into ACC_H.  The epilogue frees ACC_H
+  // as soon as it has pulled a tile into registers, so tile j+1 is computed while tile j is still
+  // being activated.
+  __device__ void mlp_first(int nkc, bool lo1, int nt) {
     for (int j = 0; j < nt; ++j) {
-      if (j == 3) MSTAMP(48);
       if (j >= 1) wait_hidden_free();
-      if (j == 3) MSTAMP(49);
       gemm_tile_ts(nkc, lo1);
-      if (j == 3) MSTAMP(50);
       umma_commit(&sm->h_full);
-      if (j >= 1) second(j - 1, lo2, n_out);
-      if (j == 3) MSTAMP(53);
     }
     wait_hidden_free();  // keeps the phase count exact for a second MLP in the same launch
-    second(nt - 1, lo2, n_out);
+  }
+  // Second MLP GEMM (issuer B, its own thread: MMAs from two threads overlap in the tensor pipe):
+  // ACC_A (+)= act(hidden tile j) . W2_j^T as soon as the epilogue has published tile j.
+  __device__ void mlp_second(bool lo2, int nt, int n_out) {
+    for (int j = 0; j < nt; ++j) {
+      ok = ok && mbar_wait(&sm->ah_ready, ah_count & 1, &sm->abort_flag);
+      ++ah_count;
+      tc_fence_after();
+      gemm_chunks_ss(n_out, lo2, j > 0);
+      umma_commit(&sm->ah_free);
+    }
     umma_commit(&sm->acc_full);
   }
   __device__ void wait_hidden_free() {
     ok = ok && mbar_wait(&sm->acch_free, hfree_count & 1, &sm->abort_flag);
     ++hfree_count;
     tc_fence_after();
-  }
-  __device__ void second(int j, bool lo2, int n_out) {
-    ok = ok && mbar_wait(&sm->ah_ready, ah_count & 1, &sm->abort_flag);
-    ++ah_count;
-    tc_fence_after();
-    if (j == 2) MSTAMP(51);
-    gemm_chunks_ss(n_out, lo2, j > 0);
-    if (j == 2) MSTAMP(52);
-    umma_commit(&sm->ah_free);
   }
 };
 
@@ -424,48 +417,46 @@ struct Epilogue {
   }
   // hidden tile j: act(ACC_H + bias) -> split -> swizzled shared-memory operand
   __device__ void hidden_tile(int j, const float* bias) {
+    if (j == 3) TSTAMP(40);
     ok = mbar_wait(&sm->h_full, h_count & 1, &sm->abort_flag) && ok;
     ++h_count;
     tc_fence_after();
+    if (j == 3) TSTAMP(41);
     uint32_t r[2][16];
 #pragma unroll
     for (int c = 0; c < 2; ++c) tmem_ld16(t_row + kAccH + HPART * wg + 16 * c, r[c]);
     tmem_wait_ld();
     tc_fence_before();
     mbar_arrive(&sm->acch_free);  // the accumulator is in registers: the next tile's GEMM may overwrite it
+    if (j == 3) TSTAMP(42);
+    uint32_t hi[16], lo[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const float2 bb = *reinterpret_cast<const float2*>(bias + j * HT + HPART * wg + 2 * i);
+      const float x0 = gelu_fast(__uint_as_float(r[i >> 3][(2 * i) & 15]) + bb.x);
+      const float x1 = gelu_fast(__uint_as_float(r[i >> 3][(2 * i + 1) & 15]) + bb.y);
+      split2(x0, x1, hi[i], lo[i]);
+    }
+    if (j == 3) TSTAMP(43);
+    if (j >= 1) {  // the previous tile's second GEMM must have finished reading the operand buffer
+      ok = mbar_wait(&sm->ah_free, free_count & 1, &sm->abort_flag) && ok;
+      ++free_count;
+    }
+    if (j == 3) TSTAMP(44);
     // this thread's 32 hidden columns sit in k-chunk wg / 2, 16-byte chunks 4 * (wg % 2) .. + 3 of the
     // 128-byte row; chunk c of row r lives at chunk position c ^ (r % 8)
     uint8_t* base_hi = sm->ah[0][wg >> 1] + row * 128;
     uint8_t* base_lo = sm->ah[1][wg >> 1] + row * 128;
 #pragma unroll
-    for (int half = 0; half < 2; ++half) {
-      uint32_t hi[8], lo[8];
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const float2 bb = *reinterpret_cast<const float2*>(bias + j * HT + HPART * wg + 16 * half + 2 * i);
-#ifdef EXP_NOGELU
-        const float x0 = __uint_as_float(r[half][2 * i]) + bb.x;
-        const float x1 = __uint_as_float(r[half][2 * i + 1]) + bb.y;
-#else
-        const float x0 = gelu_fast(__uint_as_float(r[half][2 * i]) + bb.x);
-        const float x1 = gelu_fast(__uint_as_float(r[half][2 * i + 1]) + bb.y);
-#endif
-        split2(x0, x1, hi[i], lo[i]);
-      }
-      if (half == 0 && j >= 1) {  // the previous tile's second GEMM must have finished reading the buffer
-        ok = mbar_wait(&sm->ah_free, free_count & 1, &sm->abort_flag) && ok;
-        ++free_count;
-      }
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        const int pos = ((4 * (wg & 1) + 2 * half + c) ^ (row & 7)) * 16;
-        *reinterpret_cast<uint4*>(base_hi + pos) = make_uint4(hi[4 * c], hi[4 * c + 1], hi[4 * c + 2], hi[4 * c + 3]);
-        *reinterpret_cast<uint4*>(base_lo + pos) = make_uint4(lo[4 * c], lo[4 * c + 1], lo[4 * c + 2], lo[4 * c + 3]);
-      }
+    for (int c = 0; c < 4; ++c) {
+      const int pos = ((4 * (wg & 1) + c) ^ (row & 7)) * 16;
+      *reinterpret_cast<uint4*>(base_hi + pos) = make_uint4(hi[4 * c], hi[4 * c + 1], hi[4 * c + 2], hi[4 * c + 3]);
+      *reinterpret_cast<uint4*>(base_lo + pos) = make_uint4(lo[4 * c], lo[4 * c + 1], lo[4 * c + 2], lo[4 * c + 3]);
     }
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic writes -> visible to the MMA's reads
     tc_fence_before();
     mbar_arrive(&sm->ah_ready);
+    if (j == 3) TSTAMP(45);
   }
   // After an MLP: consume the ah_free completion of its last tile, which no hidden_tile waited for,
   // so that the parity bookkeeping is exact when a second MLP runs in the same launch.
@@ -536,10 +527,11 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const DenseArgs a
   const long row0 = (long)blockIdx.x * BM;
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < NSLOT; ++i) {
-      mbar_init(&sm->w_full[i], 1);
-      mbar_init(&sm->w_empty[i], 1);
-    }
+    for (int r = 0; r < 2; ++r)
+      for (int i = 0; i < NSLOT; ++i) {
+        mbar_init(&sm->w_full[r][i], 1);
+        mbar_init(&sm->w_empty[r][i], 1);
+      }
     mbar_init(&sm->ep_done, kEpi);
     mbar_init(&sm->acc_full, 1);
     mbar_init(&sm->h_full, 1);
@@ -582,34 +574,41 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const DenseArgs a
   const int lo_post = a.post_w.tc_lo, lo_pre = a.pre_w.tc_lo;
 
   if (warp == 0) {
-    // ------------------------------ weight producer ------------------------------
+    // --------------------- weight producer A: everything but the second MLP GEMM ---------------------
     if (lane == 0) {
-      Producer p{sm, 0, true};
+      Producer p{sm, 0, 0, true};
       if (a.do_post) {
         p.matrix(a.post_w.tc_wo, NKC, lo_post & 1, kSlab);
-        p.mlp(a.post_w.tc_w1, lo_post & 2, NKC, a.post_w.tc_w2, lo_post & 4, kSlab, nt);
+        p.mlp_first(a.post_w.tc_w1, lo_post & 2, NKC, nt);
       }
       if (a.do_head) {
-        p.mlp(a.tc_wa, a.tc_head_lo & 1, NKC, a.tc_wb, a.tc_head_lo & 2, 16 * 128, nt);
+        p.mlp_first(a.tc_wa, a.tc_head_lo & 1, NKC, nt);
       } else if (a.do_pre) {
         p.matrix(a.pre_w.tc_wf, NKC, lo_pre & 8, kSlab);
         p.matrix(a.pre_w.tc_wqkv, 3 * NKC, lo_pre & 16, kSlab);
       }
     }
-  } else if (warp == 1) {
-    // --------------------------------- MMA issuer ---------------------------------
+  } else if (warp == 19) {
+    // --------------------- weight producer B: the second MLP GEMM's k-chunks ---------------------
     if (lane == 0) {
-      Issuer m{sm, tmem, 0, 0, 0, 0, true};
+      Producer p{sm, 1, 0, true};
+      if (a.do_post) p.mlp_second(a.post_w.tc_w2, lo_post & 4, kSlab, nt);
+      if (a.do_head) p.mlp_second(a.tc_wb, a.tc_head_lo & 2, 16 * 128, nt);
+    }
+  } else if (warp == 1) {
+    // --------------------------------- MMA issuer A ---------------------------------
+    if (lane == 0) {
+      Issuer m{sm, tmem, 0, 0, 0, 0, 0, true};
       if (a.do_post) {
         m.wait_epilogue();                               // A_x = attention output
         m.gemm_full_ts(kAccA, D, NKC, lo_post & 1);
         umma_commit(&sm->acc_full);
         m.wait_epilogue();                               // A_x = x2 (and ACC_A drained)
-        m.mlp(NKC, lo_post & 2, lo_post & 4, nt, D);
+        m.mlp_first(NKC, lo_post & 2, nt);
       }
       if (a.do_head) {
         m.wait_epilogue();                               // A_x = z
-        m.mlp(NKC, a.tc_head_lo & 1, a.tc_head_lo & 2, nt, 16);
+        m.mlp_first(NKC, a.tc_head_lo & 1, nt);
       } else if (a.do_pre) {
         m.wait_epilogue();                               // A_x = layer input
         m.gemm_full_ts(kAccA, D, NKC, lo_pre & 8);
@@ -621,6 +620,13 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const DenseArgs a
           umma_commit(&sm->acc_full);
         }
       }
+    }
+  } else if (warp == 18) {
+    // --------------------------------- MMA issuer B ---------------------------------
+    if (lane == 0) {
+      Issuer m{sm, tmem, 1, 0, 0, 0, 0, true};
+      if (a.do_post) m.mlp_second(lo_post & 4, nt, D);
+      if (a.do_head) m.mlp_second(a.tc_head_lo & 2, nt, 16);
     }
   } else {
     // ---------------------------------- epilogue ----------------------------------
