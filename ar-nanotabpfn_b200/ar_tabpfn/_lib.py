@@ -58,6 +58,7 @@ _SIGNATURES = {
     "artab_head_sample": (_i, [C.POINTER(Model), _p, _p, _p, _i, _p, _p, _p, _p]),
     "artab_plan_splits": (_i, [_i, _i, _i, _i, _i, _i]),
     "artab_profile_enable": (None, [_i]),
+    "artab_set_dependent_launch": (None, [_i]),
     "artab_profile_read": (_i, [C.POINTER(C.c_double), C.POINTER(C.c_int64), _i]),
     "artab_launch_count": (C.c_int64, []),
     "artab_launch_count_reset": (None, []),

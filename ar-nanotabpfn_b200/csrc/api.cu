@@ -3,6 +3,7 @@
 // points.  Nothing here allocates or synchronises.
 #include <cstdarg>
 #include <cstdio>
+#include <atomic>
 #include <cstring>
 #include <vector>
 
@@ -34,6 +35,9 @@ static thread_local std::vector<ProfSlot>* g_prof = nullptr;
 static thread_local std::vector<ProfSlot>* g_prof_pool = nullptr;
 
 void count_launch() { ++g_launches; }
+
+static std::atomic<int> g_dependent_launch{1};
+bool dependent_launch_enabled() { return g_dependent_launch.load(std::memory_order_relaxed) != 0; }
 
 void prof_begin(int kind, cudaStream_t s) {
   if (!g_prof_on) return;
@@ -161,7 +165,7 @@ bool chain_on_tc(const artab_model* m, const artab_state* st) {
 }
 
 int run_ctx(const artab_model* m, const artab_state* st, int layer, int rows, int rows_per_group, int n_splits,
-            float* out, float* lse, cudaStream_t s) {
+            float* out, float* lse, bool kv_stable, cudaStream_t s) {
   const Layout lo = layout_of(m, st);
   CtxAttnArgs c;
   memset(&c, 0, sizeof(c));
@@ -183,6 +187,7 @@ int run_ctx(const artab_model* m, const artab_state* st, int layer, int rows, in
   c.out_lane_major = out == st->attn && chain_on_tc(m, st);
   c.lse = lse;
   c.status = st->status;
+  c.kv_stable = kv_stable ? 1 : 0;
   return use_tc(st->dtype, m->head_dim) ? launch_ctx_attn_tc(c, s) : launch_ctx_attn_simt(c, s);
 }
 
@@ -258,10 +263,10 @@ int run_layers(const artab_model* m, artab_state* st, int rows, int rows_per_gro
   for (int l = 0; l < m->n_layers; ++l) {
     int rc;
     if (!need_merge && n_splits == 1) {
-      rc = run_ctx(m, st, l, rows, rows_per_group, 1, st->attn, st->lse_part, s);
+      rc = run_ctx(m, st, l, rows, rows_per_group, 1, st->attn, st->lse_part, true, s);
       if (rc) return rc;
     } else {
-      rc = run_ctx(m, st, l, rows, rows_per_group, n_splits, st->o_part, st->lse_part, s);
+      rc = run_ctx(m, st, l, rows, rows_per_group, n_splits, st->o_part, st->lse_part, true, s);
       if (rc) return rc;
       BufMergeArgs b = buf_proto;
       b.kv_buf = st->kv_buf ? off(st->kv_buf, lo.buf_layer * l, st->dtype) : nullptr;
@@ -353,6 +358,8 @@ int artab_plan_splits(int dtype, int rows, int rows_per_group, int n_groups, int
 
 void artab_profile_enable(int on) { g_prof_on = on != 0; }
 
+void artab_set_dependent_launch(int on) { g_dependent_launch.store(on != 0, std::memory_order_relaxed); }
+
 int artab_profile_read(double* ms_per_kind, int64_t* launches_per_kind, int n_kinds) {
   for (int i = 0; i < n_kinds; ++i) {
     ms_per_kind[i] = 0.0;
@@ -415,7 +422,7 @@ int artab_prefill(const artab_model* m, artab_state* st, const float* xc, const 
   if (rc) return rc;
   for (int l = 0; l + 1 < m->n_layers; ++l) {
     // dense non-causal self-attention over the context rows of each group
-    rc = run_ctx(m, st, l, rows, st->n_ctx, 1, st->attn, st->lse_part, s);
+    rc = run_ctx(m, st, l, rows, st->n_ctx, 1, st->attn, st->lse_part, false, s);
     if (rc) return rc;
     DenseArgs d = dense_base(m, st, rows);
     d.do_post = 1;

@@ -16,6 +16,7 @@ struct CtxAttnArgs {
   int out_lane_major; // n_splits == 1 only: write the [rows][H*Dh] result in the lane-major layout
   float* lse;         // [splits][rows][H]
   int32_t* status;    // device status word (bounded waits), may be null for SIMT
+  int kv_stable;      // k_ctx / v_ctx were not written by the kernel launched just before this one
 };
 
 struct BufMergeArgs {

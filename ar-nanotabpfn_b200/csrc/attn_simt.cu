@@ -305,6 +305,11 @@ __global__ void __launch_bounds__(128) buf_merge_kernel(const BufMergeArgs a) {
     }
   }
 
+  // The buffer pass above read only what kernels older than the preceding one wrote (q and the
+  // buffer rows); the context partials come from the preceding kernel.
+  dep_wait();
+  dep_trigger();
+
   // log-sum-exp merge with the context partials, all in registers
 #pragma unroll
   for (int w = 0; w < 2; ++w) {
@@ -385,16 +390,18 @@ template <typename T>
 int launch_buf_t(const BufMergeArgs& a, cudaStream_t s) {
   const int wpb = 4;
   const unsigned grid = (unsigned)((a.n_items + wpb - 1) / wpb);
+  cudaError_t le = cudaSuccess;
   prof_begin(PROF_BUF, s);
   switch (a.head_dim) {
-    case 16: buf_merge_kernel<T, 16><<<grid, wpb * 32, 0, s>>>(a); break;
-    case 32: buf_merge_kernel<T, 32><<<grid, wpb * 32, 0, s>>>(a); break;
-    case 64: buf_merge_kernel<T, 64><<<grid, wpb * 32, 0, s>>>(a); break;
+    case 16: le = launch_dependent(buf_merge_kernel<T, 16>, dim3(grid), dim3(wpb * 32), 0, s, a); break;
+    case 32: le = launch_dependent(buf_merge_kernel<T, 32>, dim3(grid), dim3(wpb * 32), 0, s, a); break;
+    case 64: le = launch_dependent(buf_merge_kernel<T, 64>, dim3(grid), dim3(wpb * 32), 0, s, a); break;
     default:
       set_error("buffer attention: head_dim %d not supported (16, 32, 64)", a.head_dim);
       return ARTAB_EINVAL;
   }
   prof_end(s);
+  ARTAB_REQUIRE(le == cudaSuccess, ARTAB_ELAUNCH, "buf_merge_kernel: %s", cudaGetErrorString(le));
   count_launch();
   return check_launch("buf_merge_kernel");
 }

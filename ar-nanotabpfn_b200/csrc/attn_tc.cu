@@ -166,6 +166,7 @@ struct TcParams {
   int rows, rows_per_group, n_groups, n_heads, n_ctx, n_ctx_pad, n_splits;
   float scale_log2e;
   int out_lane_major;
+  int kv_stable;  // the context K/V were written long before the preceding kernel: prefetch them early
   float* out;
   float* lse;
   int32_t* status;
@@ -246,6 +247,8 @@ ctx_attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   const size_t out_row = ((size_t)split * p.rows + group_row0 + m0 + row) * p.n_heads + h;
 
   if (nt <= 0) {  // empty split: contributes nothing to the merge
+    dep_wait();
+    dep_trigger();
     if (row_valid) {
       float4* o = reinterpret_cast<float4*>(p.out + out_row * DH);
 #pragma unroll
@@ -278,23 +281,34 @@ ctx_attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   tc_fence_after();
   const uint32_t tmem = sm->tmem_base;
   volatile int* abort_flag = &sm->abort_flag;
+  if (warp != 0) {  // the producer waits after its early K/V prefetch
+    dep_wait();
+    dep_trigger();
+  }
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
     if (lane == 0) {
-      mbar_expect_tx(&sm->q_full, BM * 64);
-      tma_load_2d(sm->q, &tm_q, h * DH, (int)(group_row0 + m0), &sm->q_full);
       const int krow0 = (g * p.n_heads + h) * p.n_ctx_pad;
       const int vrow0 = (g * p.n_heads + h) * 2 * DH;
-      int issued = 0;
-      for (int j = 0; j < nt; ++j) {
+      auto load_kv = [&](int j) {
         const int st = j % NSTAGE;
-        if (j >= NSTAGE && !mbar_wait(&sm->kv_empty[st], ((j / NSTAGE) + 1) & 1, abort_flag)) break;
         const int key0 = (tile_begin + j) * BN;
         mbar_expect_tx(&sm->kv_full[st], BN * 64 + 2 * 64 * 128);
         tma_load_2d(sm->k[st], &tm_k, 0, krow0 + key0, &sm->kv_full[st]);
         tma_load_2d(sm->v[st][0], &tm_v, key0, vrow0, &sm->kv_full[st]);
         tma_load_2d(sm->v[st][1], &tm_v, key0 + 64, vrow0, &sm->kv_full[st]);
+      };
+      // the first ring of K/V tiles may be fetched while the preceding kernel (which produces Q) runs
+      int issued = 0;
+      const int early = p.kv_stable ? min(nt, NSTAGE) : 0;
+      for (; issued < early; ++issued) load_kv(issued);
+      dep_wait();
+      mbar_expect_tx(&sm->q_full, BM * 64);
+      tma_load_2d(sm->q, &tm_q, h * DH, (int)(group_row0 + m0), &sm->q_full);
+      for (int j = issued; j < nt; ++j) {
+        if (j >= NSTAGE && !mbar_wait(&sm->kv_empty[j % NSTAGE], ((j / NSTAGE) + 1) & 1, abort_flag)) break;
+        load_kv(j);
         issued = j + 1;
       }
       if (*abort_flag) {  // drain our own copies before the CTA may exit
@@ -495,14 +509,16 @@ int launch_ctx_attn_tc(const CtxAttnArgs& a, cudaStream_t s) {
   p.n_splits = a.n_splits;
   p.scale_log2e = a.scale * kLog2e;
   p.out_lane_major = a.out_lane_major && a.n_splits == 1;
+  p.kv_stable = a.kv_stable;
   p.out = a.out;
   p.lse = a.lse;
   p.status = a.status;
   const int rows_in_group = a.n_groups == 1 ? a.rows : a.rows_per_group;
   dim3 grid((rows_in_group + BM - 1) / BM, a.n_heads, a.n_groups * a.n_splits);
   prof_begin(PROF_CTX, s);
-  ctx_attn_tc_kernel<<<grid, kThreads, smem, s>>>(tq, tk, tv, p);
+  const cudaError_t le = launch_dependent(ctx_attn_tc_kernel, grid, dim3(kThreads), smem, s, tq, tk, tv, p);
   prof_end(s);
+  ARTAB_REQUIRE(le == cudaSuccess, ARTAB_ELAUNCH, "ctx_attn_tc_kernel: %s", cudaGetErrorString(le));
   count_launch();
   return check_launch("ctx_attn_tc_kernel");
 }

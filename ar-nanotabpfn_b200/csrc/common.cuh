@@ -18,6 +18,36 @@ enum ProfKind : int { PROF_EMBED = 0, PROF_DENSE = 1, PROF_CTX = 2, PROF_BUF = 3
 void prof_begin(int kind, cudaStream_t s);
 void prof_end(cudaStream_t s);
 
+// ---- programmatic dependent launch ---------------------------------------------
+// Kernels of the decode chain are launched with the programmatic-stream-serialization attribute:
+// a kernel may start while its predecessor in the stream still runs, does the work that needs
+// nothing from it (barrier set-up, tensor-memory allocation, loads of weights), and then executes
+// dep_wait(), which returns once the predecessor grid has completed and its writes are visible.
+// Rules every such kernel follows: (1) it calls dep_wait() before it reads anything an earlier
+// kernel wrote and before it writes global memory; (2) it calls dep_trigger() only after its own
+// dep_wait(), so a dependent that starts early knows that everything older than its predecessor
+// has completed.  Without the launch attribute both calls are no-ops.
+__device__ __forceinline__ void dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void dep_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+bool dependent_launch_enabled();
+
+template <typename... P, typename... A>
+inline cudaError_t launch_dependent(void (*kernel)(P...), dim3 grid, dim3 block, size_t smem, cudaStream_t s,
+                                    A&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = dependent_launch_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<P>(args)...);
+}
+
 #define ARTAB_REQUIRE(cond, code, ...) \
   do {                                 \
     if (!(cond)) {                     \

@@ -165,11 +165,14 @@ struct __align__(1024) Smem {
   float xs[2][NWG][BM];               // LayerNorm partial sums exchanged between the column groups
   float bias_h[1024];                 // hidden bias of the current MLP (b1 / head.0 bias), d_ff <= 1024
   float vec[8][192];                  // ln2 g,b | b2 | ln3 g,b | (ln1 | final) g,b | spare
+  __nv_bfloat16* rowdst[BM];          // private-buffer K slot of each row's token (null: not cached)
   uint64_t w_full[2][NSLOT], w_empty[2][NSLOT];
   uint64_t ep_done, acc_full, h_full, acch_free, ah_ready, ah_free;
   uint32_t tmem_base;
   int abort_flag;
 };
+
+__device__ __forceinline__ bool direct_mode(int mode) { return mode == KV_PREFILL; }
 
 struct Ctx {
   Smem* sm;
@@ -675,6 +678,10 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const DenseArgs a
         *reinterpret_cast<float4*>(dst + goff + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
     };
 
+    // Everything above (and the weight producers' first tiles) needed nothing from the preceding
+    // kernel; the activations do.
+    dep_wait();
+    dep_trigger();
     if (a.do_post) {
       load_lm(a.attn);
       TSTAMP(1);
@@ -761,6 +768,7 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const DenseArgs a
           v_dst = k_dst + Dh;
         }
       }
+      if (e.wg == 0) sm->rowdst[e.row] = direct_mode(a.kv.mode) ? nullptr : k_dst;
       // Staging tile for coalesced stores: [128 rows][D bf16] with 16 bytes of padding per row
       // (conflict-free 16-byte accesses), in the hidden-operand buffer, which is idle in this phase.
       constexpr int kStageRow = D * 2 + 16;
@@ -802,19 +810,15 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const DenseArgs a
             }
           } else if (a.kv.mode == KV_DECODE || a.kv.mode == KV_TF) {
             // K (t = 1) or V (t = 2) of the buffer tokens: 16-byte chunks, Dh / 8 lanes per (row, head)
-            const int cph = Dh >> 3;  // chunks per head
+            const int cph_shift = dh_shift - 3;  // 16-byte chunks per head = Dh / 8
+            const size_t hstride = (size_t)a.kv.max_buf * 2 * Dh;
             for (int idx = tid_e; idx < BM * kChunksPerRow; idx += kEpi) {
               const int rr = idx / kChunksPerRow, ch = idx - rr * kChunksPerRow;
-              const long gr = row0 + rr;
-              if (gr >= a.rows) continue;
-              const long bb = gr / a.kv.tokens_per_stream;
-              const int jj = (int)(gr - bb * a.kv.tokens_per_stream);
-              if (jj >= a.kv.n_kv_tokens) continue;
-              const int hh = ch / cph, cc = ch - hh * cph;
-              __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(a.kv.kv_buf) +
-                                   (((size_t)(bb * a.kv.n_heads + hh) * a.kv.max_buf + a.kv.pos0 + jj) * 2 + (t - 1)) * Dh +
-                                   cc * 8;
-              *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(stage + (size_t)rr * kStageRow + ch * 16);
+              __nv_bfloat16* base = sm->rowdst[rr];
+              if (!base) continue;
+              const int hh = ch >> cph_shift, cc = ch & ((1 << cph_shift) - 1);
+              *reinterpret_cast<uint4*>(base + hh * hstride + (t - 1) * Dh + cc * 8) =
+                  *reinterpret_cast<const uint4*>(stage + (size_t)rr * kStageRow + ch * 16);
             }
           }
           e.sync_groups();  // the staging tile is reused by the next projection
@@ -894,25 +898,25 @@ int launch_dense_tc(const DenseArgs& a, cudaStream_t s) {
         e = cudaFuncSetAttribute(dense_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         configured[0] = e == cudaSuccess;
       }
-      if (e == cudaSuccess) dense_tc_kernel<64><<<grid, kThreads, smem, s>>>(a);
+      if (e == cudaSuccess) e = launch_dependent(dense_tc_kernel<64>, dim3(grid), dim3(kThreads), smem, s, a);
       break;
     case 128:
       if (!configured[1]) {
         e = cudaFuncSetAttribute(dense_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         configured[1] = e == cudaSuccess;
       }
-      if (e == cudaSuccess) dense_tc_kernel<128><<<grid, kThreads, smem, s>>>(a);
+      if (e == cudaSuccess) e = launch_dependent(dense_tc_kernel<128>, dim3(grid), dim3(kThreads), smem, s, a);
       break;
     default:
       if (!configured[2]) {
         e = cudaFuncSetAttribute(dense_tc_kernel<192>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         configured[2] = e == cudaSuccess;
       }
-      if (e == cudaSuccess) dense_tc_kernel<192><<<grid, kThreads, smem, s>>>(a);
+      if (e == cudaSuccess) e = launch_dependent(dense_tc_kernel<192>, dim3(grid), dim3(kThreads), smem, s, a);
       break;
   }
   prof_end(s);
-  ARTAB_REQUIRE(e == cudaSuccess, ARTAB_ELAUNCH, "dense_tc_kernel: shared memory refused: %s", cudaGetErrorString(e));
+  ARTAB_REQUIRE(e == cudaSuccess, ARTAB_ELAUNCH, "dense_tc_kernel: launch refused: %s", cudaGetErrorString(e));
   count_launch();
   return check_launch("dense_tc_kernel");
 }

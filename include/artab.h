@@ -278,6 +278,13 @@ ARTAB_API int artab_plan_splits(int dtype, int rows, int rows_per_group, int n_g
 ARTAB_API void artab_profile_enable(int on);
 ARTAB_API int artab_profile_read(double* ms_per_kind, int64_t* launches_per_kind, int n_kinds);
 
+/* Programmatic dependent launch (on by default, process-wide): the kernels of the decode
+ * chain are launched so that each may begin its set-up and weight prefetch while the kernel
+ * before it in the stream drains, and the private-buffer pass runs beside the context
+ * contraction; results are bit-identical either way.  Pass 0 to launch every kernel fully
+ * serialised (diagnostics).  No counterpart in the reference. */
+ARTAB_API void artab_set_dependent_launch(int on);
+
 /* Kernels launched by this library on the calling thread since the last reset
  * (a host-side counter for benchmarks). */
 ARTAB_API int64_t artab_launch_count(void);

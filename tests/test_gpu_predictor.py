@@ -133,6 +133,31 @@ def test_deterministic_and_stream_independent():
         torch.testing.assert_close(sub, a[2:5], atol=1e-5, rtol=1e-5)
 
 
+def test_dependent_launch_is_bit_identical_to_serialised_launch():
+    """The overlapped launch mode (kernels begin while their predecessor drains, the buffer
+    pass runs beside the context contraction) must not change a single bit."""
+    from ar_tabpfn import _lib
+    lib = _lib.lib()
+    fx = load_golden("dh32.pt")
+    m, _ = build_model(fx)
+    c = lambda k: fx[k].cuda()
+    try:
+        for prec in ("fp32", "bf16"):
+            p = predictor(m, "triton_shared_context", precision=prec)
+            got = {}
+            for on in (1, 0, 1):
+                lib.artab_set_dependent_launch(on)
+                ys = p.sample_sequence(c("xc"), c("yc"), c("xt"), variates=(c("expo"), c("normal"))).clone()
+                jd = p.evaluate_joint_density(c("xc"), c("yc"), c("xt"), c("yt")).clone()
+                torch.cuda.synchronize()
+                if not got:
+                    got = {"ys": ys, "ld": p.last_logdens.clone(), "jd": jd}
+                else:
+                    assert torch.equal(ys, got["ys"]) and torch.equal(jd, got["jd"])
+    finally:
+        lib.artab_set_dependent_launch(1)
+
+
 def test_sampler_density_equals_teacher_forcing_with_shifted_ar_index():
     """Round trip: the density the sampler assigned to its own draws equals the
     teacher-forced density of those draws when the AR-token index convention is
