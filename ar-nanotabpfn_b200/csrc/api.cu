@@ -4,6 +4,7 @@
 #include <cstdarg>
 #include <cstdio>
 #include <atomic>
+#include <cstdlib>
 #include <cstring>
 #include <vector>
 
@@ -36,7 +37,13 @@ static thread_local std::vector<ProfSlot>* g_prof_pool = nullptr;
 
 void count_launch() { ++g_launches; }
 
-static std::atomic<int> g_dependent_launch{1};
+// On unless the environment says ARTAB_DEPENDENT_LAUNCH=0 (profilers that replay single kernels
+// want plain launches) or artab_set_dependent_launch(0) is called.
+static int dependent_launch_default() {
+  const char* e = getenv("ARTAB_DEPENDENT_LAUNCH");
+  return !(e && e[0] == '0');
+}
+static std::atomic<int> g_dependent_launch{dependent_launch_default()};
 bool dependent_launch_enabled() { return g_dependent_launch.load(std::memory_order_relaxed) != 0; }
 
 void prof_begin(int kind, cudaStream_t s) {

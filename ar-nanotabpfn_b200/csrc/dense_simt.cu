@@ -31,14 +31,8 @@ __device__ __forceinline__ float gelu_erf(float v) { return 0.5f * v * (1.0f + e
 // consume slab by slab and hand ring slots back through "empty" mbarriers, so
 // no CTA-wide barrier sits between slabs.
 // ---------------------------------------------------------------------------
-#ifndef ARTAB_NBUF
-#define ARTAB_NBUF 6
-#endif
-#ifndef ARTAB_BUFBYTES
-#define ARTAB_BUFBYTES 24576
-#endif
-constexpr int kNBuf = ARTAB_NBUF;
-constexpr int kBufBytes = ARTAB_BUFBYTES;
+constexpr int kNBuf = 6;
+constexpr int kBufBytes = 24576;
 constexpr long long kWaitCycles = 2000000000LL;
 
 struct Stream {
@@ -146,9 +140,7 @@ __device__ __noinline__ void gemm_body(Chain& ch, int K, int N, int ksplit, int 
 
   for (int k0 = 0; k0 < K; k0 += kc) {
     const int buf = consumed % kNBuf;
-#ifndef EXP_NOWAIT
     mbar_wait(&ch.st->full[buf], (consumed / kNBuf) & 1, &ch.st->abort_flag);
-#endif
     const int rows = min(kc, K - k0);
     const int per = rows / ksplit;  // rows of this slab handled by one k-group
     if (active) {
@@ -341,9 +333,6 @@ __global__ void __launch_bounds__(288) dense_chain_kernel(const DenseArgs a) {
 
   if ((int)threadIdx.x >= T) {
     // ------------------------------ producer warp ------------------------------
-#ifdef EXP_NOWAIT
-    return;
-#endif
     if (threadIdx.x == T) {
       int issued = 0;
       bool ok = true;

@@ -150,14 +150,6 @@ __device__ __forceinline__ float gelu_fast(float x) {
   return fmaf(copysignf(1.0f - e, x), h, h);  // 0.5 x (1 + erf)
 }
 
-#ifdef DENSE_TC_TIMING
-__device__ long long g_dbg[64];
-#define TSTAMP(i) do { if (blockIdx.x == 0 && threadIdx.x == 64) g_dbg[i] = clock64(); } while (0)
-#define MSTAMP(i) do { if (blockIdx.x == 0) g_dbg[i] = clock64(); } while (0)
-#else
-#define TSTAMP(i)
-#define MSTAMP(i)
-#endif
 
 struct __align__(1024) Smem {
   uint8_t ring[2][NSLOT][192 * 128];  // two weight rings (first / second MLP GEMM), slabs <= d_model * 128 bytes
@@ -420,18 +412,15 @@ struct Epilogue {
   }
   // hidden tile j: act(ACC_H + bias) -> split -> swizzled shared-memory operand
   __device__ void hidden_tile(int j, const float* bias) {
-    if (j == 3) TSTAMP(40);
     ok = mbar_wait(&sm->h_full, h_count & 1, &sm->abort_flag) && ok;
     ++h_count;
     tc_fence_after();
-    if (j == 3) TSTAMP(41);
     uint32_t r[2][16];
 #pragma unroll
     for (int c = 0; c < 2; ++c) tmem_ld16(t_row + kAccH + HPART * wg + 16 * c, r[c]);
     tmem_wait_ld();
     tc_fence_before();
     mbar_arrive(&sm->acch_free);  // the accumulator is in registers: the next tile's GEMM may overwrite it
-    if (j == 3) TSTAMP(42);
     uint32_t hi[16], lo[16];
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
@@ -440,12 +429,10 @@ struct Epilogue {
       const float x1 = gelu_fast(__uint_as_float(r[i >> 3][(2 * i + 1) & 15]) + bb.y);
       split2(x0, x1, hi[i], lo[i]);
     }
-    if (j == 3) TSTAMP(43);
     if (j >= 1) {  // the previous tile's second GEMM must have finished reading the operand buffer
       ok = mbar_wait(&sm->ah_free, free_count & 1, &sm->abort_flag) && ok;
       ++free_count;
     }
-    if (j == 3) TSTAMP(44);
     // this thread's 32 hidden columns sit in k-chunk wg / 2, 16-byte chunks 4 * (wg % 2) .. + 3 of the
     // 128-byte row; chunk c of row r lives at chunk position c ^ (r % 8)
     uint8_t* base_hi = sm->ah[0][wg >> 1] + row * 128;
@@ -459,7 +446,6 @@ struct Epilogue {
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic writes -> visible to the MMA's reads
     tc_fence_before();
     mbar_arrive(&sm->ah_ready);
-    if (j == 3) TSTAMP(45);
   }
   // After an MLP: consume the ah_free completion of its last tile, which no hidden_tile waited for,
   // so that the parity bookkeeping is exact when a second MLP runs in the same launch.
@@ -684,30 +670,23 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const DenseArgs a
     dep_trigger();
     if (a.do_post) {
       load_lm(a.attn);
-      TSTAMP(1);
       e.publish_ax(v);
       load_lm(a.x1_in);                          // residual
-      TSTAMP(2);
       e.wait_acc();
-      TSTAMP(3);
       e.add_acc(v);
       e.layer_norm(v, sm->vec[0], sm->vec[1]);   // v = x2
-      TSTAMP(4);
       e.publish_ax(v);
       // x2 is the residual of the last LayerNorm; it waits in this thread's own slice of the x1
       // workspace (free until the next layer writes it) so that the MLP epilogue has the registers
       store_lm(a.x1_out);
-      TSTAMP(5);
-      for (int j = 0; j < nt; ++j) { e.hidden_tile(j, sm->bias_h); TSTAMP(6 + j); }
+      for (int j = 0; j < nt; ++j) e.hidden_tile(j, sm->bias_h);
       load_lm(a.x1_out);
       e.wait_acc();
-      TSTAMP(20);
       e.drain_free();
 #pragma unroll
       for (int i = 0; i < PART; ++i) v[i] += sm->vec[2][e.col0 + i];
       e.add_acc(v);
       e.layer_norm(v, sm->vec[3], sm->vec[4]);   // v = x3
-      TSTAMP(21);
       if (a.x_out) store_row(a.x_out);
     } else {
       load_row(a.x_in);
@@ -736,14 +715,11 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const DenseArgs a
       }
     } else if (a.do_pre) {
       e.publish_ax(v);
-      TSTAMP(22);
       e.wait_acc();
-      TSTAMP(23);
       e.add_acc(v);
       e.layer_norm(v, sm->vec[5], sm->vec[6]);     // v = x1
       store_lm(a.x1_out);
       e.publish_ax(v);
-      TSTAMP(24);
       // q, k, v projections, one accumulator round each.  Destinations of this row's K / V are
       // resolved once (no per-element division): context cache rows during prefill, the private
       // buffer slot (in-place append) otherwise.
@@ -852,7 +828,6 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const DenseArgs a
             }
           }
         }
-        TSTAMP(25 + t);
       }
     }
     if (!e.ok && threadIdx.x == 64 && a.status) atomicExch(a.status, 3);
@@ -868,11 +843,6 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const DenseArgs a
 
 }  // namespace
 
-#ifdef DENSE_TC_TIMING
-extern "C" ARTAB_API int artab_debug_read(long long* out) {
-  return (int)cudaMemcpyFromSymbol(out, g_dbg, sizeof(long long) * 64);
-}
-#endif
 
 bool dense_tc_applicable(const DenseArgs& a) {
   if (a.kv.dtype != ARTAB_BF16) return false;

@@ -3,6 +3,7 @@
     python ar-nanotabpfn_b200/microbench.py ctx     [--streams 1024 --heads 4 --ctx 4096 --lq 1 --splits 0]
     python ar-nanotabpfn_b200/microbench.py buffer  [--streams 1024 --heads 4 --len 63 --uniform]
     python ar-nanotabpfn_b200/microbench.py append  [--streams 4096 --heads 6 --max-buf 256]
+    python ar-nanotabpfn_b200/microbench.py chain   [--streams 512 --ctx 1024 --targets 8]
 
 ``ctx`` is the shared-context decode-attention micro-benchmark: bf16, head_dim 32,
 every stream carries ``lq`` queries against one shared context K/V ~ N(0,1); the
@@ -10,7 +11,9 @@ tcgen05 context contraction is timed alone.  ``buffer`` times the warp-level pas
 over the private buffer K/V with the log-sum-exp merge (per-stream lengths are
 uniform in [0, len] with --uniform, the kernel is launched once per distinct
 length group otherwise all streams use ``len``).  ``append`` times the in-place
-K/V append.  Inputs are larger than L2 where the kernel is bandwidth bound, or an
+K/V append.  ``chain`` runs a short shared-context sampling job (6 layers, d_model 192,
+6 heads, d_ff 768, bf16 mode) and reports the serialised per-launch time of every kernel
+kind, the per-token dense chain among them.  Inputs are larger than L2 where the kernel is bandwidth bound, or an
 L2-sized buffer is written between iterations.
 """
 from __future__ import annotations
@@ -167,9 +170,45 @@ def bench_append(a):
                       "gbs": byts / (ms * 1e-3) / 1e9, "peak_gbs": peak}), flush=True)
 
 
+def bench_chain(a):
+    import ar_tabpfn
+    lib = _lib.lib()
+    dev = torch.device("cuda")
+    torch.manual_seed(0)
+    D, H, L, Dff, F = 192, 6, 6, 768, 20
+    model = ar_tabpfn.ARTabPFN(d_model=D, n_heads=H, n_layers=L, d_ff=Dff, num_features=F, buffer_size=8,
+                               num_components=5).eval().to(dev)
+    pred = ar_tabpfn.ARTabPFNPredictor.from_trained_model(model, backend="triton_shared_context", precision="bf16")
+    B, Nc, Nt = a.streams, a.ctx, a.targets
+    g = torch.Generator(device=dev).manual_seed(1)
+    xc = torch.randn(1, Nc, F, device=dev, generator=g).expand(B, -1, -1).contiguous()
+    yc = torch.randn(1, Nc, device=dev, generator=g).expand(B, -1).contiguous()
+    xt = torch.randn(B, Nt, F, device=dev, generator=g)
+    for _ in range(a.warmup):
+        pred.sample_sequence(xc, yc, xt)
+    torch.cuda.synchronize()
+    lib.artab_profile_enable(1)
+    for _ in range(a.iters):
+        pred.sample_sequence(xc, yc, xt)
+    torch.cuda.synchronize()
+    prof = _lib.profile_read()
+    lib.artab_profile_enable(0)
+    rows = 2 * B
+    flops = 2.0 * rows * (12.0 * D * D + 4.0 * D * Dff)   # 2 hi/lo passes over Wo, W1, W2, Wf, Wq|Wk|Wv
+    out = {"bench": "chain", "streams": B, "ctx": Nc, "targets": Nt, "status": int(pred._bufs["status"].item())}
+    for name, (ms, n) in prof.items():
+        if n:
+            out[name] = {"launches": int(n), "us_per_launch": 1e3 * ms / n}
+    d = out.get("dense_chain")
+    if d:
+        d["issued_tflops_decode_launch"] = flops / (d["us_per_launch"] * 1e-6) / 1e12
+    print(json.dumps(out), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("which", choices=["ctx", "buffer", "append"])
+    ap.add_argument("which", choices=["ctx", "buffer", "append", "chain"])
+    ap.add_argument("--targets", type=int, default=8)
     ap.add_argument("--streams", type=int, default=1024)
     ap.add_argument("--heads", type=int, default=4)
     ap.add_argument("--ctx", type=int, default=4096)
@@ -182,7 +221,7 @@ def main():
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     a = ap.parse_args()
-    {"ctx": bench_ctx, "buffer": bench_buffer, "append": bench_append}[a.which](a)
+    {"ctx": bench_ctx, "buffer": bench_buffer, "append": bench_append, "chain": bench_chain}[a.which](a)
 
 
 if __name__ == "__main__":

@@ -38,6 +38,9 @@ import torch  # noqa: E402
 
 CFG = dict(d_model=192, n_heads=6, n_layers=6, d_ff=768, num_features=20, buffer_size=8, num_components=5)
 NC, NT, STREAMS, SEED = 1024, 128, 512, 2
+# DRAM bytes (read + write) of one decode-step launch of the tensor-core dense chain at this
+# workload, from the ncu capture summarised in profiles/dense_tc_kernel_config3.md
+DENSE_TC_DRAM_BYTES_PER_LAUNCH = 2.873e6   # captured on a 512-row launch (4 CTAs); weight tiles dominate
 CPU_SAMPLE = dict(streams=128, targets=16)  # bounded CPU sample of the same workload
 
 
@@ -282,12 +285,19 @@ def main():
         rows_run = STREAMS * (1 + 2 * (NT - 1)) + NC          # token rows through the layer chain per call
         roof = None
         if dom == "dense_chain":
-            flops = rows_run * L * (12 * D * D + 4 * D * Dff) * 1.0
+            # algorithmic flops of the per-token chain: Wf (folded feature attention), Wq|Wk|Wv, Wo and
+            # the two MLP matrices, 2 flops per multiply-add; the hi/lo operand split that the bf16
+            # tensor-core chain issues (2x the MMAs) is not counted
+            flops = rows_run * L * (10 * D * D + 4 * D * Dff) * 1.0
             peak = peaks.get("bf16_tflops_sustained", 1400.0)
             ach = flops / (shares[dom]["ms"] * 1e-3) / 1e12
-            roof = {"kernel": "dense_chain_kernel", "bound": "tensor", "achieved": ach, "peak": peak,
-                    "unit": "TFLOP/s", "frac": ach / peak, "traffic": None,
-                    "note": "fp32 FMA kernel measured against the bf16 tensor peak"
+            tc = args.precision == "bf16"
+            roof = {"kernel": "dense_tc_kernel" if tc else "dense_chain_kernel", "bound": "tensor",
+                    "achieved": ach, "peak": peak, "unit": "TFLOP/s", "frac": ach / peak,
+                    "traffic": DENSE_TC_DRAM_BYTES_PER_LAUNCH if tc else None,
+                    "note": ("tcgen05 chain, 8 CTAs of 128 rows per decode launch: bound by the latency of "
+                             "the dependent GEMM/LayerNorm chain inside one CTA, not by the tensor pipe"
+                             if tc else "fp32 FMA kernel measured against the bf16 tensor peak")
                             + (" (of measured)" if peaks else " (of fallback)")}
         elif dom == "context_attention":
             q_rows = STREAMS * (1 + 2 * (NT - 1)) + NC

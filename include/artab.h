@@ -40,7 +40,7 @@ extern "C" {
 #define ARTAB_ECAPACITY (-2)  /* buffer cache or workspace too small         */
 #define ARTAB_ELAUNCH (-3)    /* CUDA reported an error at launch            */
 #define ARTAB_EDRIVER (-4)    /* driver entry point (tensor-map encode) missing */
-#define ARTAB_ETIMEOUT (-5)   /* a bounded device-side wait gave up (see artab_read_status) */
+#define ARTAB_ETIMEOUT (-5)   /* a bounded device-side wait gave up (artab_state.status is non-zero) */
 
 #define ARTAB_F32 0
 #define ARTAB_BF16 1
@@ -282,7 +282,9 @@ ARTAB_API int artab_profile_read(double* ms_per_kind, int64_t* launches_per_kind
  * chain are launched so that each may begin its set-up and weight prefetch while the kernel
  * before it in the stream drains, and the private-buffer pass runs beside the context
  * contraction; results are bit-identical either way.  Pass 0 to launch every kernel fully
- * serialised (diagnostics).  No counterpart in the reference. */
+ * serialised (diagnostics); the environment variable ARTAB_DEPENDENT_LAUNCH=0 sets that
+ * default at load time, for profilers that replay single kernels.  No counterpart in the
+ * reference. */
 ARTAB_API void artab_set_dependent_launch(int on);
 
 /* Kernels launched by this library on the calling thread since the last reset
