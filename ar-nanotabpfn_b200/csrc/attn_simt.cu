@@ -161,7 +161,7 @@ __device__ __forceinline__ float fast_exp2(float x) {  // MUFU ex2: relative err
 // holding one 16-byte slice of the K row and of the V row.
 // ---------------------------------------------------------------------------
 template <typename T, int DH>
-__global__ void __launch_bounds__(128) buf_merge_kernel(const BufMergeArgs a) {
+__global__ void __launch_bounds__(128, 6) buf_merge_kernel(const BufMergeArgs a) {
   constexpr int VEC = Vec16<T>::N;
   constexpr int LPK = DH / VEC;   // lanes per key
   constexpr int KPI = 32 / LPK;   // keys per warp iteration

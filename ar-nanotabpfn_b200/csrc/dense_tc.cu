@@ -387,7 +387,8 @@ struct Epilogue {
     const int ph = xs_phase & 1;
     ++xs_phase;
     sm->xs[ph][wg][row] = part;
-    sync_groups();
+    // only the four warps that own this row quadrant (one per column group) need to meet
+    asm volatile("bar.sync %0, 128;" ::"r"(4 + (row >> 5)) : "memory");
     float tot = 0.f;
 #pragma unroll
     for (int g = 0; g < NWG; ++g) tot += sm->xs[ph][g][row];

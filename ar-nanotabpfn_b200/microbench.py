@@ -4,6 +4,8 @@
     python ar-nanotabpfn_b200/microbench.py buffer  [--streams 1024 --heads 4 --len 63 --uniform]
     python ar-nanotabpfn_b200/microbench.py append  [--streams 4096 --heads 6 --max-buf 256]
     python ar-nanotabpfn_b200/microbench.py chain   [--streams 512 --ctx 1024 --targets 8]
+    python ar-nanotabpfn_b200/microbench.py config4 [--datasets 64 --ctx 2048 --targets 256]
+    python ar-nanotabpfn_b200/microbench.py config5 [--streams 4096 --ctx 16384 --targets 256]
 
 ``ctx`` is the shared-context decode-attention micro-benchmark: bf16, head_dim 32,
 every stream carries ``lq`` queries against one shared context K/V ~ N(0,1); the
@@ -13,7 +15,10 @@ uniform in [0, len] with --uniform, the kernel is launched once per distinct
 length group otherwise all streams use ``len``).  ``append`` times the in-place
 K/V append.  ``chain`` runs a short shared-context sampling job (6 layers, d_model 192,
 6 heads, d_ff 768, bf16 mode) and reports the serialised per-launch time of every kernel
-kind, the per-token dense chain among them.  Inputs are larger than L2 where the kernel is bandwidth bound, or an
+kind, the per-token dense chain among them.  ``config4`` times the teacher-forced joint
+log-density of independent datasets (one context per dataset, "flex_attention" semantics);
+``config5`` times the scale-out sampling job (100 features, long shared context; under
+torchrun the streams are split over the ranks and the results all-gathered).  Inputs are larger than L2 where the kernel is bandwidth bound, or an
 L2-sized buffer is written between iterations.
 """
 from __future__ import annotations
@@ -205,13 +210,125 @@ def bench_chain(a):
     print(json.dumps(out), flush=True)
 
 
+def _model(num_features, seed, dev):
+    import ar_tabpfn
+    torch.manual_seed(seed)
+    m = ar_tabpfn.ARTabPFN(d_model=192, n_heads=6, n_layers=6, d_ff=768, num_features=num_features, buffer_size=8,
+                           num_components=5).eval()
+    with torch.no_grad():
+        for mod in m.modules():
+            if isinstance(mod, torch.nn.Linear):
+                torch.nn.init.xavier_uniform_(mod.weight)
+        for p in m.parameters():
+            p.copy_(p.to(torch.bfloat16).float())
+    return m.to(dev)
+
+
+def _dataset(g, n_rows, n_feat, hidden, noise, product_frac=0.0):
+    """x ~ N(0,1) (optionally a fraction of columns replaced by products of two others),
+    standardised; y = tanh-MLP(F -> hidden -> hidden -> 1) + N(0, noise^2)."""
+    x = torch.randn(n_rows, n_feat, generator=g)
+    n_prod = int(product_frac * n_feat)
+    for j in range(n_prod):
+        a, b = torch.randint(n_prod, n_feat, (2,), generator=g).tolist()
+        x[:, j] = x[:, a] * x[:, b]
+    x = (x - x.mean(0)) / x.std(0)
+    w1 = torch.randn(n_feat, hidden, generator=g) / n_feat ** 0.5
+    w2 = torch.randn(hidden, hidden, generator=g) / hidden ** 0.5
+    w3 = torch.randn(hidden, 1, generator=g) / hidden ** 0.5
+    y = (torch.tanh(torch.tanh(x @ w1) @ w2) @ w3)[:, 0] + noise * torch.randn(n_rows, generator=g)
+    return x, y
+
+
+def _event_time(fn, iters, warmup):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record()
+    for _ in range(iters):
+        fn()
+    e.record()
+    torch.cuda.synchronize()
+    return s.elapsed_time(e) / iters
+
+
+def bench_config4(a):
+    import ar_tabpfn
+    dev = torch.device("cuda")
+    model = _model(20, 3, dev)
+    pred = ar_tabpfn.ARTabPFNPredictor.from_trained_model(model, backend="flex_attention", precision=a.dtype)
+    g = torch.Generator().manual_seed(3)
+    B, Nc, Nt = a.datasets, a.ctx, a.targets
+    xs, ys = zip(*[_dataset(g, Nc + Nt, 20, 32, 0.1) for _ in range(B)])
+    x, y = torch.stack(xs).to(dev), torch.stack(ys).to(dev)
+    xc, yc, xt, yt = x[:, :Nc].contiguous(), y[:, :Nc].contiguous(), x[:, Nc:].contiguous(), y[:, Nc:].contiguous()
+    out = {}
+
+    def fn():
+        out["ld"] = pred.evaluate_joint_density(xc, yc, xt, yt)
+
+    ms = _event_time(fn, a.iters, a.warmup)
+    ld = out["ld"]
+    print(json.dumps({"bench": "config4", "datasets": B, "ctx": Nc, "targets": Nt, "precision": a.dtype, "ms": ms,
+                      "targets_per_s": B * Nt / (ms * 1e-3), "mean_logdens": float(ld.mean()),
+                      "finite": bool(torch.isfinite(ld).all()), "status": int(pred._bufs["status"].item())}),
+          flush=True)
+
+
+def bench_config5(a):
+    import torch.distributed as dist
+    import ar_tabpfn
+    world, rank = int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    model = _model(100, 4, dev)
+    pred = ar_tabpfn.ARTabPFNPredictor.from_trained_model(model, backend="triton_shared_context", precision=a.dtype)
+    g = torch.Generator().manual_seed(4)
+    B, Nc, Nt = a.streams // world, a.ctx, a.targets
+    x, y = _dataset(g, Nc + Nt, 100, 64, 0.05, product_frac=0.2)
+    x, y = x.to(dev), y.to(dev)
+    xc, yc = x[:Nc].expand(B, -1, -1), y[:Nc].expand(B, -1)   # shared context: only stream 0's copy is read
+    xt = x[Nc:].expand(B, -1, -1).contiguous()
+    gd = torch.Generator(device=dev).manual_seed(4)
+    expo = torch.empty(Nt, a.streams, 5, device=dev).exponential_(1.0, generator=gd)
+    normal = torch.randn(Nt, a.streams, device=dev, generator=gd)
+    var = (expo[:, rank * B:(rank + 1) * B].contiguous(), normal[:, rank * B:(rank + 1) * B].contiguous())
+    gathered = [torch.empty(world * B, Nt, device=dev) for _ in range(2)] if world > 1 else None
+    out = {}
+
+    def fn():
+        ys = pred.sample_sequence(xc, yc, xt, variates=var)
+        if world > 1:
+            dist.all_gather_into_tensor(gathered[0], ys.contiguous())
+            dist.all_gather_into_tensor(gathered[1], pred.last_logdens.contiguous())
+        out["ys"] = ys
+
+    ms = torch.tensor([_event_time(fn, a.iters, a.warmup)], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    if rank == 0:
+        ys, ld = out["ys"], pred.last_logdens
+        print(json.dumps({"bench": "config5", "n_gpus": world, "streams": a.streams, "ctx": Nc, "targets": Nt,
+                          "precision": a.dtype, "ms": float(ms), "targets_per_s": a.streams * Nt / (float(ms) * 1e-3),
+                          "scaling": "strong", "finite": bool(torch.isfinite(ys).all() and torch.isfinite(ld).all()),
+                          "mean_logdens": float(ld.mean()), "status": int(pred._bufs["status"].item())}), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("which", choices=["ctx", "buffer", "append", "chain"])
-    ap.add_argument("--targets", type=int, default=8)
-    ap.add_argument("--streams", type=int, default=1024)
+    ap.add_argument("which", choices=["ctx", "buffer", "append", "chain", "config4", "config5"])
+    ap.add_argument("--datasets", type=int, default=64)
+    ap.add_argument("--targets", type=int, default=None)
+    ap.add_argument("--streams", type=int, default=None)
     ap.add_argument("--heads", type=int, default=4)
-    ap.add_argument("--ctx", type=int, default=4096)
+    ap.add_argument("--ctx", type=int, default=None)
     ap.add_argument("--lq", type=int, default=1)
     ap.add_argument("--splits", type=int, default=0)
     ap.add_argument("--len", type=int, default=63)
@@ -221,7 +338,14 @@ def main():
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     a = ap.parse_args()
-    {"ctx": bench_ctx, "buffer": bench_buffer, "append": bench_append, "chain": bench_chain}[a.which](a)
+    defaults = {"ctx": dict(streams=1024, ctx=4096), "buffer": dict(streams=1024), "append": dict(streams=4096),
+                "chain": dict(streams=512, ctx=1024, targets=8), "config4": dict(ctx=2048, targets=256),
+                "config5": dict(streams=4096, ctx=16384, targets=256)}[a.which]
+    for k, v in defaults.items():
+        if getattr(a, k) is None:
+            setattr(a, k, v)
+    {"ctx": bench_ctx, "buffer": bench_buffer, "append": bench_append, "chain": bench_chain,
+     "config4": bench_config4, "config5": bench_config5}[a.which](a)
 
 
 if __name__ == "__main__":
