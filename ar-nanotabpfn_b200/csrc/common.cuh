@@ -32,20 +32,38 @@ __device__ __forceinline__ void dep_trigger() { asm volatile("griddepcontrol.lau
 
 bool dependent_launch_enabled();
 
+// cluster_x > 1 launches thread-block clusters of that many CTAs along x (grid.x a multiple of it).
 template <typename... P, typename... A>
-inline cudaError_t launch_dependent(void (*kernel)(P...), dim3 grid, dim3 block, size_t smem, cudaStream_t s,
-                                    A&&... args) {
+inline cudaError_t launch_dependent_cluster(void (*kernel)(P...), dim3 grid, dim3 block, size_t smem, cudaStream_t s,
+                                            unsigned cluster_x, A&&... args) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
   cfg.blockDim = block;
   cfg.dynamicSmemBytes = smem;
   cfg.stream = s;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchAttribute attr[2];
+  unsigned n = 0;
+  if (dependent_launch_enabled()) {
+    attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[n].val.programmaticStreamSerializationAllowed = 1;
+    ++n;
+  }
+  if (cluster_x > 1) {
+    attr[n].id = cudaLaunchAttributeClusterDimension;
+    attr[n].val.clusterDim.x = cluster_x;
+    attr[n].val.clusterDim.y = 1;
+    attr[n].val.clusterDim.z = 1;
+    ++n;
+  }
   cfg.attrs = attr;
-  cfg.numAttrs = dependent_launch_enabled() ? 1 : 0;
+  cfg.numAttrs = n;
   return cudaLaunchKernelEx(&cfg, kernel, static_cast<P>(args)...);
+}
+
+template <typename... P, typename... A>
+inline cudaError_t launch_dependent(void (*kernel)(P...), dim3 grid, dim3 block, size_t smem, cudaStream_t s,
+                                    A&&... args) {
+  return launch_dependent_cluster(kernel, grid, block, smem, s, 1u, static_cast<A&&>(args)...);
 }
 
 #define ARTAB_REQUIRE(cond, code, ...) \

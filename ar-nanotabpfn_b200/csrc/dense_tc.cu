@@ -18,6 +18,8 @@
 // columns); LayerNorm statistics are exchanged through shared memory.
 // All mbarrier waits are bounded; on expiry the CTA flags an abort, stops
 // producing results, drains and frees TMEM.
+#include <cstdlib>
+
 #include "dense.cuh"
 #include "kv_scatter.cuh"
 
@@ -37,6 +39,7 @@ constexpr uint32_t kAxHi = 192;  // activation operand, hi part (<= 96 packed co
 constexpr uint32_t kAxLo = 288;  // activation operand, lo part
 constexpr uint32_t kAccH = 384;  // hidden-tile accumulator, 128 columns
 constexpr long long kWaitCycles = 2000000000LL;
+constexpr int kPairMaxCtas = 148;  // CTA pairs only while all of them fit on the GPU at once
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void mbar_init(uint64_t* b, uint32_t count) {
@@ -67,6 +70,57 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* b, uint32_t parity, volatile
       return false;
     }
   }
+}
+
+// mbarrier wait that also acquires what another CTA of the cluster released before its remote arrive
+__device__ __forceinline__ bool mbar_try_cluster(uint64_t* b, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(b)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_cluster(uint64_t* b, uint32_t parity, volatile int* abort_flag) {
+  const long long t0 = clock64();
+  for (;;) {
+    if (mbar_try_cluster(b, parity)) return true;
+    if (*abort_flag) return false;
+    if (clock64() - t0 > kWaitCycles) {
+      *abort_flag = 1;
+      return false;
+    }
+  }
+}
+// ---- thread-block cluster (a pair of CTAs shares one 128-row tile) ----
+__device__ __forceinline__ uint32_t cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t cluster_size() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// shared-memory address of the same object in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t map_to_rank(uint32_t saddr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(saddr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void st_remote_f4(uint32_t raddr, float x, float y, float z, float w) {
+  asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(raddr), "f"(x), "f"(y), "f"(z), "f"(w)
+               : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_remote(uint32_t raddr) {  // releases this thread's earlier stores
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(raddr) : "memory");
 }
 
 constexpr uint64_t kLayoutSw128 = 2;
@@ -160,6 +214,10 @@ struct __align__(1024) Smem {
   __nv_bfloat16* rowdst[BM];          // private-buffer K slot of each row's token (null: not cached)
   uint64_t w_full[2][NSLOT], w_empty[2][NSLOT];
   uint64_t ep_done, acc_full, h_full, acch_free, ah_ready, ah_free;
+  // CTA-pair exchange of the MLP partial sums: x_ready = the peer's exchange buffer may be written,
+  // x_full = the peer's partial has landed in ours, xchg_done = our threads have consumed it
+  uint64_t x_ready, x_full, xchg_done;
+  uint64_t in_done;  // the peer has read its inputs (its residual input aliases our parking buffer)
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -200,16 +258,25 @@ struct Producer {
     for (int i = 0; i < n; ++i) slab(p + (size_t)i * slab_bytes, slab_bytes);
   }
   // first GEMM of an MLP: per 128-wide hidden tile nkc slabs of 16 KB per part
-  __device__ void mlp_first(const void* w1, bool lo1, int nkc, int nt) {
+  // (hidden tiles first, first + step, ... < nt: a CTA pair shares the tiles of one MLP)
+  __device__ void mlp_first(const void* w1, bool lo1, int nkc, int nt, int first, int step) {
     const uint8_t* p = reinterpret_cast<const uint8_t*>(w1);
-    const int n = nt * nkc * (lo1 ? 2 : 1);  // tile-major: hi k-chunks then lo k-chunks of every tile
-    for (int i = 0; i < n; ++i) slab(p + (size_t)i * (HT * 128), HT * 128);
+    const int per = nkc * (lo1 ? 2 : 1);  // tile-major: hi k-chunks then lo k-chunks of every tile
+    for (int j = first; j < nt; j += step)
+      for (int i = 0; i < per; ++i) slab(p + (size_t)(j * per + i) * (HT * 128), HT * 128);
   }
   // second GEMM of an MLP: per hidden tile two k-chunk slabs per part
-  __device__ void mlp_second(const void* w2, bool lo2, uint32_t bytes2, int nt) {
+  __device__ void mlp_second(const void* w2, bool lo2, uint32_t bytes2, int nt, int first, int step) {
     const uint8_t* p = reinterpret_cast<const uint8_t*>(w2);
-    const int n = nt * 2 * (lo2 ? 2 : 1);
-    for (int i = 0; i < n; ++i) slab(p + (size_t)i * bytes2, bytes2);
+    const int per = 2 * (lo2 ? 2 : 1);
+    for (int j = first; j < nt; j += step)
+      for (int i = 0; i < per; ++i) slab(p + (size_t)(j * per + i) * bytes2, bytes2);
+  }
+  // k-chunk groups [g0, g1) of a "full" matrix stack
+  __device__ void matrix_range(const void* w, int g0, int g1, bool has_lo, uint32_t slab_bytes) {
+    const uint8_t* p = reinterpret_cast<const uint8_t*>(w);
+    const int per = has_lo ? 2 : 1;
+    for (int i = g0 * per; i < g1 * per; ++i) slab(p + (size_t)i * slab_bytes, slab_bytes);
   }
 };
 
@@ -412,7 +479,8 @@ struct Epilogue {
     for (int i = 0; i < PART; ++i) v[i] = (v[i] - mean) * rstd * gamma[col0 + i] + beta[col0 + i];
   }
   // hidden tile j: act(ACC_H + bias) -> split -> swizzled shared-memory operand
-  __device__ void hidden_tile(int j, const float* bias) {
+  // (jl counts this CTA's tiles, j is the tile's index in the MLP)
+  __device__ void hidden_tile(int jl, int j, const float* bias) {
     ok = mbar_wait(&sm->h_full, h_count & 1, &sm->abort_flag) && ok;
     ++h_count;
     tc_fence_after();
@@ -430,7 +498,7 @@ struct Epilogue {
       const float x1 = gelu_fast(__uint_as_float(r[i >> 3][(2 * i + 1) & 15]) + bb.y);
       split2(x0, x1, hi[i], lo[i]);
     }
-    if (j >= 1) {  // the previous tile's second GEMM must have finished reading the operand buffer
+    if (jl >= 1) {  // the previous tile's second GEMM must have finished reading the operand buffer
       ok = mbar_wait(&sm->ah_free, free_count & 1, &sm->abort_flag) && ok;
       ++free_count;
     }
@@ -453,6 +521,44 @@ struct Epilogue {
   __device__ void drain_free() {
     ok = mbar_wait(&sm->ah_free, free_count & 1, &sm->abort_flag) && ok;
     ++free_count;
+  }
+  // CTA pair: v[i] += (own MLP partial + the peer's).  Each CTA holds the second GEMM's sum over its
+  // half of the hidden tiles in ACC_A.  The partials cross through distributed shared memory: the
+  // second weight ring and the hidden-operand buffer, idle once the MLP's MMAs have completed, form
+  // the 96 KB landing zone [column group of 4][128 rows] float4.  a + b == b + a exactly, so both
+  // CTAs end up with the same bits.  Called after wait_acc() (this CTA's MLP MMAs have completed).
+  __device__ void exchange_add(float* v, uint32_t peer) {
+    float4* xbuf = reinterpret_cast<float4*>(&sm->ring[1][0][0]);
+    static_assert(sizeof(Smem::ring) / 2 + sizeof(Smem::ah) >= (size_t)BM * D * 4, "exchange buffer too small");
+    if (wg == 0 && row == 0) mbar_arrive_remote(map_to_rank(smem_u32(&sm->x_ready), peer));  // our zone is free
+    ok = mbar_wait_cluster(&sm->x_ready, 0, &sm->abort_flag) && ok;                         // the peer's is
+    const uint32_t remote = map_to_rank(smem_u32(xbuf), peer);
+    uint32_t r[16];
+#pragma unroll
+    for (int c = 0; c < NCH; ++c) {
+      tmem_ld16(t_row + kAccA + col0 + 16 * c, r);
+      tmem_wait_ld();
+#pragma unroll
+      for (int q = 0; q < 4; ++q)
+        st_remote_f4(remote + (uint32_t)((((col0 + 16 * c) >> 2) + q) * BM + row) * 16, __uint_as_float(r[4 * q]),
+                     __uint_as_float(r[4 * q + 1]), __uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3]));
+    }
+    mbar_arrive_remote(map_to_rank(smem_u32(&sm->x_full), peer));
+    ok = mbar_wait_cluster(&sm->x_full, 0, &sm->abort_flag) && ok;
+#pragma unroll
+    for (int c = 0; c < NCH; ++c) {
+      tmem_ld16(t_row + kAccA + col0 + 16 * c, r);
+      tmem_wait_ld();
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const float4 t = xbuf[(((col0 + 16 * c) >> 2) + q) * BM + row];
+        v[16 * c + 4 * q] += __uint_as_float(r[4 * q]) + t.x;
+        v[16 * c + 4 * q + 1] += __uint_as_float(r[4 * q + 1]) + t.y;
+        v[16 * c + 4 * q + 2] += __uint_as_float(r[4 * q + 2]) + t.z;
+        v[16 * c + 4 * q + 3] += __uint_as_float(r[4 * q + 3]) + t.w;
+      }
+    }
+    mbar_arrive(&sm->xchg_done);
   }
 };
 
@@ -514,7 +620,13 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const DenseArgs a
   constexpr int NKC = D / 64;
   constexpr uint32_t kSlab = D * 128;
   const int nt = a.Dff / HT;
-  const long row0 = (long)blockIdx.x * BM;
+  // A CTA pair (cluster of 2) may share one row tile: both walk the whole chain, but each takes
+  // every other hidden tile of the layer's MLP (partial sums exchanged once) and a part of the
+  // Q / K / V projections.  csize == 1: one CTA does everything.
+  const uint32_t crank = cluster_rank(), csize = cluster_size();
+  const long row0 = (long)(blockIdx.x / csize) * BM;
+  const int t_begin = (csize == 2 && crank == 1) ? 2 : 0;   // projections (0 q, 1 k, 2 v) of this CTA
+  const int t_end = (csize == 2 && crank == 0) ? 2 : 3;
 
   if (threadIdx.x == 0) {
     for (int r = 0; r < 2; ++r)
@@ -528,6 +640,10 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const DenseArgs a
     mbar_init(&sm->acch_free, kEpi);
     mbar_init(&sm->ah_ready, kEpi);
     mbar_init(&sm->ah_free, 1);
+    mbar_init(&sm->x_ready, 1);
+    mbar_init(&sm->x_full, kEpi);
+    mbar_init(&sm->xchg_done, kEpi);
+    mbar_init(&sm->in_done, kEpi / 32);
     sm->abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -559,9 +675,11 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const DenseArgs a
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  if (csize > 1) cluster_sync_all();  // the peer's barriers exist before anyone arrives on them
   const uint32_t tmem = sm->tmem_base;
 
   const int lo_post = a.post_w.tc_lo, lo_pre = a.pre_w.tc_lo;
+  const int n_mine = (nt - (int)crank + (int)csize - 1) / (int)csize;  // hidden tiles of the layer MLP done here
 
   if (warp == 0) {
     // --------------------- weight producer A: everything but the second MLP GEMM ---------------------
@@ -569,21 +687,25 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const DenseArgs a
       Producer p{sm, 0, 0, true};
       if (a.do_post) {
         p.matrix(a.post_w.tc_wo, NKC, lo_post & 1, kSlab);
-        p.mlp_first(a.post_w.tc_w1, lo_post & 2, NKC, nt);
+        p.mlp_first(a.post_w.tc_w1, lo_post & 2, NKC, nt, crank, csize);
       }
       if (a.do_head) {
-        p.mlp_first(a.tc_wa, a.tc_head_lo & 1, NKC, nt);
+        p.mlp_first(a.tc_wa, a.tc_head_lo & 1, NKC, nt, 0, 1);
       } else if (a.do_pre) {
         p.matrix(a.pre_w.tc_wf, NKC, lo_pre & 8, kSlab);
-        p.matrix(a.pre_w.tc_wqkv, 3 * NKC, lo_pre & 16, kSlab);
+        p.matrix_range(a.pre_w.tc_wqkv, t_begin * NKC, t_end * NKC, lo_pre & 16, kSlab);
       }
     }
   } else if (warp == 19) {
     // --------------------- weight producer B: the second MLP GEMM's k-chunks ---------------------
     if (lane == 0) {
       Producer p{sm, 1, 0, true};
-      if (a.do_post) p.mlp_second(a.post_w.tc_w2, lo_post & 4, kSlab, nt);
-      if (a.do_head) p.mlp_second(a.tc_wb, a.tc_head_lo & 2, 16 * 128, nt);
+      if (a.do_post) p.mlp_second(a.post_w.tc_w2, lo_post & 4, kSlab, nt, crank, csize);
+      if (a.do_head) {
+        // this ring is part of the pair's exchange zone until the epilogue has consumed the partials
+        if (a.do_post && csize > 1) p.ok = mbar_wait(&sm->xchg_done, 0, &sm->abort_flag) && p.ok;
+        p.mlp_second(a.tc_wb, a.tc_head_lo & 2, 16 * 128, nt, 0, 1);
+      }
     }
   } else if (warp == 1) {
     // --------------------------------- MMA issuer A ---------------------------------
@@ -594,7 +716,7 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const DenseArgs a
         m.gemm_full_ts(kAccA, D, NKC, lo_post & 1);
         umma_commit(&sm->acc_full);
         m.wait_epilogue();                               // A_x = x2 (and ACC_A drained)
-        m.mlp_first(NKC, lo_post & 2, nt);
+        m.mlp_first(NKC, lo_post & 2, n_mine);
       }
       if (a.do_head) {
         m.wait_epilogue();                               // A_x = z
@@ -604,8 +726,8 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const DenseArgs a
         m.gemm_full_ts(kAccA, D, NKC, lo_pre & 8);
         umma_commit(&sm->acc_full);
         m.wait_epilogue();                               // A_x = x1
-        for (int t = 0; t < 3; ++t) {
-          if (t > 0) m.wait_epilogue();                  // previous projection drained from ACC_A
+        for (int t = t_begin; t < t_end; ++t) {
+          if (t > t_begin) m.wait_epilogue();            // previous projection drained from ACC_A
           m.gemm_full_ts(kAccA, D, NKC, lo_pre & 16);
           umma_commit(&sm->acc_full);
         }
@@ -615,7 +737,7 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const DenseArgs a
     // --------------------------------- MMA issuer B ---------------------------------
     if (lane == 0) {
       Issuer m{sm, tmem, 1, 0, 0, 0, 0, true};
-      if (a.do_post) m.mlp_second(lo_post & 4, nt, D);
+      if (a.do_post) m.mlp_second(lo_post & 4, n_mine, D);
       if (a.do_head) m.mlp_second(a.tc_head_lo & 2, nt, 16);
     }
   } else {
@@ -678,23 +800,36 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const DenseArgs a
       e.layer_norm(v, sm->vec[0], sm->vec[1]);   // v = x2
       e.publish_ax(v);
       // x2 is the residual of the last LayerNorm; it waits in this thread's own slice of the x1
-      // workspace (free until the next layer writes it) so that the MLP epilogue has the registers
+      // workspace (free until the next layer writes it) so that the MLP epilogue has the registers.
+      // In a CTA pair the peer parks the same values at the same place, which is also where both
+      // read their residual input: park only once the peer has consumed its inputs.
+      if (csize > 1) {
+        __syncwarp();
+        if (lane == 0) mbar_arrive_remote(map_to_rank(smem_u32(&sm->in_done), crank ^ 1u));
+        e.ok = mbar_wait_cluster(&sm->in_done, 0, &sm->abort_flag) && e.ok;
+      }
       store_lm(a.x1_out);
-      for (int j = 0; j < nt; ++j) e.hidden_tile(j, sm->bias_h);
+      {
+        int jl = 0;
+        for (int j = crank; j < nt; j += csize, ++jl) e.hidden_tile(jl, j, sm->bias_h);
+      }
       load_lm(a.x1_out);
       e.wait_acc();
       e.drain_free();
 #pragma unroll
       for (int i = 0; i < PART; ++i) v[i] += sm->vec[2][e.col0 + i];
-      e.add_acc(v);
+      if (csize > 1)
+        e.exchange_add(v, crank ^ 1u);
+      else
+        e.add_acc(v);
       e.layer_norm(v, sm->vec[3], sm->vec[4]);   // v = x3
-      if (a.x_out) store_row(a.x_out);
+      if (a.x_out && crank == 0) store_row(a.x_out);
     } else {
       load_row(a.x_in);
     }
     if (a.do_final) {
       e.layer_norm(v, sm->vec[5], sm->vec[6]);                 // v = z
-      if (a.z_out) store_row(a.z_out);
+      if (a.z_out && crank == 0) store_row(a.z_out);
     }
     if (a.do_head) {
       // the hidden bias buffer now takes the head's first-layer bias (every thread is past the MLP)
@@ -702,7 +837,7 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const DenseArgs a
       for (int i = threadIdx.x - 64; i < a.Dff; i += kEpi) sm->bias_h[i] = a.ba[i];
       e.sync_groups();
       e.publish_ax(v);
-      for (int j = 0; j < nt; ++j) e.hidden_tile(j, sm->bias_h);
+      for (int j = 0; j < nt; ++j) e.hidden_tile(j, j, sm->bias_h);  // (a pair computes the head twice)
       e.wait_acc();
       e.drain_free();
       if (e.wg == 0) {
@@ -712,7 +847,7 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const DenseArgs a
         float raw[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) raw[i] = __uint_as_float(r[i]) + (i < 3 * a.n_comp ? __ldg(a.bb + i) : 0.f);
-        if (valid && e.ok) head_row_thread(a, raw, grow);
+        if (valid && e.ok && crank == 0) head_row_thread(a, raw, grow);
       }
     } else if (a.do_pre) {
       e.publish_ax(v);
@@ -752,13 +887,13 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const DenseArgs a
       uint8_t* stage = &sm->ah[0][0][0];
       const bool direct = a.kv.mode == KV_PREFILL;   // context cache: direct stores are already coalesced
       const int tid_e = threadIdx.x - 64;
-      for (int t = 0; t < 3; ++t) {
+      for (int t = t_begin; t < t_end; ++t) {
         e.wait_acc();
         uint32_t r[Epilogue<D>::NCH][16];
 #pragma unroll
         for (int c = 0; c < Epilogue<D>::NCH; ++c) tmem_ld16(e.t_row + kAccA + e.col0 + 16 * c, r[c]);
         tmem_wait_ld();
-        if (t < 2) {  // the accumulator is in registers: the next projection may overwrite it
+        if (t + 1 < t_end) {  // the accumulator is in registers: the next projection may overwrite it
           tc_fence_before();
           mbar_arrive(&sm->ep_done);
         }
@@ -840,6 +975,7 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const DenseArgs a
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
   }
+  if (csize > 1) cluster_sync_all();  // neither CTA leaves while the other could still address its shared memory
 }
 
 }  // namespace
@@ -859,7 +995,12 @@ int launch_dense_tc(const DenseArgs& a, cudaStream_t s) {
   if (a.rows <= 0) return ARTAB_OK;
   ARTAB_REQUIRE(dense_tc_applicable(a), ARTAB_EINVAL, "tensor-core dense chain: unsupported shape or missing tiles");
   const size_t smem = sizeof(Smem) + 1024;
-  const int grid = (a.rows + BM - 1) / BM;
+  const int tiles = (a.rows + BM - 1) / BM;
+  // Few row tiles (a decode step): the chain's latency is what counts, so a CTA pair shares each
+  // tile.  Many tiles (prefill, teacher forcing): one CTA per tile keeps every SM on its own rows.
+  static const bool allow_pair = !(getenv("ARTAB_DENSE_PAIR") && getenv("ARTAB_DENSE_PAIR")[0] == '0');
+  const unsigned csize = (allow_pair && 2 * tiles <= kPairMaxCtas && a.Dff / HT >= 2) ? 2u : 1u;
+  const int grid = tiles * (int)csize;
   cudaError_t e = cudaSuccess;
   static bool configured[3] = {false, false, false};
   prof_begin(PROF_DENSE, s);
@@ -869,21 +1010,21 @@ int launch_dense_tc(const DenseArgs& a, cudaStream_t s) {
         e = cudaFuncSetAttribute(dense_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         configured[0] = e == cudaSuccess;
       }
-      if (e == cudaSuccess) e = launch_dependent(dense_tc_kernel<64>, dim3(grid), dim3(kThreads), smem, s, a);
+      if (e == cudaSuccess) e = launch_dependent_cluster(dense_tc_kernel<64>, dim3(grid), dim3(kThreads), smem, s, csize, a);
       break;
     case 128:
       if (!configured[1]) {
         e = cudaFuncSetAttribute(dense_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         configured[1] = e == cudaSuccess;
       }
-      if (e == cudaSuccess) e = launch_dependent(dense_tc_kernel<128>, dim3(grid), dim3(kThreads), smem, s, a);
+      if (e == cudaSuccess) e = launch_dependent_cluster(dense_tc_kernel<128>, dim3(grid), dim3(kThreads), smem, s, csize, a);
       break;
     default:
       if (!configured[2]) {
         e = cudaFuncSetAttribute(dense_tc_kernel<192>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         configured[2] = e == cudaSuccess;
       }
-      if (e == cudaSuccess) e = launch_dependent(dense_tc_kernel<192>, dim3(grid), dim3(kThreads), smem, s, a);
+      if (e == cudaSuccess) e = launch_dependent_cluster(dense_tc_kernel<192>, dim3(grid), dim3(kThreads), smem, s, csize, a);
       break;
   }
   prof_end(s);
