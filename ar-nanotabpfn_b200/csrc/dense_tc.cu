@@ -11,13 +11,15 @@
 //     with tcgen05.st, read as the A operand), the 64-wide hidden tile of the MLP
 //     goes through shared memory (swizzled K-major, written by the epilogue);
 //   * weights are bf16 hi(/lo) tiles pre-swizzled on the host into the exact
-//     shared-memory image, streamed by a producer warp with plain bulk copies
-//     through a 6-slot ring (full / empty mbarriers).
-// Warp 0: weight producer.  Warp 1: MMA issuer, owns the 512 TMEM columns.
+//     shared-memory image, streamed by two producer warps with plain bulk copies
+//     through two 3-slot rings (full / empty mbarriers).
+// Warp 0: weight producer A.  Warp 1: MMA issuer A, owns the 512 TMEM columns.
 // Warps 2-17: 512 epilogue threads, four per row (each owns a quarter of the
 // columns); LayerNorm statistics are exchanged through shared memory.
-// All mbarrier waits are bounded; on expiry the CTA flags an abort, stops
-// producing results, drains and frees TMEM.
+// Warp 18: MMA issuer B (second GEMM of the MLP).  Warp 19: its weight producer.
+// With few row tiles in flight a cluster of two CTAs shares one tile: see the
+// kernel body.  All mbarrier waits are bounded; on expiry the CTA flags an
+// abort, stops producing results, drains and frees TMEM.
 #include <cstdlib>
 
 #include "dense.cuh"
