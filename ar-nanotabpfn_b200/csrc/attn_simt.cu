@@ -236,6 +236,8 @@ __global__ void __launch_bounds__(128, 6) buf_merge_kernel(const BufMergeArgs a)
     float sc0[CH], sc1[CH];
 #pragma unroll
     for (int c = 0; c < CH; ++c) {
+      sc0[c] = sc1[c] = -INFINITY;
+      if (key0 + c * KPI >= len) continue;  // warp-uniform: a short tail skips the empty iterations
       float kf[VEC];
       Vec16<T>::unpack(kr[c], kf);
       float s0 = 0.f, s1 = 0.f;
@@ -270,6 +272,7 @@ __global__ void __launch_bounds__(128, 6) buf_merge_kernel(const BufMergeArgs a)
       }
 #pragma unroll
       for (int c = 0; c < CH; ++c) {
+        if (key0 + c * KPI >= len) continue;
         float vf[VEC];
         Vec16<T>::unpack(vr[c], vf);
         const float p0 = fast_exp2(sc0[c] - mn0), p1 = fast_exp2(sc1[c] - mn1);  // masked keys: exp2(-inf) = 0

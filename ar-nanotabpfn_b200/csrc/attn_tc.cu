@@ -42,6 +42,7 @@ struct __align__(1024) Smem {
   uint8_t k[NSTAGE][BN * 64];       // [128 keys][32 bf16], 64-byte swizzle
   uint8_t v[NSTAGE][2][64 * 128];   // V^T hi|lo: two boxes of [64 rows][64 keys], 128-byte swizzle
   uint64_t q_full, s_full, p_full, o_full;
+  uint64_t s_free;                  // every softmax thread has read its scores of the current tile
   uint64_t kv_full[NSTAGE], kv_empty[NSTAGE];
   float xmax[2][2][BM];             // row maxima exchanged between the two softmax warpgroups
   float xsum[BM];                   // row sum of the second warpgroup (epilogue)
@@ -176,8 +177,9 @@ struct TcParams {
 // softmax warpgroups own columns [0,64) and [64,128) of the same rows and exchange their row
 // maxima through shared memory.  MASKED: columns >= n_valid are -inf.
 template <bool MASKED>
-__device__ __forceinline__ void softmax_tile(Smem* sm, uint32_t t_row, int wg, int row, int parity, float sc,
-                                             int n_valid, float& m, float& l, float& alpha) {
+__device__ __forceinline__ bool softmax_tile(Smem* sm, uint32_t t_row, int wg, int row, int parity, float sc,
+                                             int n_valid, float& m, float& l, float& alpha, bool first,
+                                             volatile int* abort_flag) {
   uint32_t r[32];
   float mx = -INFINITY;
   const int col0 = 64 * wg;
@@ -197,11 +199,22 @@ __device__ __forceinline__ void softmax_tile(Smem* sm, uint32_t t_row, int wg, i
   mx = fmaxf(mx, sm->xmax[parity][wg ^ 1][row]);
   const float m_new = fmaxf(m, mx * sc);  // column 0 of every tile is valid, so mx is finite
   alpha = ex2_approx(m - m_new);          // m = -inf on the first tile gives 0
+  // This tile's scores were computed while the previous tile's P . V may still be running: P has one
+  // buffer, so it is rewritten only once that MMA has completed (the maxima above overlapped it).
+  bool ok = true;
+  if (!first) {
+    ok = mbar_wait(&sm->o_full, parity ^ 1, abort_flag);
+    tc_fence_after();
+  }
   float sum = 0.f;
 #pragma unroll 1
   for (int c = 0; c < 2; ++c) {
     tmem_ld32(t_row + kColS + col0 + 32 * c, r);
     tmem_wait_ld();
+    if (c == 1) {  // the scores are in registers: the next tile's Q.K^T may overwrite them
+      tc_fence_before();
+      mbar_arrive(&sm->s_free);
+    }
     uint32_t pk[16];
 #pragma unroll
     for (int i = 0; i < 32; i += 2) {
@@ -218,6 +231,7 @@ __device__ __forceinline__ void softmax_tile(Smem* sm, uint32_t t_row, int wg, i
   }
   l = l * alpha + sum;
   m = m_new;
+  return ok;
 }
 
 __global__ void __launch_bounds__(kThreads, 2)
@@ -263,6 +277,7 @@ ctx_attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     mbar_init(&sm->s_full, 1);
     mbar_init(&sm->p_full, 256);
     mbar_init(&sm->o_full, 1);
+    mbar_init(&sm->s_free, 256);
     for (int s = 0; s < NSTAGE; ++s) {
       mbar_init(&sm->kv_full[s], 1);
       mbar_init(&sm->kv_empty[s], 1);
@@ -331,18 +346,31 @@ ctx_attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       constexpr uint32_t idesc_pv = make_idesc(BM, 2 * DH);
       bool ok = mbar_wait(&sm->q_full, 0, abort_flag);
       const uint32_t q_addr = smem_u32(sm->q);
-      for (int j = 0; ok && j < nt; ++j) {
+      // S = Q . K^T of tile j   (M 128, N 128, K 32 = two k-steps of 16 bf16 = 32 bytes)
+      auto issue_qk = [&](int j) -> bool {
         const int st = j % NSTAGE;
-        ok = mbar_wait(&sm->kv_full[st], (j / NSTAGE) & 1, abort_flag);
-        if (!ok) break;
+        if (!mbar_wait(&sm->kv_full[st], (j / NSTAGE) & 1, abort_flag)) return false;
         tc_fence_after();
-        // S = Q . K^T   (M 128, N 128, K 32 = two k-steps of 16 bf16 = 32 bytes)
         const uint32_t k_addr = smem_u32(sm->k[st]);
 #pragma unroll
         for (int ks = 0; ks < 2; ++ks)
           umma_ss(tmem + kColS, make_desc(q_addr + 32 * ks, 512, kLayoutSw64),
                   make_desc(k_addr + 32 * ks, 512, kLayoutSw64), idesc_qk, ks);
         umma_commit(&sm->s_full);
+        return true;
+      };
+      ok = ok && issue_qk(0);
+      for (int j = 0; ok && j < nt; ++j) {
+        const int st = j % NSTAGE;
+        // The next tile's scores are computed while the softmax threads still turn this tile's
+        // into P: they release S as soon as their last score is in registers.
+        if (j + 1 < nt) {
+          ok = mbar_wait(&sm->s_free, j & 1, abort_flag);
+          if (!ok) break;
+          tc_fence_after();
+          ok = issue_qk(j + 1);
+          if (!ok) break;
+        }
         // softmax writes P (and has folded the previous O tile) -> O = P . [V_hi | V_lo]
         ok = mbar_wait(&sm->p_full, j & 1, abort_flag);
         if (!ok) break;
@@ -373,13 +401,13 @@ ctx_attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       tc_fence_after();
       const int n_valid = p.n_ctx - (tile_begin + j) * BN;
       if (n_valid >= BN)
-        softmax_tile<false>(sm, t_row, wg, row, j & 1, sc, BN, m, l, alpha);
+        ok = softmax_tile<false>(sm, t_row, wg, row, j & 1, sc, BN, m, l, alpha, j == 0, abort_flag) && ok;
       else
-        softmax_tile<true>(sm, t_row, wg, row, j & 1, sc, n_valid, m, l, alpha);
+        ok = softmax_tile<true>(sm, t_row, wg, row, j & 1, sc, n_valid, m, l, alpha, j == 0, abort_flag) && ok;
       // warpgroup 0 folds the previous tile's O (its MMA completed before this tile's S) and
       // rescales; the read must precede the arrival below, which lets the next P.V overwrite O
       if (wg == 0 && j > 0) {
-        ok = mbar_wait(&sm->o_full, (j - 1) & 1, abort_flag) && ok;  // already complete: keeps the phase in step
+        // (o_full of tile j - 1 was awaited inside softmax_tile)
 #pragma unroll 1
         for (int hl = 0; hl < 2; ++hl) {  // hi and lo halves of V
           tmem_ld32(t_row + kColO + 32 * hl, r);
