@@ -199,13 +199,7 @@ __device__ __forceinline__ bool softmax_tile(Smem* sm, uint32_t t_row, int wg, i
   mx = fmaxf(mx, sm->xmax[parity][wg ^ 1][row]);
   const float m_new = fmaxf(m, mx * sc);  // column 0 of every tile is valid, so mx is finite
   alpha = ex2_approx(m - m_new);          // m = -inf on the first tile gives 0
-  // This tile's scores were computed while the previous tile's P . V may still be running: P has one
-  // buffer, so it is rewritten only once that MMA has completed (the maxima above overlapped it).
   bool ok = true;
-  if (!first) {
-    ok = mbar_wait(&sm->o_full, parity ^ 1, abort_flag);
-    tc_fence_after();
-  }
   float sum = 0.f;
 #pragma unroll 1
   for (int c = 0; c < 2; ++c) {
@@ -226,6 +220,13 @@ __device__ __forceinline__ bool softmax_tile(Smem* sm, uint32_t t_row, int wg, i
       }
       sum += p0 + p1;
       pk[i >> 1] = pack_bf16(p0, p1);
+    }
+    // This tile's scores were computed while the previous tile's P . V may still be running: P has
+    // one buffer, so it is rewritten only once that MMA has completed (the maxima and the first
+    // half of the exponentials above overlapped it).
+    if (c == 0 && !first) {
+      ok = mbar_wait(&sm->o_full, parity ^ 1, abort_flag);
+      tc_fence_after();
     }
     tmem_st16(t_row + kColP + 32 * wg + 16 * c, pk);
   }
