@@ -231,6 +231,12 @@ DenseArgs dense_base(const artab_model* m, const artab_state* st, int rows) {
   d.kv.head_dim = m->head_dim;
   d.status = st->status;
   d.lane_major = chain_on_tc(m, st);
+  // the context-partial workspace is idle while a dense chain runs: its first two slots serve the
+  // CTA pairs' exchange
+  if (st->max_splits >= 2) {
+    d.pair_scratch = st->o_part;
+    d.pair_slot_stride = (size_t)st->max_rows * m->d_model;
+  }
   fill_head(m, d);
   return d;
 }

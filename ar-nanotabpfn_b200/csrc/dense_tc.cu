@@ -216,9 +216,7 @@ struct __align__(1024) Smem {
   __nv_bfloat16* rowdst[BM];          // private-buffer K slot of each row's token (null: not cached)
   uint64_t w_full[2][NSLOT], w_empty[2][NSLOT];
   uint64_t ep_done, acc_full, h_full, acch_free, ah_ready, ah_free;
-  // CTA-pair exchange of the MLP partial sums: x_ready = the peer's exchange buffer may be written,
-  // x_full = the peer's partial has landed in ours, xchg_done = our threads have consumed it
-  uint64_t x_ready, x_full, xchg_done;
+  uint64_t x_full;   // CTA pair: the peer's MLP partial sums have been written to the global scratch
   uint64_t in_done;  // the peer has read its inputs (its residual input aliases our parking buffer)
   uint32_t tmem_base;
   int abort_flag;
@@ -525,16 +523,11 @@ struct Epilogue {
     ++free_count;
   }
   // CTA pair: v[i] += (own MLP partial + the peer's).  Each CTA holds the second GEMM's sum over its
-  // half of the hidden tiles in ACC_A.  The partials cross through distributed shared memory: the
-  // second weight ring and the hidden-operand buffer, idle once the MLP's MMAs have completed, form
-  // the 96 KB landing zone [column group of 4][128 rows] float4.  a + b == b + a exactly, so both
-  // CTAs end up with the same bits.  Called after wait_acc() (this CTA's MLP MMAs have completed).
-  __device__ void exchange_add(float* v, uint32_t peer) {
-    float4* xbuf = reinterpret_cast<float4*>(&sm->ring[1][0][0]);
-    static_assert(sizeof(Smem::ring) / 2 + sizeof(Smem::ah) >= (size_t)BM * D * 4, "exchange buffer too small");
-    if (wg == 0 && row == 0) mbar_arrive_remote(map_to_rank(smem_u32(&sm->x_ready), peer));  // our zone is free
-    ok = mbar_wait_cluster(&sm->x_ready, 0, &sm->abort_flag) && ok;                         // the peer's is
-    const uint32_t remote = map_to_rank(smem_u32(xbuf), peer);
+  // half of the hidden tiles in ACC_A.  The partials cross through a global scratch (lane-major like
+  // the other row workspaces, so both directions are coalesced float4 streams that stay in L2): write
+  // own partial, release-arrive on the peer's barrier, acquire-wait on ours, read the peer's.
+  // a + b == b + a exactly, so both CTAs end up with the same bits.  Called after wait_acc().
+  __device__ void exchange_add(float* v, uint32_t peer, float* mine, const float* theirs, size_t lm0) {
     uint32_t r[16];
 #pragma unroll
     for (int c = 0; c < NCH; ++c) {
@@ -542,25 +535,27 @@ struct Epilogue {
       tmem_wait_ld();
 #pragma unroll
       for (int q = 0; q < 4; ++q)
-        st_remote_f4(remote + (uint32_t)((((col0 + 16 * c) >> 2) + q) * BM + row) * 16, __uint_as_float(r[4 * q]),
-                     __uint_as_float(r[4 * q + 1]), __uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3]));
+        *reinterpret_cast<float4*>(mine + lm0 + (size_t)(4 * c + q) * 128) =
+            make_float4(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]), __uint_as_float(r[4 * q + 2]),
+                        __uint_as_float(r[4 * q + 3]));
     }
-    mbar_arrive_remote(map_to_rank(smem_u32(&sm->x_full), peer));
+    mbar_arrive_remote(map_to_rank(smem_u32(&sm->x_full), peer));  // releases the stores above
     ok = mbar_wait_cluster(&sm->x_full, 0, &sm->abort_flag) && ok;
 #pragma unroll
     for (int c = 0; c < NCH; ++c) {
+      float4 t[4];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) t[q] = __ldcg(reinterpret_cast<const float4*>(theirs + lm0 + (size_t)(4 * c + q) * 128));
       tmem_ld16(t_row + kAccA + col0 + 16 * c, r);
       tmem_wait_ld();
 #pragma unroll
       for (int q = 0; q < 4; ++q) {
-        const float4 t = xbuf[(((col0 + 16 * c) >> 2) + q) * BM + row];
-        v[16 * c + 4 * q] += __uint_as_float(r[4 * q]) + t.x;
-        v[16 * c + 4 * q + 1] += __uint_as_float(r[4 * q + 1]) + t.y;
-        v[16 * c + 4 * q + 2] += __uint_as_float(r[4 * q + 2]) + t.z;
-        v[16 * c + 4 * q + 3] += __uint_as_float(r[4 * q + 3]) + t.w;
+        v[16 * c + 4 * q] += __uint_as_float(r[4 * q]) + t[q].x;
+        v[16 * c + 4 * q + 1] += __uint_as_float(r[4 * q + 1]) + t[q].y;
+        v[16 * c + 4 * q + 2] += __uint_as_float(r[4 * q + 2]) + t[q].z;
+        v[16 * c + 4 * q + 3] += __uint_as_float(r[4 * q + 3]) + t[q].w;
       }
     }
-    mbar_arrive(&sm->xchg_done);
   }
 };
 
@@ -642,9 +637,7 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const DenseArgs a
     mbar_init(&sm->acch_free, kEpi);
     mbar_init(&sm->ah_ready, kEpi);
     mbar_init(&sm->ah_free, 1);
-    mbar_init(&sm->x_ready, 1);
     mbar_init(&sm->x_full, kEpi);
-    mbar_init(&sm->xchg_done, kEpi);
     mbar_init(&sm->in_done, kEpi / 32);
     sm->abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -704,8 +697,6 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const DenseArgs a
       Producer p{sm, 1, 0, true};
       if (a.do_post) p.mlp_second(a.post_w.tc_w2, lo_post & 4, kSlab, nt, crank, csize);
       if (a.do_head) {
-        // this ring is part of the pair's exchange zone until the epilogue has consumed the partials
-        if (a.do_post && csize > 1) p.ok = mbar_wait(&sm->xchg_done, 0, &sm->abort_flag) && p.ok;
         p.mlp_second(a.tc_wb, a.tc_head_lo & 2, 16 * 128, nt, 0, 1);
       }
     }
@@ -821,7 +812,8 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const DenseArgs a
 #pragma unroll
       for (int i = 0; i < PART; ++i) v[i] += sm->vec[2][e.col0 + i];
       if (csize > 1)
-        e.exchange_add(v, crank ^ 1u);
+        e.exchange_add(v, crank ^ 1u, a.pair_scratch + (size_t)crank * a.pair_slot_stride,
+                       a.pair_scratch + (size_t)(crank ^ 1u) * a.pair_slot_stride, lm0);
       else
         e.add_acc(v);
       e.layer_norm(v, sm->vec[3], sm->vec[4]);   // v = x3
@@ -1001,7 +993,7 @@ int launch_dense_tc(const DenseArgs& a, cudaStream_t s) {
   // Few row tiles (a decode step): the chain's latency is what counts, so a CTA pair shares each
   // tile.  Many tiles (prefill, teacher forcing): one CTA per tile keeps every SM on its own rows.
   static const bool allow_pair = !(getenv("ARTAB_DENSE_PAIR") && getenv("ARTAB_DENSE_PAIR")[0] == '0');
-  const unsigned csize = (allow_pair && 2 * tiles <= kPairMaxCtas && a.Dff / HT >= 2) ? 2u : 1u;
+  const unsigned csize = (allow_pair && a.pair_scratch && 2 * tiles <= kPairMaxCtas && a.Dff / HT >= 2) ? 2u : 1u;
   const int grid = tiles * (int)csize;
   cudaError_t e = cudaSuccess;
   static bool configured[3] = {false, false, false};
