@@ -236,6 +236,7 @@ DenseArgs dense_base(const artab_model* m, const artab_state* st, int rows) {
   if (st->max_splits >= 2) {
     d.pair_scratch = st->o_part;
     d.pair_slot_stride = (size_t)st->max_rows * m->d_model;
+    d.pair_slots = st->max_splits >= 4 ? 4 : 2;
   }
   fill_head(m, d);
   return d;

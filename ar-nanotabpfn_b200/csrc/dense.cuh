@@ -42,10 +42,11 @@ struct DenseArgs {
   float* ld_out;
   int32_t* comp_out;
   int32_t* status;     // device status word (bounded waits), may be null
-  // tensor-core chain: scratch for the CTA-pair exchange, 2 slots of pair_slot_stride floats
+  // tensor-core chain: scratch for the CTA-pair exchange, pair_slots slots of pair_slot_stride floats
   // (>= rows rounded up to 128, times D, each); null: one CTA per row tile
   float* pair_scratch;
   size_t pair_slot_stride;
+  int pair_slots;      // slots available in pair_scratch (2: layer MLP only, 4: head MLP too)
   const void *tc_wa, *tc_wb;  // tensor-core tiles of the head matrices (null: fp32 chain)
   int tc_head_lo;
 };

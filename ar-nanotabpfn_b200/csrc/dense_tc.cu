@@ -675,6 +675,10 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const DenseArgs a
 
   const int lo_post = a.post_w.tc_lo, lo_pre = a.pre_w.tc_lo;
   const int n_mine = (nt - (int)crank + (int)csize - 1) / (int)csize;  // hidden tiles of the layer MLP done here
+  // the head MLP is shared the same way when the scratch has room for a second exchange
+  const bool head_pair = csize > 1 && a.pair_slots >= 4;
+  const int h_first = head_pair ? (int)crank : 0, h_step = head_pair ? (int)csize : 1;
+  const int h_mine = head_pair ? n_mine : nt;
 
   if (warp == 0) {
     // --------------------- weight producer A: everything but the second MLP GEMM ---------------------
@@ -685,7 +689,7 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const DenseArgs a
         p.mlp_first(a.post_w.tc_w1, lo_post & 2, NKC, nt, crank, csize);
       }
       if (a.do_head) {
-        p.mlp_first(a.tc_wa, a.tc_head_lo & 1, NKC, nt, 0, 1);
+        p.mlp_first(a.tc_wa, a.tc_head_lo & 1, NKC, nt, h_first, h_step);
       } else if (a.do_pre) {
         p.matrix(a.pre_w.tc_wf, NKC, lo_pre & 8, kSlab);
         p.matrix_range(a.pre_w.tc_wqkv, t_begin * NKC, t_end * NKC, lo_pre & 16, kSlab);
@@ -697,7 +701,7 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const DenseArgs a
       Producer p{sm, 1, 0, true};
       if (a.do_post) p.mlp_second(a.post_w.tc_w2, lo_post & 4, kSlab, nt, crank, csize);
       if (a.do_head) {
-        p.mlp_second(a.tc_wb, a.tc_head_lo & 2, 16 * 128, nt, 0, 1);
+        p.mlp_second(a.tc_wb, a.tc_head_lo & 2, 16 * 128, nt, h_first, h_step);
       }
     }
   } else if (warp == 1) {
@@ -713,7 +717,7 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const DenseArgs a
       }
       if (a.do_head) {
         m.wait_epilogue();                               // A_x = z
-        m.mlp_first(NKC, a.tc_head_lo & 1, nt);
+        m.mlp_first(NKC, a.tc_head_lo & 1, h_mine);
       } else if (a.do_pre) {
         m.wait_epilogue();                               // A_x = layer input
         m.gemm_full_ts(kAccA, D, NKC, lo_pre & 8);
@@ -731,7 +735,7 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const DenseArgs a
     if (lane == 0) {
       Issuer m{sm, tmem, 1, 0, 0, 0, 0, true};
       if (a.do_post) m.mlp_second(lo_post & 4, n_mine, D);
-      if (a.do_head) m.mlp_second(a.tc_head_lo & 2, nt, 16);
+      if (a.do_head) m.mlp_second(a.tc_head_lo & 2, h_mine, 16);
     }
   } else {
     // ---------------------------------- epilogue ----------------------------------
@@ -831,16 +835,45 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const DenseArgs a
       for (int i = threadIdx.x - 64; i < a.Dff; i += kEpi) sm->bias_h[i] = a.ba[i];
       e.sync_groups();
       e.publish_ax(v);
-      for (int j = 0; j < nt; ++j) e.hidden_tile(j, j, sm->bias_h);  // (a pair computes the head twice)
+      {
+        int jl = 0;
+        for (int j = h_first; j < nt; j += h_step, ++jl) e.hidden_tile(jl, j, sm->bias_h);
+      }
       e.wait_acc();
       e.drain_free();
+      // 16 raw head outputs per row, held by the first column group; a pair adds its two partials
+      // (second exchange of the launch: slots 2 and 3 of the scratch, barrier phase 1)
+      uint32_t r[16];
+      float peer_raw[16];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) peer_raw[i] = 0.f;
       if (e.wg == 0) {
-        uint32_t r[16];
         tmem_ld16(e.t_row + kAccA, r);
         tmem_wait_ld();
+      }
+      if (head_pair) {
+        float* mine = a.pair_scratch + (size_t)(2 + crank) * a.pair_slot_stride + (size_t)grow * 16;
+        const float* theirs = a.pair_scratch + (size_t)(2 + (crank ^ 1u)) * a.pair_slot_stride + (size_t)grow * 16;
+        if (e.wg == 0) {
+#pragma unroll
+          for (int q = 0; q < 4; ++q)
+            reinterpret_cast<uint4*>(mine)[q] = make_uint4(r[4 * q], r[4 * q + 1], r[4 * q + 2], r[4 * q + 3]);
+        }
+        mbar_arrive_remote(map_to_rank(smem_u32(&sm->x_full), crank ^ 1u));
+        e.ok = mbar_wait_cluster(&sm->x_full, a.do_post ? 1 : 0, &sm->abort_flag) && e.ok;
+        if (e.wg == 0) {
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const float4 t = __ldcg(reinterpret_cast<const float4*>(theirs) + q);
+            peer_raw[4 * q] = t.x; peer_raw[4 * q + 1] = t.y; peer_raw[4 * q + 2] = t.z; peer_raw[4 * q + 3] = t.w;
+          }
+        }
+      }
+      if (e.wg == 0) {
         float raw[16];
 #pragma unroll
-        for (int i = 0; i < 16; ++i) raw[i] = __uint_as_float(r[i]) + (i < 3 * a.n_comp ? __ldg(a.bb + i) : 0.f);
+        for (int i = 0; i < 16; ++i)
+          raw[i] = (__uint_as_float(r[i]) + peer_raw[i]) + (i < 3 * a.n_comp ? __ldg(a.bb + i) : 0.f);
         if (valid && e.ok && crank == 0) head_row_thread(a, raw, grow);
       }
     } else if (a.do_pre) {
