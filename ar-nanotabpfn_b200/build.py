@@ -15,7 +15,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(HERE)
 CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "libartab_b200.so")
-SOURCES = ["api.cu", "dense_simt.cu", "attn_simt.cu", "attn_tc.cu", "noalloc.cu", "dense_tc.cu"]
+SOURCES = ["api.cu", "dense_simt.cu", "attn_simt.cu", "attn_tc.cu", "buf_mma.cu", "noalloc.cu", "dense_tc.cu"]
 FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "--expt-relaxed-constexpr", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden",

@@ -37,7 +37,9 @@ struct BufMergeArgs {
 int launch_ctx_attn_simt(const CtxAttnArgs& a, cudaStream_t s);
 int launch_ctx_attn_tc(const CtxAttnArgs& a, cudaStream_t s);  // tcgen05, bf16, head_dim 32
 bool ctx_attn_tc_supported(int dtype, int head_dim);
-int launch_buf_merge(const BufMergeArgs& a, cudaStream_t s);
+int launch_buf_merge(const BufMergeArgs& a, cudaStream_t s);      // picks the MMA kernel when it applies
+int launch_buf_merge_mma(const BufMergeArgs& a, cudaStream_t s);  // mma.sync, bf16, head_dim 32
+bool buf_mma_supported(int dtype, int head_dim);
 int launch_kv_append(int dtype, void* kv, const void* k_new, const void* v_new, long n_bh, int dh, int max_buf,
                      int pos, cudaStream_t s);
 

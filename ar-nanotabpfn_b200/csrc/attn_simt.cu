@@ -419,6 +419,7 @@ int launch_ctx_attn_simt(const CtxAttnArgs& a, cudaStream_t s) {
 
 int launch_buf_merge(const BufMergeArgs& a, cudaStream_t s) {
   if (a.n_items <= 0) return ARTAB_OK;
+  if (buf_mma_supported(a.dtype, a.head_dim)) return launch_buf_merge_mma(a, s);
   return a.dtype == ARTAB_BF16 ? launch_buf_t<__nv_bfloat16>(a, s) : launch_buf_t<float>(a, s);
 }
 

@@ -1,0 +1,276 @@
+// Private-buffer pass + log-sum-exp merge on warp-level tensor-core MMAs (bf16 caches, head_dim 32).
+//
+// Same job and the same one-warp-per-(stream, head[, item]) mapping as buf_merge_kernel, but the two
+// queries of an item are rows 0 and 1 of an m16n8k16 A fragment, so a block of 16 keys costs
+// 4 (Q.K^T) + 8 (P.V with P split into bf16 hi + lo, which keeps P at fp32 accuracy) MMAs and a
+// two-value softmax per lane instead of ~140 scalar instructions.  K fragments are read straight
+// from global memory (a B fragment of K^T is two bf16 of one key row = one 32-bit load); V goes
+// through a 4-slot shared-memory ring filled with cp.async and is read with ldmatrix.trans.
+// At short buffers (a decode step of 512 streams) the pass is instruction-bound, at long ones it
+// is a pure HBM stream; both get the shorter instruction stream.
+#include "attn.cuh"
+
+namespace artab {
+
+namespace {
+
+constexpr int DH = 32;     // head_dim served by this kernel
+constexpr int KB = 16;     // keys per block (the k extent of one P.V MMA)
+constexpr int NR = 4;      // V ring slots per warp
+constexpr int PITCH = 80;  // bytes per staged V row: 64 of data + 16 of padding (conflict-free ldmatrix)
+constexpr int WPB = 4;     // warps per CTA
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
+  // rows 8-15 of A (fragment registers a1, a3) are always zero here: only two query rows exist
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t saddr, uint32_t (&r)[4]) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(saddr)
+               : "memory");
+}
+__device__ __forceinline__ void cp_async16(uint32_t saddr, const void* gptr, bool valid) {
+  const uint32_t n = valid ? 16u : 0u;  // 0 source bytes: the 16 destination bytes are zero-filled
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(saddr), "l"(gptr), "r"(n) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ float fast_exp2(float x) {  // MUFU ex2: exp2(-inf) = 0
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+__global__ void __launch_bounds__(WPB * 32, 6) buf_mma_kernel(const BufMergeArgs a) {
+  __shared__ __align__(16) uint8_t vs[WPB][NR][KB * PITCH];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const long item = (long)blockIdx.x * WPB + warp;
+  if (item >= a.n_items) return;  // warp-uniform; the kernel has no CTA-wide barrier
+  const int g = lane >> 2;   // fragment row: query index (rows 0, 1) / key inside an 8-key tile
+  const int t4 = lane & 3;   // fragment column pair
+
+  long b;
+  int h, len;
+  long rows2[2];
+  if (a.mode_tf) {
+    const int ips = a.nt + 1;
+    const int i = (int)(item % ips);
+    const long bh = item / ips;
+    b = bh / a.n_heads;
+    h = (int)(bh - b * a.n_heads);
+    len = i;
+    rows2[0] = i < a.nt ? b * 2 * a.nt + a.nt + i : -1;
+    rows2[1] = i >= 1 ? b * 2 * a.nt + i - 1 : -1;
+  } else {
+    b = item / a.n_heads;
+    h = (int)(item - b * a.n_heads);
+    len = a.len0;
+    rows2[0] = b * a.n_new + a.n_new - 1;
+    rows2[1] = a.n_new == 2 ? b * a.n_new : -1;
+  }
+
+  // A fragments of Q for the two 16-wide k-steps: row g = query g, columns t4*2 + {0,1} (+8)
+  uint32_t qa[2][2] = {{0u, 0u}, {0u, 0u}};
+  if (g < 2 && rows2[g] >= 0) {
+    const uint32_t* qp = reinterpret_cast<const uint32_t*>(reinterpret_cast<const __nv_bfloat16*>(a.q) +
+                                                           ((size_t)rows2[g] * a.n_heads + h) * DH) + t4;
+#pragma unroll
+    for (int ks = 0; ks < 2; ++ks) {
+      qa[ks][0] = __ldg(qp + 8 * ks);
+      qa[ks][1] = __ldg(qp + 8 * ks + 4);
+    }
+  }
+  const __nv_bfloat16* kv =
+      reinterpret_cast<const __nv_bfloat16*>(a.kv_buf) + ((size_t)(b * a.n_heads + h) * a.max_buf) * 2 * DH;
+  const float sc = a.scale * kLog2e;
+  const int nblk = (len + KB - 1) / KB;
+
+  // V rows of block kb -> ring slot kb % NR: 16 keys x 4 chunks of 16 bytes, two chunks per lane
+  const uint32_t vs_base = smem_u32(&vs[warp][0][0]);
+  auto stage_v = [&](int kb) {
+    if (kb < nblk) {
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        const int c = lane * 2 + i, key = c >> 2, part = c & 3;
+        const int gkey = kb * KB + key;
+        const bool valid = gkey < len;
+        const __nv_bfloat16* src = kv + (valid ? ((size_t)gkey * 2 * DH + DH + part * 8) : 0);
+        cp_async16(vs_base + (uint32_t)((kb % NR) * (KB * PITCH) + key * PITCH + part * 16), src, valid);
+      }
+    }
+    cp_async_commit();  // one group per call, empty or not: the wait below counts groups
+  };
+  // B fragments of K^T for block kb: [8-key tile][k-step][b0, b1]; key = tile * 8 + g, columns like A
+  auto load_k = [&](int kb, uint32_t (&kf)[2][2][2]) {
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt) {
+      const int key = kb * KB + nt * 8 + g;
+      const bool valid = key < len;
+      const uint32_t* kp = reinterpret_cast<const uint32_t*>(kv + (size_t)(valid ? key : 0) * 2 * DH) + t4;
+#pragma unroll
+      for (int ks = 0; ks < 2; ++ks) {
+        kf[nt][ks][0] = valid ? __ldg(kp + 8 * ks) : 0u;
+        kf[nt][ks][1] = valid ? __ldg(kp + 8 * ks + 4) : 0u;
+      }
+    }
+  };
+
+  float m = -INFINITY, l = 0.f;
+  float o[4][4];  // [8-dim tile][c0..c3]: c0, c1 = row g, dims tile*8 + t4*2 + {0,1}; c2, c3 stay zero
+#pragma unroll
+  for (int j = 0; j < 4; ++j)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) o[j][e] = 0.f;
+
+  uint32_t kf[2][2][2];
+#pragma unroll
+  for (int i = 0; i < NR - 1; ++i) stage_v(i);
+  if (nblk > 0) load_k(0, kf);
+
+  for (int kb = 0; kb < nblk; ++kb) {
+    uint32_t kn[2][2][2];
+    if (kb + 1 < nblk) load_k(kb + 1, kn);
+    stage_v(kb + NR - 1);  // into the slot read in the previous iteration (its ldmatrix results were consumed)
+
+    // scores of 16 keys for the two queries
+    float s[2][4];
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) s[nt][e] = 0.f;
+#pragma unroll
+      for (int ks = 0; ks < 2; ++ks) mma_bf16(s[nt], qa[ks][0], qa[ks][1], kf[nt][ks][0], kf[nt][ks][1]);
+    }
+    // this lane's four scores of row g: keys kb*16 + nt*8 + t4*2 + {0, 1}
+    const int key0 = kb * KB + t4 * 2;
+    float sv[4];
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+      for (int e = 0; e < 2; ++e) sv[nt * 2 + e] = key0 + nt * 8 + e < len ? s[nt][e] * sc : -INFINITY;
+    float bm = fmaxf(fmaxf(sv[0], sv[1]), fmaxf(sv[2], sv[3]));
+    bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 1));
+    bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 2));   // finite: key kb*16 of every block is valid
+    const float m_new = fmaxf(m, bm);
+    const float alpha = fast_exp2(m - m_new);              // first block: exp2(-inf) = 0
+    float p[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) p[i] = fast_exp2(sv[i] - m_new);
+    l = l * alpha + (p[0] + p[1]) + (p[2] + p[3]);         // this lane's share of the row sum
+    m = m_new;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      o[j][0] *= alpha;
+      o[j][1] *= alpha;
+    }
+    // P as the A operand of P.V (k = 16 keys): a0 = keys t4*2+{0,1}, a2 = the same + 8; hi + lo parts
+    const uint32_t ph0 = pack_bf16(p[0], p[1]), ph1 = pack_bf16(p[2], p[3]);
+    const uint32_t pl0 = pack_bf16(p[0] - __uint_as_float(ph0 << 16), p[1] - __uint_as_float(ph0 & 0xffff0000u));
+    const uint32_t pl1 = pack_bf16(p[2] - __uint_as_float(ph1 << 16), p[3] - __uint_as_float(ph1 & 0xffff0000u));
+
+    // V block kb has landed once all but the NR - 1 newest groups are complete
+    cp_async_wait<NR - 1>();
+    __syncwarp();
+    const uint32_t slot = vs_base + (uint32_t)((kb % NR) * (KB * PITCH));
+    const int mi = lane >> 3, r8 = lane & 7;
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
+      // matrices: (dim tile 2c, keys 0-7), (2c, keys 8-15), (2c+1, keys 0-7), (2c+1, keys 8-15)
+      uint32_t vb[4];
+      ldmatrix_x4_trans(slot + (uint32_t)(((mi & 1) * 8 + r8) * PITCH + (2 * c + (mi >> 1)) * 16), vb);
+      mma_bf16(o[2 * c], ph0, ph1, vb[0], vb[1]);
+      mma_bf16(o[2 * c], pl0, pl1, vb[0], vb[1]);
+      mma_bf16(o[2 * c + 1], ph0, ph1, vb[2], vb[3]);
+      mma_bf16(o[2 * c + 1], pl0, pl1, vb[2], vb[3]);
+    }
+    if (kb + 1 < nblk) {
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+        for (int ks = 0; ks < 2; ++ks) {
+          kf[nt][ks][0] = kn[nt][ks][0];
+          kf[nt][ks][1] = kn[nt][ks][1];
+        }
+    }
+  }
+  cp_async_wait<0>();
+  l += __shfl_xor_sync(0xffffffffu, l, 1);
+  l += __shfl_xor_sync(0xffffffffu, l, 2);
+
+  // The pass above read only what kernels older than the preceding one wrote (q and the buffer
+  // rows); the context partials come from the preceding kernel.
+  dep_wait();
+  dep_trigger();
+
+  if (g >= 2 || rows2[g & 1] < 0) return;
+  const long r = rows2[g];
+  const float lse_b = l > 0.f ? (m + log2f(l)) * kLn2 : -INFINITY;  // natural log, like the partials
+  float top = lse_b;
+  for (int sp = 0; sp < a.n_splits; ++sp)
+    top = fmaxf(top, __ldg(a.lse_part + ((size_t)sp * a.rows + r) * a.n_heads + h));
+  float wsum = 0.f, out[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) out[i] = 0.f;
+  if (l > 0.f) {
+    const float wb = expf(lse_b - top);
+    wsum = wb;
+    const float inv = wb / l;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      out[2 * j] = o[j][0] * inv;
+      out[2 * j + 1] = o[j][1] * inv;
+    }
+  }
+  for (int sp = 0; sp < a.n_splits; ++sp) {
+    const size_t ro = ((size_t)sp * a.rows + r) * a.n_heads + h;
+    const float ls = __ldg(a.lse_part + ro);
+    if (ls == -INFINITY) continue;
+    const float ws = expf(ls - top);
+    wsum += ws;
+    const float* op = a.o_part + ro * DH + t4 * 2;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 v = *reinterpret_cast<const float2*>(op + 8 * j);
+      out[2 * j] = fmaf(ws, v.x, out[2 * j]);
+      out[2 * j + 1] = fmaf(ws, v.y, out[2 * j + 1]);
+    }
+  }
+  const float inv = wsum > 0.f ? 1.0f / wsum : 0.f;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int col = h * DH + 8 * j + t4 * 2;
+    float* dst = a.out + (a.out_lane_major ? lane_major_index(r, col, a.n_heads * DH) : (size_t)r * a.n_heads * DH + col);
+    *reinterpret_cast<float2*>(dst) = make_float2(out[2 * j] * inv, out[2 * j + 1] * inv);
+  }
+}
+
+}  // namespace
+
+bool buf_mma_supported(int dtype, int head_dim) { return dtype == ARTAB_BF16 && head_dim == DH; }
+
+int launch_buf_merge_mma(const BufMergeArgs& a, cudaStream_t s) {
+  if (a.n_items <= 0) return ARTAB_OK;
+  ARTAB_REQUIRE(buf_mma_supported(a.dtype, a.head_dim), ARTAB_EINVAL, "buffer attention (mma): bf16, head_dim 32 only");
+  const unsigned grid = (unsigned)((a.n_items + WPB - 1) / WPB);
+  prof_begin(PROF_BUF, s);
+  const cudaError_t le = launch_dependent(buf_mma_kernel, dim3(grid), dim3(WPB * 32), 0, s, a);
+  prof_end(s);
+  ARTAB_REQUIRE(le == cudaSuccess, ARTAB_ELAUNCH, "buf_mma_kernel: %s", cudaGetErrorString(le));
+  count_launch();
+  return check_launch("buf_mma_kernel");
+}
+
+}  // namespace artab
