@@ -3,9 +3,10 @@
 // Same job and the same one-warp-per-(stream, head[, item]) mapping as buf_merge_kernel, but the two
 // queries of an item are rows 0 and 1 of an m16n8k16 A fragment, so a block of 16 keys costs
 // 4 (Q.K^T) + 8 (P.V with P split into bf16 hi + lo, which keeps P at fp32 accuracy) MMAs and a
-// two-value softmax per lane instead of ~140 scalar instructions.  K fragments are read straight
-// from global memory (a B fragment of K^T is two bf16 of one key row = one 32-bit load); V goes
-// through a 4-slot shared-memory ring filled with cp.async and is read with ldmatrix.trans.
+// two-value softmax per lane instead of ~140 scalar instructions.  A key's K row and V row are
+// adjacent in memory, so a block of 16 keys is one contiguous 2 KB span: it goes through a 4-slot
+// shared-memory ring filled with 16-byte cp.async copies and is read with ldmatrix (K^T fragments)
+// and ldmatrix.trans (V fragments).
 // At short buffers (a decode step of 512 streams) the pass is instruction-bound, at long ones it
 // is a pure HBM stream; both get the shorter instruction stream.
 #include "attn.cuh"
@@ -17,7 +18,7 @@ namespace {
 constexpr int DH = 32;     // head_dim served by this kernel
 constexpr int KB = 16;     // keys per block (the k extent of one P.V MMA)
 constexpr int NR = 4;      // V ring slots per warp
-constexpr int PITCH = 80;  // bytes per staged V row: 64 of data + 16 of padding (conflict-free ldmatrix)
+constexpr int PITCH = 144; // bytes per staged key: K row (64) + V row (64) + 16 of padding (conflict-free ldmatrix)
 constexpr int WPB = 4;     // warps per CTA
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -31,6 +32,12 @@ __device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a2
 }
 __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t saddr, uint32_t (&r)[4]) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(saddr)
+               : "memory");
+}
+__device__ __forceinline__ void ldmatrix_x4(uint32_t saddr, uint32_t (&r)[4]) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
                : "r"(saddr)
                : "memory");
@@ -98,34 +105,21 @@ __global__ void __launch_bounds__(WPB * 32, 6) buf_mma_kernel(const BufMergeArgs
   const float sc = a.scale * kLog2e;
   const int nblk = (len + KB - 1) / KB;
 
-  // V rows of block kb -> ring slot kb % NR: 16 keys x 4 chunks of 16 bytes, two chunks per lane
+  // K and V rows of block kb -> ring slot kb % NR: 16 keys x 8 chunks of 16 bytes (a key's K row and
+  // V row are adjacent in memory), four chunks per lane, fully coalesced
   const uint32_t vs_base = smem_u32(&vs[warp][0][0]);
-  auto stage_v = [&](int kb) {
+  auto stage = [&](int kb) {
     if (kb < nblk) {
 #pragma unroll
-      for (int i = 0; i < 2; ++i) {
-        const int c = lane * 2 + i, key = c >> 2, part = c & 3;
+      for (int i = 0; i < 4; ++i) {
+        const int c = i * 32 + lane, key = c >> 3, part = c & 7;
         const int gkey = kb * KB + key;
         const bool valid = gkey < len;
-        const __nv_bfloat16* src = kv + (valid ? ((size_t)gkey * 2 * DH + DH + part * 8) : 0);
+        const __nv_bfloat16* src = kv + (valid ? ((size_t)gkey * 2 * DH + part * 8) : 0);
         cp_async16(vs_base + (uint32_t)((kb % NR) * (KB * PITCH) + key * PITCH + part * 16), src, valid);
       }
     }
     cp_async_commit();  // one group per call, empty or not: the wait below counts groups
-  };
-  // B fragments of K^T for block kb: [8-key tile][k-step][b0, b1]; key = tile * 8 + g, columns like A
-  auto load_k = [&](int kb, uint32_t (&kf)[2][2][2]) {
-#pragma unroll
-    for (int nt = 0; nt < 2; ++nt) {
-      const int key = kb * KB + nt * 8 + g;
-      const bool valid = key < len;
-      const uint32_t* kp = reinterpret_cast<const uint32_t*>(kv + (size_t)(valid ? key : 0) * 2 * DH) + t4;
-#pragma unroll
-      for (int ks = 0; ks < 2; ++ks) {
-        kf[nt][ks][0] = valid ? __ldg(kp + 8 * ks) : 0u;
-        kf[nt][ks][1] = valid ? __ldg(kp + 8 * ks + 4) : 0u;
-      }
-    }
   };
 
   float m = -INFINITY, l = 0.f;
@@ -135,24 +129,27 @@ __global__ void __launch_bounds__(WPB * 32, 6) buf_mma_kernel(const BufMergeArgs
 #pragma unroll
     for (int e = 0; e < 4; ++e) o[j][e] = 0.f;
 
-  uint32_t kf[2][2][2];
 #pragma unroll
-  for (int i = 0; i < NR - 1; ++i) stage_v(i);
-  if (nblk > 0) load_k(0, kf);
+  for (int i = 0; i < NR - 1; ++i) stage(i);
+  const int mi = lane >> 3, r8 = lane & 7;  // ldmatrix: lane -> (matrix, row) whose address it supplies
 
   for (int kb = 0; kb < nblk; ++kb) {
-    uint32_t kn[2][2][2];
-    if (kb + 1 < nblk) load_k(kb + 1, kn);
-    stage_v(kb + NR - 1);  // into the slot read in the previous iteration (its ldmatrix results were consumed)
+    stage(kb + NR - 1);  // into the slot read in the previous iteration (its fragments were consumed)
+    cp_async_wait<NR - 1>();  // block kb has landed once all but the NR - 1 newest groups are complete
+    __syncwarp();
+    const uint32_t slot = vs_base + (uint32_t)((kb % NR) * (KB * PITCH));
 
-    // scores of 16 keys for the two queries
+    // Scores of 16 keys for the two queries.  B fragments of K^T = plain ldmatrix of [8 keys][8 dims]
+    // blocks; the four matrices of a call are dims 0-7, 8-15 (k-step 0) and 16-23, 24-31 (k-step 1).
     float s[2][4];
 #pragma unroll
     for (int nt = 0; nt < 2; ++nt) {
+      uint32_t kf[4];
+      ldmatrix_x4(slot + (uint32_t)((nt * 8 + r8) * PITCH + mi * 16), kf);
 #pragma unroll
       for (int e = 0; e < 4; ++e) s[nt][e] = 0.f;
-#pragma unroll
-      for (int ks = 0; ks < 2; ++ks) mma_bf16(s[nt], qa[ks][0], qa[ks][1], kf[nt][ks][0], kf[nt][ks][1]);
+      mma_bf16(s[nt], qa[0][0], qa[0][1], kf[0], kf[1]);
+      mma_bf16(s[nt], qa[1][0], qa[1][1], kf[2], kf[3]);
     }
     // this lane's four scores of row g: keys kb*16 + nt*8 + t4*2 + {0, 1}
     const int key0 = kb * KB + t4 * 2;
@@ -180,30 +177,16 @@ __global__ void __launch_bounds__(WPB * 32, 6) buf_mma_kernel(const BufMergeArgs
     const uint32_t ph0 = pack_bf16(p[0], p[1]), ph1 = pack_bf16(p[2], p[3]);
     const uint32_t pl0 = pack_bf16(p[0] - __uint_as_float(ph0 << 16), p[1] - __uint_as_float(ph0 & 0xffff0000u));
     const uint32_t pl1 = pack_bf16(p[2] - __uint_as_float(ph1 << 16), p[3] - __uint_as_float(ph1 & 0xffff0000u));
-
-    // V block kb has landed once all but the NR - 1 newest groups are complete
-    cp_async_wait<NR - 1>();
-    __syncwarp();
-    const uint32_t slot = vs_base + (uint32_t)((kb % NR) * (KB * PITCH));
-    const int mi = lane >> 3, r8 = lane & 7;
 #pragma unroll
     for (int c = 0; c < 2; ++c) {
-      // matrices: (dim tile 2c, keys 0-7), (2c, keys 8-15), (2c+1, keys 0-7), (2c+1, keys 8-15)
+      // V fragments (ldmatrix.trans of [8 keys][8 dims] blocks of the V half of the staged rows):
+      // (dim tile 2c, keys 0-7), (2c, keys 8-15), (2c+1, keys 0-7), (2c+1, keys 8-15)
       uint32_t vb[4];
-      ldmatrix_x4_trans(slot + (uint32_t)(((mi & 1) * 8 + r8) * PITCH + (2 * c + (mi >> 1)) * 16), vb);
+      ldmatrix_x4_trans(slot + (uint32_t)(((mi & 1) * 8 + r8) * PITCH + 64 + (2 * c + (mi >> 1)) * 16), vb);
       mma_bf16(o[2 * c], ph0, ph1, vb[0], vb[1]);
       mma_bf16(o[2 * c], pl0, pl1, vb[0], vb[1]);
       mma_bf16(o[2 * c + 1], ph0, ph1, vb[2], vb[3]);
       mma_bf16(o[2 * c + 1], pl0, pl1, vb[2], vb[3]);
-    }
-    if (kb + 1 < nblk) {
-#pragma unroll
-      for (int nt = 0; nt < 2; ++nt)
-#pragma unroll
-        for (int ks = 0; ks < 2; ++ks) {
-          kf[nt][ks][0] = kn[nt][ks][0];
-          kf[nt][ks][1] = kn[nt][ks][1];
-        }
     }
   }
   cp_async_wait<0>();
