@@ -233,10 +233,10 @@ DenseArgs dense_base(const artab_model* m, const artab_state* st, int rows) {
   d.lane_major = chain_on_tc(m, st);
   // the context-partial workspace is idle while a dense chain runs: its first two slots serve the
   // CTA pairs' exchange
-  if (st->max_splits >= 2) {
+  if (st->max_splits >= 6) {
     d.pair_scratch = st->o_part;
     d.pair_slot_stride = (size_t)st->max_rows * m->d_model;
-    d.pair_slots = st->max_splits >= 4 ? 4 : 2;
+    d.pair_slots = st->max_splits;
   }
   fill_head(m, d);
   return d;

@@ -46,7 +46,7 @@ struct DenseArgs {
   // (>= rows rounded up to 128, times D, each); null: one CTA per row tile
   float* pair_scratch;
   size_t pair_slot_stride;
-  int pair_slots;      // slots available in pair_scratch (2: layer MLP only, 4: head MLP too)
+  int pair_slots;      // slots in pair_scratch; a pair uses 6: MLP exchange (0, 1), head exchange (2, 3), parking (4, 5)
   const void *tc_wa, *tc_wb;  // tensor-core tiles of the head matrices (null: fp32 chain)
   int tc_head_lo;
 };

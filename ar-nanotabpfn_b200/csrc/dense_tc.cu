@@ -217,7 +217,6 @@ struct __align__(1024) Smem {
   uint64_t w_full[2][NSLOT], w_empty[2][NSLOT];
   uint64_t ep_done, acc_full, h_full, acch_free, ah_ready, ah_free;
   uint64_t x_full;   // CTA pair: the peer's MLP partial sums have been written to the global scratch
-  uint64_t in_done;  // the peer has read its inputs (its residual input aliases our parking buffer)
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -638,7 +637,6 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const DenseArgs a
     mbar_init(&sm->ah_ready, kEpi);
     mbar_init(&sm->ah_free, 1);
     mbar_init(&sm->x_full, kEpi);
-    mbar_init(&sm->in_done, kEpi / 32);
     sm->abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -675,8 +673,8 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const DenseArgs a
 
   const int lo_post = a.post_w.tc_lo, lo_pre = a.pre_w.tc_lo;
   const int n_mine = (nt - (int)crank + (int)csize - 1) / (int)csize;  // hidden tiles of the layer MLP done here
-  // the head MLP is shared the same way when the scratch has room for a second exchange
-  const bool head_pair = csize > 1 && a.pair_slots >= 4;
+  // the head MLP is shared the same way (second exchange, its own scratch slots)
+  const bool head_pair = csize > 1;
   const int h_first = head_pair ? (int)crank : 0, h_step = head_pair ? (int)csize : 1;
   const int h_mine = head_pair ? n_mine : nt;
 
@@ -796,21 +794,17 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const DenseArgs a
       e.add_acc(v);
       e.layer_norm(v, sm->vec[0], sm->vec[1]);   // v = x2
       e.publish_ax(v);
-      // x2 is the residual of the last LayerNorm; it waits in this thread's own slice of the x1
-      // workspace (free until the next layer writes it) so that the MLP epilogue has the registers.
-      // In a CTA pair the peer parks the same values at the same place, which is also where both
-      // read their residual input: park only once the peer has consumed its inputs.
-      if (csize > 1) {
-        __syncwarp();
-        if (lane == 0) mbar_arrive_remote(map_to_rank(smem_u32(&sm->in_done), crank ^ 1u));
-        e.ok = mbar_wait_cluster(&sm->in_done, 0, &sm->abort_flag) && e.ok;
-      }
-      store_lm(a.x1_out);
+      // x2 is the residual of the last LayerNorm; it waits in this thread's own slice of a workspace
+      // so that the MLP epilogue has the registers: the x1 workspace (free until the next layer
+      // writes it), or, in a CTA pair, this CTA's own slot of the pair scratch — the peer reads its
+      // residual input from the x1 workspace at its own pace.
+      float* park = csize > 1 ? a.pair_scratch + (size_t)(4 + crank) * a.pair_slot_stride : a.x1_out;
+      store_lm(park);
       {
         int jl = 0;
         for (int j = crank; j < nt; j += csize, ++jl) e.hidden_tile(jl, j, sm->bias_h);
       }
-      load_lm(a.x1_out);
+      load_lm(park);
       e.wait_acc();
       e.drain_free();
 #pragma unroll
@@ -1026,7 +1020,8 @@ int launch_dense_tc(const DenseArgs& a, cudaStream_t s) {
   // Few row tiles (a decode step): the chain's latency is what counts, so a CTA pair shares each
   // tile.  Many tiles (prefill, teacher forcing): one CTA per tile keeps every SM on its own rows.
   static const bool allow_pair = !(getenv("ARTAB_DENSE_PAIR") && getenv("ARTAB_DENSE_PAIR")[0] == '0');
-  const unsigned csize = (allow_pair && a.pair_scratch && 2 * tiles <= kPairMaxCtas && a.Dff / HT >= 2) ? 2u : 1u;
+  const unsigned csize =
+      (allow_pair && a.pair_scratch && a.pair_slots >= 6 && 2 * tiles <= kPairMaxCtas && a.Dff / HT >= 2) ? 2u : 1u;
   const int grid = tiles * (int)csize;
   cudaError_t e = cudaSuccess;
   static bool configured[3] = {false, false, false};
