@@ -875,8 +875,8 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const DenseArgs a
       e.wait_acc();
       e.add_acc(v);
       e.layer_norm(v, sm->vec[5], sm->vec[6]);     // v = x1
-      store_lm(a.x1_out);
-      e.publish_ax(v);
+      e.publish_ax(v);       // the Q projection's MMAs start on this ...
+      store_lm(a.x1_out);    // ... while the residual for the next launch drains to memory
       // q, k, v projections, one accumulator round each.  Destinations of this row's K / V are
       // resolved once (no per-element division): context cache rows during prefill, the private
       // buffer slot (in-place append) otherwise.

@@ -295,8 +295,8 @@ def main():
             roof = {"kernel": "dense_tc_kernel" if tc else "dense_chain_kernel", "bound": "tensor",
                     "achieved": ach, "peak": peak, "unit": "TFLOP/s", "frac": ach / peak,
                     "traffic": DENSE_TC_DRAM_BYTES_PER_LAUNCH if tc else None,
-                    "note": ("tcgen05 chain, 8 CTAs of 128 rows per decode launch: bound by the latency of "
-                             "the dependent GEMM/LayerNorm chain inside one CTA, not by the tensor pipe"
+                    "note": ("tcgen05 chain, 8 row tiles of 128 rows (16 CTAs in pairs) per decode launch: bound by the "
+                             "latency of the dependent GEMM/LayerNorm chain of a row tile, not by the tensor pipe"
                              if tc else "fp32 FMA kernel measured against the bf16 tensor peak")
                             + (" (of measured)" if peaks else " (of fallback)")}
         elif dom == "context_attention":
@@ -312,7 +312,7 @@ def main():
             byts = sum(range(1, NT)) * STREAMS * H * 32 * 2 * esz * L * 1.0
             peak = peaks.get("hbm_gbs", 6650.0)
             ach = byts / (shares[dom]["ms"] * 1e-3) / 1e9
-            roof = {"kernel": "buf_merge_kernel", "bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s",
+            roof = {"kernel": "buf_mma_kernel" if args.precision == "bf16" else "buf_merge_kernel", "bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s",
                     "frac": ach / peak, "traffic": None, "note": "of measured" if peaks else "of fallback"}
         line = {
             "metric": "ar_targets_decoded_per_sec", "value": targets / (ms_dev * 1e-3), "unit": "targets/s",
