@@ -40,7 +40,7 @@ CFG = dict(d_model=192, n_heads=6, n_layers=6, d_ff=768, num_features=20, buffer
 NC, NT, STREAMS, SEED = 1024, 128, 512, 2
 # DRAM bytes (read + write) of one decode-step launch of the tensor-core dense chain at this
 # workload, from the ncu capture summarised in profiles/dense_tc_kernel_config3.md
-DENSE_TC_DRAM_BYTES_PER_LAUNCH = 2.873e6   # captured on a 512-row launch (4 CTAs); weight tiles dominate
+DENSE_TC_DRAM_BYTES_PER_LAUNCH = 3.657e6   # 1024-row decode launch (8 row tiles, 16 CTAs); weight tiles dominate
 CPU_SAMPLE = dict(streams=128, targets=16)  # bounded CPU sample of the same workload
 
 
