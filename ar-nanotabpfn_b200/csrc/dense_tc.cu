@@ -646,25 +646,6 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const DenseArgs a
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
-  // small per-column vectors -> shared memory (read by every epilogue thread, many times)
-  for (int i = threadIdx.x; i < D; i += kThreads) {
-    if (a.do_post) {
-      sm->vec[0][i] = a.post_w.ln2_g[i];
-      sm->vec[1][i] = a.post_w.ln2_b[i];
-      sm->vec[2][i] = a.post_w.b2[i];
-      sm->vec[3][i] = a.post_w.ln3_g[i];
-      sm->vec[4][i] = a.post_w.ln3_b[i];
-    }
-    if (a.do_final) {
-      sm->vec[5][i] = a.lnf_g[i];
-      sm->vec[6][i] = a.lnf_b[i];
-    } else if (a.do_pre) {
-      sm->vec[5][i] = a.pre_w.ln1_g[i];
-      sm->vec[6][i] = a.pre_w.ln1_b[i];
-    }
-  }
-  if (a.do_post)
-    for (int i = threadIdx.x; i < a.Dff; i += kThreads) sm->bias_h[i] = a.post_w.b1[i];
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -782,6 +763,26 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const DenseArgs a
         *reinterpret_cast<float4*>(dst + goff + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
     };
 
+    // Small per-column vectors -> shared memory (read by every epilogue thread, many times).  The
+    // loads are issued now and consumed behind the first GEMM: their latency hides under it.
+    for (int i = threadIdx.x - 64; i < D; i += kEpi) {
+      if (a.do_post) {
+        sm->vec[0][i] = a.post_w.ln2_g[i];
+        sm->vec[1][i] = a.post_w.ln2_b[i];
+        sm->vec[2][i] = a.post_w.b2[i];
+        sm->vec[3][i] = a.post_w.ln3_g[i];
+        sm->vec[4][i] = a.post_w.ln3_b[i];
+      }
+      if (a.do_final) {
+        sm->vec[5][i] = a.lnf_g[i];
+        sm->vec[6][i] = a.lnf_b[i];
+      } else if (a.do_pre) {
+        sm->vec[5][i] = a.pre_w.ln1_g[i];
+        sm->vec[6][i] = a.pre_w.ln1_b[i];
+      }
+    }
+    if (a.do_post)
+      for (int i = threadIdx.x - 64; i < a.Dff; i += kEpi) sm->bias_h[i] = a.post_w.b1[i];
     // Everything above (and the weight producers' first tiles) needed nothing from the preceding
     // kernel; the activations do.
     dep_wait();
@@ -791,6 +792,7 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const DenseArgs a
       e.publish_ax(v);
       load_lm(a.x1_in);                          // residual
       e.wait_acc();
+      e.sync_groups();                           // the staged vectors are complete
       e.add_acc(v);
       e.layer_norm(v, sm->vec[0], sm->vec[1]);   // v = x2
       e.publish_ax(v);
@@ -818,6 +820,7 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const DenseArgs a
       if (a.x_out && crank == 0) store_row(a.x_out);
     } else {
       load_row(a.x_in);
+      e.sync_groups();                           // the staged vectors are complete
     }
     if (a.do_final) {
       e.layer_norm(v, sm->vec[5], sm->vec[6]);                 // v = z
