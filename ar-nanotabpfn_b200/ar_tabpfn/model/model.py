@@ -161,11 +161,16 @@ class MixtureGaussianHead(nn.Module):
         return cached[1]
 
     def sample(self, z: Tensor, num_samples: int = 1) -> Tensor:
-        """z [B,T,D] -> [B,T,1,1].  Consumes torch's generator exactly like the
-        reference: one Exp(1) fill of [B*T,K] (inside torch.multinomial) followed by
-        one N(0,1) fill of [B,T,1,1]."""
-        if num_samples != 1:
-            raise NotImplementedError("num_samples = 1 only")
+        """z [B,T,D] -> [B,T,num_samples,1].  With num_samples = 1 (what the sampler uses) torch's
+        generator is consumed exactly like the reference: one Exp(1) fill of [B*T,K] (inside
+        torch.multinomial) followed by one N(0,1) fill of [B,T,1,1].  num_samples > 1 draws the
+        samples one after the other in that same pattern: the distribution is the reference's
+        (model.py:251-266), the random stream is not (the reference's multinomial takes another
+        route for several samples)."""
+        if num_samples < 1:
+            raise ValueError("num_samples must be >= 1")
+        if num_samples > 1:
+            return torch.cat([self.sample(z, 1) for _ in range(num_samples)], dim=2)
         import ctypes as C
         lib = _lib.lib()
         B, T, D = z.shape

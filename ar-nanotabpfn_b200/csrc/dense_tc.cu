@@ -117,10 +117,6 @@ __device__ __forceinline__ uint32_t map_to_rank(uint32_t saddr, uint32_t rank) {
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(saddr), "r"(rank));
   return r;
 }
-__device__ __forceinline__ void st_remote_f4(uint32_t raddr, float x, float y, float z, float w) {
-  asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(raddr), "f"(x), "f"(y), "f"(z), "f"(w)
-               : "memory");
-}
 __device__ __forceinline__ void mbar_arrive_remote(uint32_t raddr) {  // releases this thread's earlier stores
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(raddr) : "memory");
 }

@@ -141,3 +141,9 @@ def test_embedder_and_head_vs_oracle():
     mean, std, w, _ = orc.head_params(sd, z)
     want, _ = orc.head_sample(mean, std, w, expo.cpu().view(B, T, 5), normal.cpu().view(B, T))
     torch.testing.assert_close(ys.cpu().view(B, T), want, atol=1e-5, rtol=1e-5)
+    # several samples per position: reference shape [B,T,num_samples,1]; the first draw replays the stream above
+    torch.manual_seed(3)
+    y3 = m.head.sample(z.cuda(), num_samples=3)
+    assert y3.shape == (B, T, 3, 1) and torch.isfinite(y3).all()
+    torch.testing.assert_close(y3[:, :, 0, 0].cpu(), want, atol=1e-5, rtol=1e-5)
+    assert not torch.equal(y3[:, :, 0], y3[:, :, 1])
