@@ -3,7 +3,7 @@
 // Queries of every sample stream are stacked into 128-row M tiles and contracted
 // against the shared context K/V: S = Q.K^T and O = P.V are tcgen05.mma
 // instructions with the accumulators in tensor memory (TMEM); Q, K and V^T tiles
-// arrive in shared memory by TMA (plain loads, no cluster multicast) in the
+// arrive in shared memory by TMA (plain per-CTA loads) in the
 // swizzled K-major layouts the MMA descriptors name.  Softmax runs on four warps
 // that own one query row per thread (TMEM lane == row), keeps the running
 // max / sum / output in registers and hands P back to the tensor core through
