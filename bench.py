@@ -42,6 +42,10 @@ NC, NT, STREAMS, SEED = 1024, 128, 512, 2
 # workload, from the ncu capture summarised in profiles/dense_tc_kernel_config3.md
 DENSE_TC_DRAM_BYTES_PER_LAUNCH = 3.657e6   # 1024-row decode launch (8 row tiles, 16 CTAs); weight tiles dominate
 CPU_SAMPLE = dict(streams=128, targets=16)  # bounded CPU sample of the same workload
+WORKLOAD_CONFIG = {"workload": "config3: 6L d192 h6 ff768, ctx 1024x20, 128 targets, 512 streams/GPU, "
+                               "shared context KV, prefill included in every step",
+                   "streams_per_gpu": STREAMS, "targets": NT, "context_rows": NC,
+                   "l2": "256 MB buffer written between timed iterations; KV working set 288 MiB > L2"}
 
 
 def make_dataset(seed, n_rows, n_feat, hidden=32, noise=0.1):
@@ -162,7 +166,7 @@ def run_reference_arm(args):
         "impl": "reference", "metric": "ar_targets_decoded_per_sec", "value": rate, "unit": "targets/s",
         "n_gpus": args.gpus, "steps": max(1, min(args.steps, 3)), "warmup": 1, "ms_per_step": per * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "config3: 6L d192 h6 ff768, ctx 1024x20, 128 targets, 512 streams/GPU"},
+        "config": WORKLOAD_CONFIG,
         "cpu_baseline": {"value": rate, "unit": "targets/s", "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": rate, "unit": "targets/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
@@ -319,10 +323,7 @@ def main():
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_dev,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "bf16" if args.precision == "bf16" else "f32", "data": "synthetic",
-            "config": {"workload": "config3: 6L d192 h6 ff768, ctx 1024x20, 128 targets, 512 streams/GPU, "
-                                   "shared context KV, prefill included in every step",
-                       "streams_per_gpu": STREAMS, "targets": NT, "context_rows": NC,
-                       "l2": "256 MB buffer written between timed iterations; KV working set 288 MiB > L2"},
+            "config": WORKLOAD_CONFIG,
             "e2e": {"value": targets / (ms_e2e * 1e-3), "unit": "targets/s",
                     "h2d_bytes_per_step": (xc_h.numel() + yc_h.numel() + xt_h.numel()) * 4,
                     "d2h_bytes_per_step": 2 * STREAMS * NT * 4, "ms_per_step": ms_e2e},
