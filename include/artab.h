@@ -144,7 +144,9 @@ typedef struct artab_state {
   float* x1;            /* [max_rows][D] post-norm1 activations */
   float* attn;          /* [max_rows][D] merged attention output */
   void* q;              /* [max_rows][H][Dh] queries, cache dtype */
-  float* o_part;        /* [max_splits][max_rows][H][Dh] context partial outputs */
+  float* o_part;        /* [max_splits][max_rows][H][Dh] context partial outputs; between the attention
+                         * stages the tensor-core dense chain uses slots 0-5 as scratch for its CTA
+                         * pairs (max_splits < 6: one CTA per row tile) */
   float* lse_part;      /* [max_splits][max_rows][H] natural-log LSE of each partial */
   int32_t* status;      /* device word: 0, or the code of a bounded wait that gave up */
 } artab_state;
