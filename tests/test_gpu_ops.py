@@ -97,6 +97,26 @@ def test_hybrid_bf16_vs_fp32_torch(tk, shape):
     torch.testing.assert_close(lse_c, want_l, atol=2e-3, rtol=2e-3)
 
 
+@pytest.mark.parametrize("shape", [(3, 2, 37, 100, 32), (2, 6, 128, 260, 32), (2, 2, 9, 50, 16)])
+def test_teacher_forcing_bf16_vs_fp32_torch(tk, shape):
+    """bf16 mode, block-causal buffer visibility (buffer query i sees buffer keys <= i, target query i
+    sees buffer keys < i; target 0 sees the context only): within 1e-2 relative of masked fp32 attention."""
+    B, H, Nt, Nc, Dh = shape
+    g = torch.Generator().manual_seed(7)
+    q = torch.randn(B, H, 2 * Nt, Dh, generator=g).bfloat16().cuda()
+    k, v = (torch.randn(H, Nc, Dh, generator=g).bfloat16().cuda() for _ in range(2))
+    kb, vb = (torch.randn(B, H, Nt, Dh, generator=g).bfloat16().cuda() for _ in range(2))
+    got = tk.hybrid_teacher_forcing_attention(q, k, v, kb, vb, Nt).float()
+    i = torch.arange(Nt, device="cuda")
+    buf_vis = torch.cat([i[:, None] >= i[None, :], i[:, None] > i[None, :]], dim=0)      # [2Nt, Nt]
+    mask = torch.cat([torch.ones(2 * Nt, Nc, dtype=torch.bool, device="cuda"), buf_vis], dim=1)
+    kf = torch.cat([k.unsqueeze(0).expand(B, -1, -1, -1), kb], dim=2)
+    vf = torch.cat([v.unsqueeze(0).expand(B, -1, -1, -1), vb], dim=2)
+    want, _ = ref_attention(q, kf, vf, mask=mask)
+    err = (got - want).abs().max() / want.abs().max()
+    assert err < 1e-2, err
+
+
 def test_kv_append_in_place():
     import ctypes as C
     from ar_tabpfn import _lib
