@@ -4,20 +4,23 @@
 // against the shared context K/V: S = Q.K^T and O = P.V are tcgen05.mma
 // instructions with the accumulators in tensor memory (TMEM); Q, K and V^T tiles
 // arrive in shared memory by TMA (plain per-CTA loads) in the
-// swizzled K-major layouts the MMA descriptors name.  Softmax runs on four warps
-// that own one query row per thread (TMEM lane == row), keeps the running
-// max / sum / output in registers and hands P back to the tensor core through
-// TMEM (P aliases the S columns as packed bf16).
+// swizzled K-major layouts the MMA descriptors name.  Softmax runs on two warpgroups
+// that split a key tile's 128 score columns and own one query row per thread
+// (TMEM lane == row); the running max / sum / output stay in registers and P goes
+// back to the tensor core through its own TMEM columns as packed bf16.  V is kept as
+// a bf16 hi part and a bf16 lo part, so O = P.[V_hi | V_lo] has 64 columns.
 //
 // One CTA = one (M tile, head, context group, key split).  Warp 0 issues TMA,
-// warp 1 issues MMA and owns the TMEM allocation, warps 2-5 do softmax.  Two
-// CTAs are resident per SM (256 TMEM columns each), so the MMA of one overlaps
-// the softmax of the other.  Every mbarrier wait is bounded: on expiry the CTA
-// raises its abort flag, records a code in the status word, drains its own
-// copies, frees its TMEM and returns.
+// warp 1 issues MMA and owns the TMEM allocation, warps 2-5 and 6-9 do softmax.
+// The next tile's Q.K^T is issued as soon as every softmax thread has its scores in
+// registers, so it overlaps the exponentials; P has one buffer, so it is rewritten only
+// once the previous P.V has completed.  Two CTAs are resident per SM (256 TMEM
+// columns each), so the MMA of one overlaps the softmax of the other.  Every mbarrier
+// wait is bounded: on expiry the CTA raises its abort flag, records a code in the
+// status word, drains its own copies, frees its TMEM and returns.
 //
 // Output per (split, row, head): normalised O [32] fp32 and the natural-log LSE,
-// merged later with the private-buffer pass (buf_merge_kernel).
+// merged later with the private-buffer pass (buf_mma_kernel / buf_merge_kernel).
 #include <cuda.h>
 
 #include "attn.cuh"
