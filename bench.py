@@ -39,7 +39,7 @@ import torch  # noqa: E402
 CFG = dict(d_model=192, n_heads=6, n_layers=6, d_ff=768, num_features=20, buffer_size=8, num_components=5)
 NC, NT, STREAMS, SEED = 1024, 128, 512, 2
 # DRAM bytes (read + write) of one decode-step launch of the tensor-core dense chain at this
-# workload, from the ncu capture summarised in profiles/dense_tc_kernel_config3.md
+# workload, from the ncu capture of that kernel summarised under profiles/
 DENSE_TC_DRAM_BYTES_PER_LAUNCH = 3.657e6   # 1024-row decode launch (8 row tiles, 16 CTAs); weight tiles dominate
 CPU_SAMPLE = dict(streams=128, targets=16)  # bounded CPU sample of the same workload
 WORKLOAD_CONFIG = {"workload": "config3: 6L d192 h6 ff768, ctx 1024x20, 128 targets, 512 streams/GPU, "

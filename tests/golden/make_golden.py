@@ -156,7 +156,9 @@ def compact(o):
 
 
 def main():
-    root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: make_golden.py <path to the reference checkout>")
+    root = sys.argv[1]
     ref, tk = import_reference(root)
     torch.set_num_threads(8)
     torch.save(compact(ops_fixture(tk)), os.path.join(HERE, "ops.pt"))
