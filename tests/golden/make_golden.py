@@ -36,7 +36,7 @@ def import_reference(root: str):
 
 
 def xavier_model(ref, seed, **kw):
-    """BASELINE config-1 style model: reference defaults + Xavier-uniform on
+    """Small CPU-sized model of the first benchmark configuration: reference defaults + Xavier-uniform on
     every nn.Linear weight."""
     torch.manual_seed(seed)
     m = ref.ARTabPFN(**kw).eval()
