@@ -74,7 +74,7 @@ __device__ __forceinline__ void sync_compute(int n_threads) { asm volatile("bar.
 
 // columns-per-thread / k-split plan for an [R x K] . [K x N] product on T threads
 __host__ __device__ inline void plan_gemm(int N, int T, int& cpt, int& ksplit) {
-  for (cpt = 4; cpt >= 1; --cpt) {
+  for (cpt = 4; cpt >= 1; --cpt) {  // every thread busy: the column groups divide the threads
     if (N % cpt) continue;
     const int cols = N / cpt;
     if (cols <= T && T % cols == 0 && T / cols <= 4) {
@@ -82,8 +82,15 @@ __host__ __device__ inline void plan_gemm(int N, int T, int& cpt, int& ksplit) {
       return;
     }
   }
-  cpt = 1;      // narrow outputs (the head's 3K columns): threads beyond N idle
   ksplit = 1;
+  for (cpt = 1; cpt <= 4; ++cpt)    // otherwise the fewest columns per thread that cover N; the rest idle
+    if (N % cpt == 0 && N / cpt <= T) return;
+  cpt = 1;  // N > 4 T or no divisor: refused on the host (gemm_plan_ok)
+}
+__host__ __device__ inline bool gemm_plan_ok(int N, int T) {
+  int cpt, ks;
+  plan_gemm(N, T, cpt, ks);
+  return N % cpt == 0 && N / cpt <= T && (size_t)4 * ks * N * sizeof(float) <= (size_t)kBufBytes;
 }
 
 // rows of W per slab: as many as fit a ring slot, a multiple of 4 per k-group
@@ -505,6 +512,13 @@ int launch_dense(const DenseArgs& a, cudaStream_t s) {
                 "dense chain: d_model must be a multiple of 32 and d_ff a multiple of 4 (got %d, %d)", a.D, a.Dff);
   ARTAB_REQUIRE(3 * a.n_comp <= a.D && a.n_comp <= 32, ARTAB_EINVAL, "dense chain: need 3*K <= d_model and K <= 32");
   ARTAB_REQUIRE(a.D % 16 == 0 && a.Dff % 16 == 0, ARTAB_EINVAL, "dense chain: d_model and d_ff must be multiples of 16");
+  {
+    const int T = a.D <= 256 ? a.D : 256;
+    ARTAB_REQUIRE(gemm_plan_ok(a.D, T) && gemm_plan_ok(3 * a.D, T) && gemm_plan_ok(a.Dff, T) &&
+                      gemm_plan_ok(3 * a.n_comp, T),
+                  ARTAB_EINVAL, "dense chain: no thread plan for d_model %d, d_ff %d (d_ff must be at most %d)", a.D,
+                  a.Dff, 4 * T);
+  }
   const int wide = 3 * a.D > a.Dff ? 3 * a.D : a.Dff;
   const size_t smem = (size_t)kNBuf * kBufBytes + (size_t)kRows * (2 * a.D + wide + 3 * a.D) * sizeof(float) +
                       sizeof(Stream) + 128;

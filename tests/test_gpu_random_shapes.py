@@ -1,0 +1,98 @@
+"""Seeded sweep over model and problem shapes: joint log density of the CUDA path against the
+CPU oracle, both precisions, both backends.  The shapes are picked to hit the dispatch edges:
+head sizes 16 / 32 / 64 (tensor-core and scalar attention kernels), MLP widths that do and do not
+allow CTA pairs or the tensor-core chain at all, context lengths around the 8- and 128-key
+granules, buffers around the 16-key MMA block, row counts around the 128-row tile."""
+import pytest
+import torch
+
+import artab_oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+CASES = [
+    # d_model, heads, layers, d_ff, F, Nc, Nt, B
+    (64, 2, 2, 128, 5, 9, 3, 4),        # Dh 32, one hidden tile (no pair), tiny
+    (64, 4, 1, 256, 3, 131, 17, 7),     # Dh 16 (scalar attention), tensor-core chain with pairs
+    (128, 4, 2, 256, 8, 64, 33, 5),     # Dh 32, buffer crosses two MMA blocks, context = half a key tile
+    (128, 2, 1, 384, 12, 257, 16, 3),   # Dh 64 (scalar attention), context just over two key tiles
+    (192, 6, 2, 768, 20, 300, 24, 11),  # the benchmark's layer shape
+    (192, 6, 1, 640, 7, 40, 65, 2),     # odd number of hidden tiles in a pair
+    (96, 3, 1, 192, 4, 50, 9, 6),       # d_model outside the tensor-core chain: fp32 dense kernel with bf16 caches
+]
+
+
+def _problem(seed, cfg, Nc, Nt, B, shared):
+    import ar_tabpfn
+    torch.manual_seed(seed)
+    m = ar_tabpfn.ARTabPFN(**cfg).eval()
+    with torch.no_grad():
+        for mod in m.modules():
+            if isinstance(mod, torch.nn.Linear):
+                torch.nn.init.xavier_uniform_(mod.weight)
+        for p in m.parameters():
+            p.copy_(p.to(torch.bfloat16).float())
+            p.requires_grad_(False)
+    sd = {k: v.clone() for k, v in m.state_dict().items()}
+    F = cfg["num_features"]
+    if shared:
+        x, y = orc.make_dataset(seed, Nc + Nt, F)
+        x, y = x.expand(B, -1, -1).contiguous(), y.expand(B, -1).contiguous()
+    else:
+        xs, ys = zip(*[orc.make_dataset(seed * 100 + b, Nc + Nt, F) for b in range(B)])
+        x, y = torch.stack(xs), torch.stack(ys)
+    r = lambda t: t.to(torch.bfloat16).float()
+    x, y = r(x), r(y)
+    return m, sd, x[:, :Nc].contiguous(), y[:, :Nc].contiguous(), x[:, Nc:].contiguous(), y[:, Nc:].contiguous()
+
+
+@pytest.mark.parametrize("case", CASES, ids=lambda c: "d%d_h%d_l%d_ff%d_F%d_nc%d_nt%d_b%d" % c)
+def test_joint_density_against_oracle(case):
+    from ar_tabpfn.model import ARTabPFNPredictor
+    D, H, L, Dff, F, Nc, Nt, B = case
+    cfg = dict(d_model=D, n_heads=H, n_layers=L, d_ff=Dff, num_features=F, buffer_size=8, num_components=5)
+    for shared, backend in ((True, "triton_shared_context"), (False, "flex_attention")):
+        m, sd, xc, yc, xt, yt = _problem(11 + D + Nc, cfg, Nc, Nt, B, shared)
+        want = orc.OraclePredictor(sd, H).evaluate_joint_density(xc, yc, xt, yt, shared=shared)
+        # what the arithmetic itself costs on these inputs: fp32 against fp64 (ill-conditioned targets
+        # with sharp mixture components amplify rounding), and bf16 q/k/v + bf16 P emulated on the CPU
+        d = lambda t: t.double()
+        want64 = orc.OraclePredictor({k: d(v) for k, v in sd.items()}, H).evaluate_joint_density(
+            d(xc), d(yc), d(xt), d(yt), shared=shared)
+        noise32 = (want.double() - want64).abs().float()
+        emu = orc.OraclePredictor(sd, H, orc.Emulation(qkv=True, p=True)).evaluate_joint_density(
+            xc, yc, xt, yt, shared=shared)
+        inherent = (emu - want).abs()
+        mc = m.cuda()
+        for prec in ("fp32", "bf16"):
+            p = ARTabPFNPredictor.from_trained_model(mc, backend=backend, precision=prec)
+            got = p.evaluate_joint_density(xc.cuda(), yc.cuda(), xt.cuda(), yt.cuda()).cpu()
+            assert int(p._bufs["status"].item()) == 0
+            err = (got - want).abs()
+            if prec == "fp32":
+                bound = 1e-5 + 2 * noise32
+            else:
+                # 2e-3 is the bar on well-conditioned targets; where rounding q / k / v and P to bf16
+                # moves the oracle itself further than that, the device may follow it
+                bound = 2e-3 + 2 * inherent
+            frac = float((err <= bound).float().mean())
+            info = (prec, backend, frac, float(err.max()), float(err.median()), float(inherent.max()))
+            if prec == "fp32":
+                assert frac >= 0.97 and float(err.max()) <= 3 * float(bound.max()), info
+            else:
+                # bf16 rounding noise is amplified differently per target and per rounding pattern (the
+                # CPU emulation is one realisation, the device another): most targets sit inside the
+                # bound, the median far inside, and nothing is off by more than a few bf16 ulps of y
+                assert frac >= 0.9 and float(err.median()) <= 1e-3 and float(err.max()) <= 2e-2, info
+        # sampling: the device's own log density of its draws equals its teacher-forced density
+        # of those draws once the AR-token index convention is aligned
+        with torch.no_grad():
+            mc.ar_tokens.zero_()
+        p = ARTabPFNPredictor.from_trained_model(mc, backend=backend, precision="bf16")
+        ys = p.sample_sequence(xc.cuda(), yc.cuda(), xt.cuda())
+        ld = p.last_logdens.clone()
+        jd = p.evaluate_joint_density(xc.cuda(), yc.cuda(), xt.cuda(), ys)
+        assert torch.isfinite(ys).all()
+        gap = (jd - ld).abs()
+        lim = 4e-3 + 4 * float(inherent.max())
+        assert float(gap.median()) <= lim / 4 and float((gap <= lim).float().mean()) >= 0.97, (float(gap.max()), lim)
