@@ -72,12 +72,15 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* b, uint32_t parity, volatile
 // compute threads only (the producer warp never joins)
 __device__ __forceinline__ void sync_compute(int n_threads) { asm volatile("bar.sync 1, %0;" ::"r"(n_threads) : "memory"); }
 
-// columns-per-thread / k-split plan for an [R x K] . [K x N] product on T threads
-__host__ __device__ inline void plan_gemm(int N, int T, int& cpt, int& ksplit) {
+// columns-per-thread / k-split plan for an [R x K] . [K x N] product on T threads.  `cap` = columns the
+// k-split scratch holds per row ([3][R][D] floats: (ksplit - 1) * N must fit in 3 * D).
+// A k-group walks its share of a slab four rows at a time (16-byte reads of the activations), so
+// K must be a multiple of 4 * ksplit.
+__host__ __device__ inline void plan_gemm(int K, int N, int T, int cap, int& cpt, int& ksplit) {
   for (cpt = 4; cpt >= 1; --cpt) {  // every thread busy: the column groups divide the threads
     if (N % cpt) continue;
     const int cols = N / cpt;
-    if (cols <= T && T % cols == 0 && T / cols <= 4) {
+    if (cols <= T && T % cols == 0 && T / cols <= 4 && (T / cols - 1) * N <= cap && K % (4 * (T / cols)) == 0) {
       ksplit = T / cols;
       return;
     }
@@ -87,16 +90,16 @@ __host__ __device__ inline void plan_gemm(int N, int T, int& cpt, int& ksplit) {
     if (N % cpt == 0 && N / cpt <= T) return;
   cpt = 1;  // N > 4 T or no divisor: refused on the host (gemm_plan_ok)
 }
-__host__ __device__ inline bool gemm_plan_ok(int N, int T) {
+__host__ __device__ inline bool gemm_plan_ok(int K, int N, int T, int cap) {
   int cpt, ks;
-  plan_gemm(N, T, cpt, ks);
-  return N % cpt == 0 && N / cpt <= T && (size_t)4 * ks * N * sizeof(float) <= (size_t)kBufBytes;
+  plan_gemm(K, N, T, cap, cpt, ks);
+  return N % cpt == 0 && N / cpt <= T && K % (4 * ks) == 0 && (size_t)4 * ks * N * sizeof(float) <= (size_t)kBufBytes;
 }
 
 // rows of W per slab: as many as fit a ring slot, a multiple of 4 per k-group
-__host__ __device__ inline int slab_rows(int K, int N, int T) {
+__host__ __device__ inline int slab_rows(int K, int N, int T, int cap) {
   int cpt, ks;
-  plan_gemm(N, T, cpt, ks);
+  plan_gemm(K, N, T, cap, cpt, ks);
   const int q = 4 * ks;
   int kc = (kBufBytes / (4 * N)) / q * q;
   if (kc < q) kc = q;
@@ -104,8 +107,9 @@ __host__ __device__ inline int slab_rows(int K, int N, int T) {
 }
 
 // producer: stream every slab of one matrix (lane 0 of the producer warp)
-__device__ __forceinline__ bool produce(Stream* st, float* ring, int& issued, const float* w, int K, int N, int T) {
-  const int kc = slab_rows(K, N, T);
+__device__ __forceinline__ bool produce(Stream* st, float* ring, int& issued, const float* w, int K, int N, int T,
+                                        int cap) {
+  const int kc = slab_rows(K, N, T, cap);
   for (int k0 = 0; k0 < K; k0 += kc) {
     const int rows = min(kc, K - k0);
     const uint32_t bytes = (uint32_t)rows * N * 4u;
@@ -128,6 +132,7 @@ struct Chain {
   int scratch;     // offset of the k-split partial sums [ksplit-1][R][N]
   int consumed;    // slabs consumed so far
   int T;           // compute threads
+  int cap;         // scratch columns per row (see plan_gemm)
 };
 
 // out[r][n] = act(bias[n] + sum_k a[r][k] * W[k][n]) for the CTA's R rows; a and out in shared memory.
@@ -137,7 +142,7 @@ __device__ __noinline__ void gemm_body(Chain& ch, int K, int N, int ksplit, int 
   const int cols = (N + CPT - 1) / CPT;
   const int cg = threadIdx.x % cols, kg = threadIdx.x / cols;
   const bool active = kg < ksplit && (CPT > 1 || cg < N);
-  const int kc = slab_rows(K, N, ch.T);
+  const int kc = slab_rows(K, N, ch.T, ch.cap);
   int consumed = ch.consumed;
   float acc[CPT][R];
 #pragma unroll
@@ -215,7 +220,7 @@ __device__ __forceinline__ void gemm_rows(Chain& ch, int K, int N, const float* 
                                           const float* __restrict__ bias, bool gelu, float* s_o, int ldo) {
   const int a_off = (int)(s_a - g_smem), o_off = (int)(s_o - g_smem);
   int cpt, ksplit;
-  plan_gemm(N, ch.T, cpt, ksplit);
+  plan_gemm(K, N, ch.T, ch.cap, cpt, ksplit);
   switch (cpt) {
     case 4: gemm_body<R, 4>(ch, K, N, ksplit, a_off, lda, bias, gelu, o_off, ldo); break;
     case 3: gemm_body<R, 3>(ch, K, N, ksplit, a_off, lda, bias, gelu, o_off, ldo); break;
@@ -344,16 +349,16 @@ __global__ void __launch_bounds__(288) dense_chain_kernel(const DenseArgs a) {
       int issued = 0;
       bool ok = true;
       if (a.do_post) {
-        ok = ok && produce(st, ring, issued, a.post_w.wo_t, D, D, T);
-        ok = ok && produce(st, ring, issued, a.post_w.w1_t, D, Dff, T);
-        ok = ok && produce(st, ring, issued, a.post_w.w2_t, Dff, D, T);
+        ok = ok && produce(st, ring, issued, a.post_w.wo_t, D, D, T, 3 * D);
+        ok = ok && produce(st, ring, issued, a.post_w.w1_t, D, Dff, T, 3 * D);
+        ok = ok && produce(st, ring, issued, a.post_w.w2_t, Dff, D, T, 3 * D);
       }
       if (a.do_head) {
-        ok = ok && produce(st, ring, issued, a.wa_t, D, Dff, T);
-        ok = ok && produce(st, ring, issued, a.wb_t, Dff, 3 * a.n_comp, T);
+        ok = ok && produce(st, ring, issued, a.wa_t, D, Dff, T, 3 * D);
+        ok = ok && produce(st, ring, issued, a.wb_t, Dff, 3 * a.n_comp, T, 3 * D);
       } else if (a.do_pre) {
-        ok = ok && produce(st, ring, issued, a.pre_w.wf_t, D, D, T);
-        ok = ok && produce(st, ring, issued, a.pre_w.wqkv_t, D, 3 * D, T);
+        ok = ok && produce(st, ring, issued, a.pre_w.wf_t, D, D, T, 3 * D);
+        ok = ok && produce(st, ring, issued, a.pre_w.wqkv_t, D, 3 * D, T, 3 * D);
       }
     }
     return;
@@ -364,6 +369,7 @@ __global__ void __launch_bounds__(288) dense_chain_kernel(const DenseArgs a) {
   ch.scratch = (int)(scratch - g_smem);
   ch.consumed = 0;
   ch.T = T;
+  ch.cap = 3 * D;
   float* cur = s_x;
 
   if (a.do_post) {
@@ -512,13 +518,18 @@ int launch_dense(const DenseArgs& a, cudaStream_t s) {
                 "dense chain: d_model must be a multiple of 32 and d_ff a multiple of 4 (got %d, %d)", a.D, a.Dff);
   ARTAB_REQUIRE(3 * a.n_comp <= a.D && a.n_comp <= 32, ARTAB_EINVAL, "dense chain: need 3*K <= d_model and K <= 32");
   ARTAB_REQUIRE(a.D % 16 == 0 && a.Dff % 16 == 0, ARTAB_EINVAL, "dense chain: d_model and d_ff must be multiples of 16");
-  {
-    const int T = a.D <= 256 ? a.D : 256;
-    ARTAB_REQUIRE(gemm_plan_ok(a.D, T) && gemm_plan_ok(3 * a.D, T) && gemm_plan_ok(a.Dff, T) &&
-                      gemm_plan_ok(3 * a.n_comp, T),
-                  ARTAB_EINVAL, "dense chain: no thread plan for d_model %d, d_ff %d (d_ff must be at most %d)", a.D,
-                  a.Dff, 4 * T);
+  // compute threads: d_model of them (at most 256), more when a wider GEMM needs them to cover its
+  // columns at four per thread
+  int T = 0;
+  for (int t = a.D <= 256 ? a.D : 256; t <= 256 && !T; t += 32) {
+    const int cap = 3 * a.D;
+    // (K, N) of every GEMM of the chain: Wo / Wf, W1 / head.0, W2, Wq|Wk|Wv, head.2
+    if (gemm_plan_ok(a.D, a.D, t, cap) && gemm_plan_ok(a.D, a.Dff, t, cap) && gemm_plan_ok(a.Dff, a.D, t, cap) &&
+        gemm_plan_ok(a.D, 3 * a.D, t, cap) && gemm_plan_ok(a.Dff, 3 * a.n_comp, t, cap))
+      T = t;
   }
+  ARTAB_REQUIRE(T > 0, ARTAB_EINVAL, "dense chain: no thread plan for d_model %d, d_ff %d (d_ff at most 1024)", a.D,
+                a.Dff);
   const int wide = 3 * a.D > a.Dff ? 3 * a.D : a.Dff;
   const size_t smem = (size_t)kNBuf * kBufBytes + (size_t)kRows * (2 * a.D + wide + 3 * a.D) * sizeof(float) +
                       sizeof(Stream) + 128;
@@ -530,7 +541,7 @@ int launch_dense(const DenseArgs& a, cudaStream_t s) {
                   cudaGetErrorString(e));
     configured = smem;
   }
-  const int threads = (a.D <= 256 ? a.D : 256) + 32;  // compute threads + the weight-streaming warp
+  const int threads = T + 32;  // compute threads + the weight-streaming warp
   const int grid = (a.rows + kRows - 1) / kRows;
   prof_begin(PROF_DENSE, s);
   dense_chain_kernel<kRows><<<grid, threads, smem, s>>>(a);

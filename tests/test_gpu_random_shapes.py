@@ -19,6 +19,10 @@ CASES = [
     (192, 6, 2, 768, 20, 300, 24, 11),  # the benchmark's layer shape
     (192, 6, 1, 640, 7, 40, 65, 2),     # odd number of hidden tiles in a pair
     (96, 3, 1, 192, 4, 50, 9, 6),       # d_model outside the tensor-core chain: fp32 dense kernel with bf16 caches
+    (64, 2, 1, 384, 6, 20, 5, 3),       # MLP six times d_model: the fp32 kernel needs more threads than d_model
+    (64, 4, 1, 1024, 4, 30, 4, 2),      # widest MLP both dense kernels take
+    (256, 8, 1, 512, 5, 33, 6, 2),      # d_model 256: fp32 dense kernel in both modes, tensor-core attention
+    (64, 2, 1, 128, 1, 1, 1, 1),        # one context row, one target, one stream, one feature
 ]
 
 
@@ -96,3 +100,14 @@ def test_joint_density_against_oracle(case):
         gap = (jd - ld).abs()
         lim = 4e-3 + 4 * float(inherent.max())
         assert float(gap.median()) <= lim / 4 and float((gap <= lim).float().mean()) >= 0.97, (float(gap.max()), lim)
+
+
+def test_unsupported_width_is_refused():
+    """A shape no dense kernel covers is an error, never a silent partial result."""
+    import ar_tabpfn
+    from ar_tabpfn.model import ARTabPFNPredictor
+    m = ar_tabpfn.ARTabPFN(d_model=64, n_heads=2, n_layers=1, d_ff=2048, num_features=3).eval().cuda()
+    p = ARTabPFNPredictor.from_trained_model(m, backend="triton_shared_context", precision="fp32")
+    x, y = torch.randn(2, 12, 3, device="cuda"), torch.randn(2, 12, device="cuda")
+    with pytest.raises((RuntimeError, ValueError)):
+        p.evaluate_joint_density(x[:, :8], y[:, :8], x[:, 8:], y[:, 8:])
