@@ -11,7 +11,7 @@ import artab_oracle as orc
 pytestmark = pytest.mark.gpu
 
 CASES = [
-    # d_model, heads, layers, d_ff, F, Nc, Nt, B
+    # d_model, heads, layers, d_ff, F, Nc, Nt, B [, mixture components]
     (64, 2, 2, 128, 5, 9, 3, 4),        # Dh 32, one hidden tile (no pair), tiny
     (64, 4, 1, 256, 3, 131, 17, 7),     # Dh 16 (scalar attention), tensor-core chain with pairs
     (128, 4, 2, 256, 8, 64, 33, 5),     # Dh 32, buffer crosses two MMA blocks, context = half a key tile
@@ -23,6 +23,8 @@ CASES = [
     (64, 4, 1, 1024, 4, 30, 4, 2),      # widest MLP both dense kernels take
     (256, 8, 1, 512, 5, 33, 6, 2),      # d_model 256: fp32 dense kernel in both modes, tensor-core attention
     (64, 2, 1, 128, 1, 1, 1, 1),        # one context row, one target, one stream, one feature
+    (128, 4, 1, 256, 6, 70, 12, 3, 3),  # three mixture components
+    (128, 4, 1, 256, 6, 70, 12, 3, 8),  # eight: 24 head outputs, beyond the tensor-core chain's 16 -> fp32 dense kernel
 ]
 
 
@@ -50,11 +52,12 @@ def _problem(seed, cfg, Nc, Nt, B, shared):
     return m, sd, x[:, :Nc].contiguous(), y[:, :Nc].contiguous(), x[:, Nc:].contiguous(), y[:, Nc:].contiguous()
 
 
-@pytest.mark.parametrize("case", CASES, ids=lambda c: "d%d_h%d_l%d_ff%d_F%d_nc%d_nt%d_b%d" % c)
+@pytest.mark.parametrize("case", CASES, ids=lambda c: "d%d_h%d_l%d_ff%d_F%d_nc%d_nt%d_b%d" % c[:8] + ("_k%d" % c[8] if len(c) > 8 else ""))
 def test_joint_density_against_oracle(case):
     from ar_tabpfn.model import ARTabPFNPredictor
-    D, H, L, Dff, F, Nc, Nt, B = case
-    cfg = dict(d_model=D, n_heads=H, n_layers=L, d_ff=Dff, num_features=F, buffer_size=8, num_components=5)
+    D, H, L, Dff, F, Nc, Nt, B = case[:8]
+    K = case[8] if len(case) > 8 else 5
+    cfg = dict(d_model=D, n_heads=H, n_layers=L, d_ff=Dff, num_features=F, buffer_size=8, num_components=K)
     for shared, backend in ((True, "triton_shared_context"), (False, "flex_attention")):
         m, sd, xc, yc, xt, yt = _problem(11 + D + Nc, cfg, Nc, Nt, B, shared)
         want = orc.OraclePredictor(sd, H).evaluate_joint_density(xc, yc, xt, yt, shared=shared)
@@ -111,3 +114,23 @@ def test_unsupported_width_is_refused():
     x, y = torch.randn(2, 12, 3, device="cuda"), torch.randn(2, 12, device="cuda")
     with pytest.raises((RuntimeError, ValueError)):
         p.evaluate_joint_density(x[:, :8], y[:, :8], x[:, 8:], y[:, 8:])
+
+
+def test_bf16_tensors_follow_the_reference_convention():
+    """A model and inputs held in bf16 (how the reference runs its bf16 benchmarks) select the bf16
+    caches by themselves and return bf16; values agree with the explicit bf16 mode on fp32 tensors up
+    to the rounding of the returned tensor."""
+    from ar_tabpfn.model import ARTabPFNPredictor
+    cfg = dict(d_model=128, n_heads=4, n_layers=2, d_ff=256, num_features=6, buffer_size=8, num_components=5)
+    m, sd, xc, yc, xt, yt = _problem(5, cfg, 90, 14, 4, True)
+    mc = m.cuda()
+    ref = ARTabPFNPredictor.from_trained_model(mc, backend="triton_shared_context", precision="bf16")
+    want = ref.evaluate_joint_density(xc.cuda(), yc.cuda(), xt.cuda(), yt.cuda())
+    mb = mc.to(torch.bfloat16)
+    p = ARTabPFNPredictor.from_trained_model(mb, backend="triton_shared_context")
+    b = lambda t: t.cuda().to(torch.bfloat16)
+    got = p.evaluate_joint_density(b(xc), b(yc), b(xt), b(yt))
+    assert got.dtype == torch.bfloat16
+    torch.testing.assert_close(got.float(), want, atol=2e-2, rtol=1e-2)
+    ys = p.sample_sequence(b(xc), b(yc), b(xt))
+    assert ys.dtype == torch.bfloat16 and torch.isfinite(ys.float()).all()
