@@ -263,7 +263,7 @@ class ARTabPFNPredictor:
         normal = torch.empty(n_steps, batch, device=device, dtype=dtype)
         for t in range(n_steps):
             expo[t].exponential_(1)
-            normal[t] = torch.randn(batch, 1, 1, 1, device=device, dtype=dtype).view(batch)
+            normal[t].normal_()   # the same fill as torch.randn(batch, 1, 1, 1): same element count, same stream
         return expo, normal
 
     @torch.no_grad()
