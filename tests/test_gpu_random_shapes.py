@@ -23,6 +23,8 @@ CASES = [
     (64, 4, 1, 1024, 4, 30, 4, 2),      # widest MLP both dense kernels take
     (256, 8, 1, 512, 5, 33, 6, 2),      # d_model 256: fp32 dense kernel in both modes, tensor-core attention
     (64, 2, 1, 128, 1, 1, 1, 1),        # one context row, one target, one stream, one feature
+    (128, 4, 1, 256, 4, 20, 128, 37),   # teacher forcing with 9472 rows = 74 row tiles: the last size that runs CTA pairs
+    (128, 4, 1, 256, 4, 20, 125, 38),   # 9500 rows = 75 tiles: one CTA per tile
     (128, 4, 1, 256, 6, 70, 12, 3, 3),  # three mixture components
     (128, 4, 1, 256, 6, 70, 12, 3, 8),  # eight: 24 head outputs, beyond the tensor-core chain's 16 -> fp32 dense kernel
 ]
