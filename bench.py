@@ -330,7 +330,7 @@ def main():
             "gpu_launches": launches, "clocks": clk.result, "roofline": roof, "kernel_shares": shares,
             "device_status": status,
         }
-        if not args.no_cpu_baseline and world >= 1:
+        if not args.no_cpu_baseline and world == 1:
             rate, per, cores, sample = cpu_reference_rate(1, 1)
             line["cpu_baseline"] = {"value": rate, "unit": "targets/s", "cores": cores, "kind": "port",
                                     "sample": sample}
