@@ -49,6 +49,7 @@ _SIGNATURES = {
     "artab_decode_step": (_i, [C.POINTER(Model), C.POINTER(State), _p, _i, _i, _i, _p, _p, _p, _p, _p, _p]),
     "artab_decode_embedded": (_i, [C.POINTER(Model), C.POINTER(State), _p, _i, _i, _p, _p]),
     "artab_teacher_forcing": (_i, [C.POINTER(Model), C.POINTER(State), _p, _p, _i, _i, _p, _p]),
+    "artab_forward_masked": (_i, [C.POINTER(Model), C.POINTER(State), _p, _p, _p, _p, _i, _i, _i, _p, _p, _p]),
     "artab_context_attention": (_i, [_i, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i, _p, _p, _p, _p]),
     "artab_context_attention_noalloc": (_i, [_i, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i, _p, _p]),
     "artab_buffer_attention_merge": (_i, [_i, _p, _p, _i, _i, _i, _i, _i, _i, _i, _p, _p, _i, _i, _p, _p]),

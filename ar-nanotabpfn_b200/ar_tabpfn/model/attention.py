@@ -3,8 +3,9 @@
 ``MultiheadAttention`` keeps the reference's parameters (four bias-free
 projections, ar_tabpfn/model/attention.py:31-43 of the reference) so that
 state_dicts load unchanged.  On the inference path these modules are weight
-containers: the kernels read their packed weights.  The block-mask factories
-of the reference serve its training loop and are not part of this build.
+containers: the kernels read their packed weights.  The mask factories return
+small descriptions of the visibility (``DenseMask``, ``RowMask``) instead of
+flex BlockMasks; ``ARTabPFN.forward`` takes them.
 """
 from __future__ import annotations
 
@@ -24,20 +25,66 @@ class MultiheadAttention(nn.Module):
 
     def forward(self, *args, **kwargs):
         raise NotImplementedError(
-            "the training forward (flex_attention block masks) is outside this build; "
-            "use ARTabPFNPredictor for sampling and log-density evaluation")
+            "a stand-alone attention module call is outside this build: use ARTabPFN.forward "
+            "(inference only) or ARTabPFNPredictor")
 
 
-def _training_only(name):
-    def fn(*args, **kwargs):
-        raise NotImplementedError(f"{name} builds a training BlockMask and is outside this build")
-    fn.__name__ = name
-    return fn
+class DenseMask:
+    """What ``create_dense_mask`` / ``create_context_self_attention_mask`` return here: every
+    query sees every key, which the kernels do without a mask tensor."""
+
+    def __init__(self, seq_len: int):
+        self.seq_len = int(seq_len)
 
 
-create_dense_mask = _training_only("create_dense_mask")
-create_row_mask = _training_only("create_row_mask")
-create_context_self_attention_mask = _training_only("create_context_self_attention_mask")
+class RowMask:
+    """Row-attention visibility of the reference's ``create_row_mask``
+    (ar_tabpfn/model/attention.py:86-175) as data instead of a flex BlockMask.
+
+    Every row sees all context rows.  Context rows see nothing else.  The mask over the
+    buffer rows is a prefix for every other row, so it is stored as one count per
+    non-context row: ``visible[j]`` = how many leading buffer rows row ``context_len + j``
+    sees.  Buffer j sees buffers <= j; target t sees buffers <= t mod Nb while
+    t < attending_chunks * Nb and no buffer afterwards."""
+
+    def __init__(self, num_rows: int, context_len: int, buffer_len: int, visible):
+        self.num_rows, self.context_len, self.buffer_len = int(num_rows), int(context_len), int(buffer_len)
+        self.visible = [int(v) for v in visible]
+        if len(self.visible) != self.num_rows - self.context_len:
+            raise ValueError("one visible count per non-context row is needed")
+
+    @classmethod
+    def prefix(cls, context_len: int, buffer_len: int, visible) -> "RowMask":
+        """Any mask of the family: ``visible`` lists the counts of the buffer rows, then the target rows."""
+        visible = list(visible)
+        return cls(context_len + len(visible), context_len, buffer_len, visible)
+
+    @classmethod
+    def teacher_forcing(cls, context_len: int, num_targets: int) -> "RowMask":
+        """Buffer j sees buffers <= j, target i sees buffers < i (the inference pattern)."""
+        return cls.prefix(context_len, num_targets, [j + 1 for j in range(num_targets)] + list(range(num_targets)))
+
+
+def create_dense_mask(seq_len: int, device=None) -> DenseMask:
+    return DenseMask(seq_len)
+
+
+def create_context_self_attention_mask(context_len: int, device=None) -> DenseMask:
+    return DenseMask(context_len)
+
+
+def create_row_mask(num_rows: int, context_len: int, buffer_len: int, attending_chunks=None,
+                    device=None) -> RowMask:
+    """Same arguments as the reference factory; returns the visibility as a ``RowMask``."""
+    target_len = num_rows - context_len - buffer_len
+    if target_len < 0 or buffer_len < 0 or context_len < 0:
+        raise ValueError("num_rows must cover the context and buffer rows")
+    if attending_chunks is None:
+        attending_chunks = target_len // (2 * buffer_len) if buffer_len else 0
+    vis = [j + 1 for j in range(buffer_len)]
+    for t in range(target_len):
+        vis.append((t % buffer_len) + 1 if buffer_len and t < attending_chunks * buffer_len else 0)
+    return RowMask(num_rows, context_len, buffer_len, vis)
 
 
 def clear_mask_cache():

@@ -334,3 +334,38 @@ class ARTabPFNPredictor:
         self.buffer_len = int(self._state.buffer_len)
         self.seq_len = self.context_len + self.buffer_len
         return out.to(dtype)
+
+    # -------------------------------------------------------- masked forward
+    @torch.no_grad()
+    def forward_masked(self, x_context: Tensor, y_context: Tensor, x_buffer: Tensor, y_buffer: Tensor,
+                       x_target: Tensor, y_target: Tensor, visible) -> Tensor:
+        """Per-target log density [B,Nt] of the reference's training forward
+        (model.py:317-369) for inference: context rows see the context; token j of
+        [Buffer_0..Buffer_{Nb-1}, Target_0..Target_{Nt-1}] sees the context plus the first
+        ``visible[j]`` buffer rows (``RowMask.visible`` of ``create_row_mask``)."""
+        lib = _lib.lib()
+        B, Nc, F = x_context.shape
+        Nb, Nt = x_buffer.shape[1], x_target.shape[1]
+        if len(visible) != Nb + Nt:
+            raise ValueError(f"visible must list {Nb + Nt} counts (buffer rows, then target rows)")
+        if Nb > self.ar_tokens.shape[0]:
+            raise ValueError(f"{Nb} buffer rows but only {self.ar_tokens.shape[0]} AR position tokens")
+        device, dtype = x_context.device, x_context.dtype
+        if self.shared:
+            self.init_kv_cache(B, Nb, device, dtype)
+        else:
+            self.init_kv_cache(B, Nc + Nb, device, dtype)
+        self.prefill_context(x_context, y_context)
+        self._ensure_rows(B * (Nb + Nt))
+        f32 = lambda t, *shape: t.detach().to(torch.float32).reshape(*shape).contiguous()
+        xb, yb = f32(x_buffer, B, Nb, F), f32(y_buffer, B, Nb)
+        xt, yt = f32(x_target, B, Nt, F), f32(y_target, B, Nt)
+        vis = torch.tensor([int(v) for v in visible], dtype=torch.int32, device=device)
+        out = torch.empty(B, Nt, device=device, dtype=torch.float32)
+        pm = self._packed(device)
+        _lib.check(lib.artab_forward_masked(pm.ref, C.byref(self._state), _lib.ptr(xb), _lib.ptr(yb), _lib.ptr(xt),
+                                            _lib.ptr(yt), F, Nb, Nt, _lib.ptr(vis), _lib.ptr(out),
+                                            _lib.stream_ptr()))
+        self.buffer_len = int(self._state.buffer_len)
+        self.seq_len = self.context_len + self.buffer_len
+        return out.to(dtype)

@@ -216,6 +216,30 @@ class ARTabPFN(nn.Module):
         self.head = MixtureGaussianHead(d_model, d_ff, dim_y=1, num_components=num_components)
         self.ar_tokens = nn.Parameter(torch.randn(buffer_size, d_model) * 0.02)
 
-    def forward(self, *args, **kwargs):
-        raise NotImplementedError(
-            "the training forward is outside this build; use ARTabPFNPredictor.from_trained_model(model)")
+    @torch.no_grad()
+    def forward(self, x_context: Tensor, y_context: Tensor, x_buffer: Tensor, y_buffer: Tensor,
+                x_target: Tensor, mask_features, mask_rows, y_target: Optional[Tensor] = None):
+        """The reference's forward (model.py:317-369) for inference: returns the loss
+        ``-mean(log density of y_target)`` under ``mask_rows`` (a ``RowMask`` from
+        ``create_row_mask``), or None without ``y_target``, like the reference.  No autograd
+        graph is built: gradients, and with them training, are outside this build.  The
+        per-target log densities of the call are kept in ``last_logdens`` [B,Nt]."""
+        from .attention import RowMask
+        from .inference import ARTabPFNPredictor
+        if not isinstance(mask_rows, RowMask):
+            raise TypeError("mask_rows must be the RowMask returned by create_row_mask (flex BlockMasks are "
+                            "not decoded)")
+        Nc, Nb, Nt = x_context.size(1), x_buffer.size(1), x_target.size(1)
+        if (mask_rows.context_len, mask_rows.buffer_len, mask_rows.num_rows) != (Nc, Nb, Nc + Nb + Nt):
+            raise ValueError("mask_rows was built for other row counts")
+        if y_target is None:
+            return None
+        if y_target.dim() == 3:
+            y_target = y_target[..., 0]
+        pred = getattr(self, "_artab_fwd", None)
+        if pred is None:
+            pred = ARTabPFNPredictor.from_trained_model(self, backend="flex_attention")
+            object.__setattr__(self, "_artab_fwd", pred)
+        ld = pred.forward_masked(x_context, y_context, x_buffer, y_buffer, x_target, y_target, mask_rows.visible)
+        object.__setattr__(self, "last_logdens", ld)
+        return -ld.sum() / ld.numel()

@@ -585,6 +585,77 @@ int artab_teacher_forcing(const artab_model* m, artab_state* st, const float* xt
   return ARTAB_OK;
 }
 
+int artab_forward_masked(const artab_model* m, artab_state* st, const float* xb, const float* yb, const float* xt,
+                         const float* yt, int n_feat, int n_buf, int n_targets, const int32_t* visible,
+                         float* logdens, void* stream) {
+  int rc = check_model(m);
+  if (rc) return rc;
+  rc = check_state(m, st);
+  if (rc) return rc;
+  ARTAB_REQUIRE(xt && yt && logdens && visible && n_targets >= 1 && n_buf >= 0 && n_feat > 0, ARTAB_EINVAL,
+                "forward_masked: bad argument");
+  ARTAB_REQUIRE(n_buf == 0 || (xb && yb), ARTAB_EINVAL, "forward_masked: buffer rows without buffer inputs");
+  ARTAB_REQUIRE(n_buf <= m->n_ar_tokens, ARTAB_EINVAL,
+                "forward_masked: %d buffer rows but only %d AR position tokens", n_buf, m->n_ar_tokens);
+  cudaStream_t s = (cudaStream_t)stream;
+  const int tps = n_buf + n_targets;
+  const long rows_l = (long)st->n_streams * tps;
+  ARTAB_REQUIRE(rows_l <= st->max_rows, ARTAB_ECAPACITY, "forward_masked: %ld rows exceed the workspace (%d)", rows_l,
+                st->max_rows);
+  ARTAB_REQUIRE(n_buf == 0 || (n_buf <= st->max_buf && st->kv_buf), ARTAB_ECAPACITY,
+                "Shared-context buffer cache exceeded; increase max buffer length.");
+  const int rows = (int)rows_l;
+  EmbedArgs e = embed_base(m);
+  e.mode = EMB_FWD;
+  e.rows = rows;
+  e.F = n_feat;
+  e.xb = xb;
+  e.yb = yb;
+  e.Nb = n_buf;
+  e.xt = xt;
+  e.Nt = n_targets;
+  e.out = st->x;
+  rc = launch_embed(e, s);
+  if (rc) return rc;
+  KvDest kv;
+  memset(&kv, 0, sizeof(kv));
+  kv.mode = KV_TF;
+  kv.dtype = st->dtype;
+  kv.n_heads = m->n_heads;
+  kv.head_dim = m->head_dim;
+  kv.tokens_per_stream = tps;
+  kv.n_kv_tokens = n_buf;
+  kv.pos0 = 0;
+  DenseArgs d0 = dense_base(m, st, rows);
+  d0.do_pre = 1;
+  d0.pre_w = m->layers[0];
+  d0.kv = kv;
+  set_kv(m, st, 0, d0.kv);
+  rc = launch_dense(d0, s);
+  if (rc) return rc;
+  BufMergeArgs b = buf_base(m, st, rows);
+  b.mode_tf = 2;
+  b.visible = visible;
+  b.tps = tps;
+  b.len0 = n_buf;  // upper bound of every visible count
+  b.n_items = (long)st->n_streams * m->n_heads * tps;
+  DenseArgs last = dense_base(m, st, rows);
+  last.do_post = 1;
+  last.do_final = 1;
+  last.do_head = 1;
+  last.head_mode = 2;
+  last.head_tps = tps;
+  last.head_first = n_buf;
+  last.out_stride = n_targets;
+  last.out_col = 0;
+  last.y_in = yt;
+  last.ld_out = logdens;
+  rc = run_layers(m, st, rows, tps, kv, b, /*need_merge=*/n_buf > 0, last, s);
+  if (rc) return rc;
+  st->buffer_len = n_buf;
+  return ARTAB_OK;
+}
+
 int artab_context_attention(int dtype, const void* q, const void* k_ctx, const void* v_ctx, int rows,
                             int rows_per_group, int n_groups, int n_heads, int head_dim, int n_ctx, int n_ctx_pad,
                             int n_splits, float* out, float* lse, int32_t* status, void* stream) {

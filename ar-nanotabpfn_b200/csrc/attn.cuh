@@ -24,7 +24,9 @@ struct BufMergeArgs {
   const void* q;       // [rows][H][Dh]
   const void* kv_buf;  // [B][H][T][2][Dh]
   int n_heads, head_dim, max_buf;
-  int mode_tf, nt, n_new, len0;
+  int mode_tf, nt, n_new, len0;  // mode_tf: 0 decode step, 1 teacher forcing, 2 per-token visible prefix
+  const int32_t* visible;  // mode 2: [tps] token j of a stream sees buffer keys [0, visible[j])
+  int tps;                 // mode 2: tokens per stream
   long n_items;
   const float* o_part;    // [splits][rows][H][Dh]
   const float* lse_part;  // [splits][rows][H]

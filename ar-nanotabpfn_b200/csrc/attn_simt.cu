@@ -174,7 +174,16 @@ __global__ void __launch_bounds__(128, 6) buf_merge_kernel(const BufMergeArgs a)
   long b;
   int h, len;
   long row_t, row_b;
-  if (a.mode_tf) {
+  if (a.mode_tf == 2) {
+    // one query per item: token j of stream b sees the first visible[j] buffer rows
+    const int j = (int)(item % a.tps);
+    const long bh = item / a.tps;
+    b = bh / a.n_heads;
+    h = (int)(bh - b * a.n_heads);
+    len = min(max(__ldg(a.visible + j), 0), a.len0);  // len0: buffer rows written per stream
+    row_t = b * a.tps + j;
+    row_b = -1;
+  } else if (a.mode_tf) {
     const int ips = a.nt + 1;
     const int i = (int)(item % ips);
     const long bh = item / ips;
@@ -419,7 +428,7 @@ int launch_ctx_attn_simt(const CtxAttnArgs& a, cudaStream_t s) {
 
 int launch_buf_merge(const BufMergeArgs& a, cudaStream_t s) {
   if (a.n_items <= 0) return ARTAB_OK;
-  if (buf_mma_supported(a.dtype, a.head_dim)) return launch_buf_merge_mma(a, s);
+  if (a.mode_tf != 2 && buf_mma_supported(a.dtype, a.head_dim)) return launch_buf_merge_mma(a, s);
   return a.dtype == ARTAB_BF16 ? launch_buf_t<__nv_bfloat16>(a, s) : launch_buf_t<float>(a, s);
 }
 

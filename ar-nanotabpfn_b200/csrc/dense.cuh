@@ -5,7 +5,7 @@
 namespace artab {
 
 // Which rows the embedder produces and where their inputs come from.
-enum EmbedMode : int { EMB_ROWS = 0, EMB_DECODE = 1, EMB_TF = 2 };
+enum EmbedMode : int { EMB_ROWS = 0, EMB_DECODE = 1, EMB_TF = 2, EMB_FWD = 3 };
 
 struct EmbedArgs {
   int mode, rows, D, F, kind;
@@ -18,6 +18,10 @@ struct EmbedArgs {
   const float* xt;       // [B][Nt][F]
   const float* yt;       // decode: samples [B][Nt]; tf: yt [B][Nt]
   int Nt, t, n_new, S;
+  // EMB_FWD: per stream [Buffer_0..Buffer_{Nb-1}, Target_0..Target_{Nt-1}], buffer rows from their own arrays
+  const float* xb;       // [B][Nb][F]
+  const float* yb;       // [B][Nb]
+  int Nb;
   float* out;            // [rows][D]
 };
 

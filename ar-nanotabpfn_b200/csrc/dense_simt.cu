@@ -471,6 +471,21 @@ __global__ void __launch_bounds__(128) embed_kernel(const EmbedArgs a) {
       xr = a.xt + ((size_t)b * a.Nt + a.t) * a.F;
       kind = ARTAB_MARK_TARGET;
     }
+  } else if (a.mode == EMB_FWD) {
+    // masked forward: [Buffer_0..Buffer_{Nb-1}, Target_0..Target_{Nt-1}], buffer j carries ar = j (Nb <= S)
+    const int tps = a.Nb + a.Nt;
+    const long b = row / tps;
+    const int j = (int)(row - b * tps);
+    if (j < a.Nb) {
+      xr = a.xb + ((size_t)b * a.Nb + j) * a.F;
+      yv = a.yb[(size_t)b * a.Nb + j];
+      has_y = true;
+      kind = ARTAB_MARK_BUFFER;
+      ar = j;
+    } else {
+      xr = a.xt + ((size_t)b * a.Nt + (j - a.Nb)) * a.F;
+      kind = ARTAB_MARK_TARGET;
+    }
   } else {
     // teacher forcing: [Buffer_0..Buffer_{Nt-1}, Target_0..Target_{Nt-1}], buffer j carries ar = j mod S
     const long b = row / (2 * a.Nt);

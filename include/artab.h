@@ -194,6 +194,22 @@ ARTAB_API int artab_decode_embedded(const artab_model* m, artab_state* st, const
 ARTAB_API int artab_teacher_forcing(const artab_model* m, artab_state* st, const float* xt, const float* yt,
                           int n_feat, int n_targets, float* logdens, void* stream);
 
+/* Masked forward over [Buffer_0..Buffer_{Nb-1}, Target_0..Target_{Nt-1}] per stream with a
+ * per-token prefix mask on the buffer rows: token j (0 <= j < Nb + Nt) sees the whole context
+ * and buffer rows [0, visible[j]) (counts above Nb are clamped).  Buffer row j carries
+ * ar_tokens[j], so Nb <= S.  This is the row mask of the reference's training forward
+ * restricted to what it can express for the non-context rows: context rows see the context
+ * only (artab_prefill), buffer j sees buffers <= j (visible[j] = j + 1), target t sees
+ * buffers <= t mod Nb while t < attending_chunks * Nb and none after.
+ *   xb [B][Nb][F], yb [B][Nb], xt [B][Nt][F], yt [B][Nt], visible [Nb+Nt] int32 (device);
+ *   logdens [B][Nt] log density of yt under the mixture of every target row.
+ * Needs max_buf >= Nb; buffer_len is left at Nb.
+ * Replaces ARTabPFN.forward / TwoStageTransformer.forward under create_row_mask for
+ * inference (ar_tabpfn/model/model.py:317-369, 134-147; ar_tabpfn/model/attention.py:86-175). */
+ARTAB_API int artab_forward_masked(const artab_model* m, artab_state* st, const float* xb, const float* yb,
+                         const float* xt, const float* yt, int n_feat, int n_buf, int n_targets,
+                         const int32_t* visible, float* logdens, void* stream);
+
 /* ------------------------------ single operators -------------------------- */
 
 /* Shared-context attention with LSE output.

@@ -23,6 +23,8 @@ Reference locations restated here (paths inside the reference project):
   * ar_tabpfn/model/inference.py:323-366            sample_sequence
   * ar_tabpfn/model/inference.py:392-420, 835-890   teacher-forced joint density
   * ar_tabpfn/model/inference.py:423-453, 500-577   per-batch ("flex") semantics
+  * ar_tabpfn/model/model.py:317-369, ar_tabpfn/model/attention.py:86-175
+                                          training forward under create_row_mask (inference only)
 
 The model is addressed through its ``state_dict`` (a plain ``dict`` of CPU
 tensors with the reference's parameter names) so the oracle needs neither the
@@ -459,6 +461,54 @@ class OraclePredictor:
         z = self.final_norm(x)[:, Nt:]
         mean, std, w, logw = head_params(self.sd, z)
         return head_logpdf(mean, std, logw, yt)
+
+    # -- masked forward (the training forward's row mask, inference only) -------
+    def forward_masked(self, xc, yc, xb, yb, xt, yt, visible, shared: bool = False) -> Tensor:
+        """Per-target log density [B,Nt] of the training forward (model.py:317-369)
+        under a row mask of the create_row_mask family (attention.py:86-175):
+        context rows see the context; the non-context rows
+        [Buffer_0..Buffer_{Nb-1}, Target_0..Target_{Nt-1}] see the context plus the
+        first ``visible[j]`` buffer rows.  Buffer j carries ar_tokens[j] (Nb <= S).
+        Because no row is visible to a context row except context rows, the
+        context part equals ``prefill`` and the rest is one pass over Nb + Nt
+        tokens per dataset."""
+        B, Nt, _ = xt.shape
+        Nb = xb.shape[1]
+        if Nb > self.S:
+            raise ValueError("more buffer rows than AR position tokens")
+        self.prefill(xc, yc, shared=shared)
+        tgt = embed_rows(self.sd, xt, None, MARKER_TARGET)
+        if Nb:
+            ar = torch.arange(Nb).unsqueeze(0).expand(B, -1)
+            x = torch.cat([embed_rows(self.sd, xb, yb, MARKER_BUFFER, ar), tgt], dim=1)
+        else:
+            x = tgt
+        vis = torch.as_tensor(visible, dtype=torch.long).clamp(0, Nb)
+        mask = (torch.arange(Nb)[None, :] < vis[:, None])[None, None]      # [1,1,Nb+Nt,Nb]
+        for l in range(self.L):
+            x1, q, k, v = self._pre(l, x)
+            qh, kh, vh = self._heads(q), self._heads(k), self._heads(v)
+            if Nb:
+                a = self._attend(l, qh, kh[:, :, :Nb], vh[:, :, :Nb], buf_mask=mask)
+            else:
+                a = self._attend(l, qh, None, None)
+            x = self._post(l, x1, self._unheads(a))
+        z = self.final_norm(x)[:, Nb:]
+        mean, std, w, logw = head_params(self.sd, z)
+        return head_logpdf(mean, std, logw, yt)
+
+
+def row_mask_visible(n_buf: int, n_targets: int, attending_chunks: Optional[int] = None):
+    """Visible-buffer counts of the non-context rows under create_row_mask
+    (attention.py:86-175): buffer j sees buffers <= j; target t sees buffers
+    <= t mod Nb while t < attending_chunks * Nb (default attending_chunks =
+    Nt // (2 Nb)) and no buffer after that."""
+    if attending_chunks is None:
+        attending_chunks = n_targets // (2 * n_buf) if n_buf else 0
+    vis = [j + 1 for j in range(n_buf)]
+    for t in range(n_targets):
+        vis.append((t % n_buf) + 1 if n_buf and t < attending_chunks * n_buf else 0)
+    return vis
 
 
 # --------------------------------------------------------------------------

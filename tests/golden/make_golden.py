@@ -2,7 +2,7 @@
 
 Run once, in a container where the reference checkout is available:
 
-    python tests/golden/make_golden.py /path/to/reference
+    python tests/golden/make_golden.py /path/to/reference [--forward-only]
 
 It imports the reference's ``ar_tabpfn.model`` package under the alias
 ``ref_ar_tabpfn`` (so it cannot collide with the shipped drop-in package of
@@ -144,6 +144,71 @@ def model_fixture(ref, name, seed, cfg, Nc, Nt, B, shared_data, variate_seed):
     return fx
 
 
+@torch.no_grad()
+def forward_fixture(ref, root):
+    """The training forward (ARTabPFN.forward under create_row_mask) run for inference: the
+    scalar loss the reference returns plus the per-target log density and representation,
+    captured at the head.  Case "tf_style" uses the inference-style mask of the reference's
+    own test_teacher_forcing_matches_forward (buffer j sees buffers <= j, target i sees
+    buffers < i), built with the same flex primitives."""
+    attn = importlib.import_module("ref_ar_tabpfn.model.attention")
+    from torch.nn.attention.flex_attention import create_block_mask
+    cases = []
+    specs = [
+        dict(name="default_chunks", seed=21, B=3, Nc=10, Nb=4, Nt=16, chunks=None,
+             cfg=dict(d_model=32, n_heads=2, n_layers=2, d_ff=64, num_features=4, buffer_size=4, num_components=3)),
+        dict(name="dh32_three_chunks", seed=5, B=4, Nc=50, Nb=8, Nt=32, chunks=3,
+             cfg=dict(d_model=64, n_heads=2, n_layers=3, d_ff=128, num_features=5, buffer_size=8, num_components=5)),
+        dict(name="short_buffer", seed=23, B=2, Nc=33, Nb=3, Nt=12, chunks=None,
+             cfg=dict(d_model=64, n_heads=4, n_layers=2, d_ff=128, num_features=8, buffer_size=8, num_components=5)),
+        dict(name="tf_style", seed=24, B=2, Nc=8, Nb=4, Nt=4, chunks="tf",
+             cfg=dict(d_model=32, n_heads=2, n_layers=2, d_ff=64, num_features=4, buffer_size=4, num_components=3)),
+    ]
+    for sp in specs:
+        m = xavier_model(ref, sp["seed"], **sp["cfg"])
+        B, Nc, Nb, Nt, F = sp["B"], sp["Nc"], sp["Nb"], sp["Nt"], sp["cfg"]["num_features"]
+        ds = [orc.make_dataset(sp["seed"] * 1000 + b, Nc + Nb + Nt, F) for b in range(B)]   # one dataset per element
+        x, y = torch.stack([d[0] for d in ds]), torch.stack([d[1] for d in ds])
+        xc, yc = x[:, :Nc].contiguous(), y[:, :Nc].contiguous()
+        xb, yb = x[:, Nc:Nc + Nb].contiguous(), y[:, Nc:Nc + Nb].contiguous()
+        xt, yt = x[:, Nc + Nb:].contiguous(), y[:, Nc + Nb:].contiguous()
+        R = Nc + Nb + Nt
+        attn.clear_mask_cache()
+        mf = attn.create_dense_mask(seq_len=1, device="cpu")
+        if sp["chunks"] == "tf":
+            def mask_mod(b, h, q_idx, kv_idx, Nc=Nc, Nb=Nb):
+                ctx = kv_idx < Nc
+                kv_buf = (kv_idx >= Nc) & (kv_idx < Nc + Nb)
+                q_buf = (q_idx >= Nc) & (q_idx < Nc + Nb)
+                q_tgt = q_idx >= Nc + Nb
+                return ctx | (q_buf & kv_buf & (kv_idx <= q_idx)) | (q_tgt & kv_buf & ((kv_idx - Nc) < (q_idx - Nc - Nb)))
+            mr = create_block_mask(mask_mod, B=None, H=None, Q_LEN=R, KV_LEN=R, device="cpu")
+            visible = [j + 1 for j in range(Nb)] + list(range(Nt))
+        else:
+            mr = attn.create_row_mask(num_rows=R, context_len=Nc, buffer_len=Nb, attending_chunks=sp["chunks"],
+                                      device="cpu")
+            visible = orc.row_mask_visible(Nb, Nt, sp["chunks"])
+        zs = []
+        orig = m.head.forward
+
+        def spy(z, y=None, loss_mask=None):
+            zs.append(z.clone())
+            return orig(z, y, loss_mask)
+
+        m.head.forward = spy
+        try:
+            loss = m(x_context=xc, y_context=yc, x_buffer=xb, y_buffer=yb, x_target=xt, mask_features=mf,
+                     mask_rows=mr, y_target=yt)
+        finally:
+            del m.head.forward
+        z = zs[0]
+        ld = m.head.log_likelihood(z, yt.unsqueeze(-1))
+        cases.append(dict(name=sp["name"], cfg=sp["cfg"], n_heads=sp["cfg"]["n_heads"], state_dict=sd_of(m),
+                          xc=xc, yc=yc, xb=xb, yb=yb, xt=xt, yt=yt, attending_chunks=sp["chunks"],
+                          visible=visible, loss=loss.clone(), logdens=ld, z=z))
+    return cases
+
+
 def compact(o):
     """Clone every tensor so that no view drags a larger storage into the file."""
     if isinstance(o, torch.Tensor):
@@ -161,6 +226,10 @@ def main():
     root = sys.argv[1]
     ref, tk = import_reference(root)
     torch.set_num_threads(8)
+    if "--forward-only" in sys.argv[2:]:      # leaves the other fixtures as they are
+        torch.save(compact(forward_fixture(ref, root)), os.path.join(HERE, "forward.pt"))
+        print("forward.pt", os.path.getsize(os.path.join(HERE, "forward.pt")))
+        return
     torch.save(compact(ops_fixture(tk)), os.path.join(HERE, "ops.pt"))
     c1 = model_fixture(
         ref, "config1", seed=0,
@@ -178,7 +247,8 @@ def main():
         cfg=dict(d_model=64, n_heads=2, n_layers=3, d_ff=128, num_features=5, buffer_size=8, num_components=5),
         Nc=200, Nt=12, B=6, shared_data=True, variate_seed=11)
     torch.save(compact(h32), os.path.join(HERE, "dh32.pt"))
-    for f in ("ops.pt", "config1.pt", "tiny_distinct.pt", "dh32.pt"):
+    torch.save(compact(forward_fixture(ref, root)), os.path.join(HERE, "forward.pt"))
+    for f in ("ops.pt", "config1.pt", "tiny_distinct.pt", "dh32.pt", "forward.pt"):
         print(f, os.path.getsize(os.path.join(HERE, f)))
 
 

@@ -115,3 +115,43 @@ def test_variate_order_reproduces_global_generator():
     for t in range(Nt):
         assert torch.equal((w / expo[t]).argmax(-1, keepdim=True), want[t][0])
         assert torch.equal(normal[t], want[t][1].view(B))
+
+
+def test_forward_masked_matches_reference_forward():
+    """The oracle's masked forward against the reference's training forward
+    (ARTabPFN.forward under create_row_mask, and under the inference-style mask
+    of the reference's own test) run on CPU: per-target log density and loss."""
+    for c in load("forward.pt"):
+        o = orc.OraclePredictor(c["state_dict"], c["n_heads"])
+        if c["attending_chunks"] != "tf":
+            assert orc.row_mask_visible(c["xb"].shape[1], c["xt"].shape[1], c["attending_chunks"]) == c["visible"]
+        ld = o.forward_masked(c["xc"], c["yc"], c["xb"], c["yb"], c["xt"], c["yt"], c["visible"], shared=False)
+        sd64 = {k: v.double() for k, v in c["state_dict"].items()}
+        d = lambda k: c[k].double()
+        ld64 = orc.OraclePredictor(sd64, c["n_heads"]).forward_masked(d("xc"), d("yc"), d("xb"), d("yb"), d("xt"),
+                                                                      d("yt"), c["visible"], shared=False)
+        noise = (c["logdens"].double() - ld64).abs().float()     # the reference's own fp32 rounding
+        assert ((ld - c["logdens"]).abs() <= 1e-5 + 2 * noise).all(), (c["name"], (ld - c["logdens"]).abs().max())
+        torch.testing.assert_close(-ld.mean(), c["loss"], atol=1e-5, rtol=1e-5)
+
+
+def test_forward_tf_style_equals_joint_density():
+    """With buffer = target data and the inference-style mask the forward is the teacher-forced
+    joint density (the reference's test_teacher_forcing_matches_forward)."""
+    c = [x for x in load("forward.pt") if x["name"] == "tf_style"][0]
+    o = orc.OraclePredictor(c["state_dict"], c["n_heads"])
+    a = o.forward_masked(c["xc"], c["yc"], c["xt"], c["yt"], c["xt"], c["yt"], c["visible"], shared=False)
+    b = o.evaluate_joint_density(c["xc"], c["yc"], c["xt"], c["yt"], shared=False)
+    torch.testing.assert_close(a, b, atol=1e-5, rtol=1e-5)
+
+
+def test_row_mask_factory_matches_oracle():
+    """The shipped create_row_mask (host logic, no GPU) lists the same counts as the oracle."""
+    from ar_tabpfn.model import create_row_mask
+    from ar_tabpfn.model.attention import RowMask
+    for Nc, Nb, Nt, ch in [(10, 4, 16, None), (50, 8, 32, 3), (33, 3, 12, None), (5, 0, 4, None), (7, 2, 5, 1)]:
+        m = create_row_mask(num_rows=Nc + Nb + Nt, context_len=Nc, buffer_len=Nb, attending_chunks=ch, device="cpu")
+        assert m.visible == orc.row_mask_visible(Nb, Nt, ch)
+    assert RowMask.teacher_forcing(8, 4).visible == [1, 2, 3, 4, 0, 1, 2, 3]
+    with pytest.raises(ValueError):
+        create_row_mask(num_rows=5, context_len=4, buffer_len=3)
