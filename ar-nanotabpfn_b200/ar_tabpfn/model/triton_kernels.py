@@ -127,32 +127,89 @@ def _pack_buffer(k_buf: Tensor, v_buf: Tensor) -> Tensor:
     return torch.stack([k_buf, v_buf], dim=3).contiguous()
 
 
+def _stream_lengths(mask: Optional[Tensor], B: int, H: int, Lq: int, Nb: int, device) -> Optional[Tensor]:
+    """A buffer mask (True = visible, broadcastable to [B,H,Lq,Nb]) as per-stream lengths [B] int32.
+    The kernels take ragged buffers as one visible-prefix length per stream, which covers the masks
+    the reference itself uses on this path; any other pattern is refused."""
+    if mask is None:
+        return None
+    m = mask.to(device=device, dtype=torch.bool).expand(B, H, Lq, Nb)
+    lens = m[:, 0, 0].sum(dim=-1)
+    want = torch.arange(Nb, device=device)[None, None, None, :] < lens[:, None, None, None]
+    if not torch.equal(m, want.expand(B, H, Lq, Nb)):
+        raise NotImplementedError("buffer masks must be one visible prefix per stream (the same for every head "
+                                  "and query); use hybrid_teacher_forcing_attention for the block-causal pattern")
+    return lens.to(torch.int32).contiguous()
+
+
+def _buffer_merge(q: Tensor, kv: Tensor, lens: Optional[Tensor], partials, want_lse: bool):
+    """Buffer pass + LSE merge for queries q [B,H,Lq,Dh] over packed private K/V [B,H,Nb,2,Dh];
+    ``partials(qr, n)`` returns the context partials (o, l, n_splits) of n queries per stream."""
+    lib = _lib.lib()
+    B, H, Lq, Dh = q.shape
+    Nb = kv.shape[2]
+    outs, lses = [], []
+    for j0 in range(0, Lq, 2):
+        n = min(2, Lq - j0)
+        qr = _rows(q[:, :, j0:j0 + n])
+        o, l, splits = partials(qr, n)
+        merged = torch.empty(B * n, H, Dh, device=q.device, dtype=torch.float32)
+        lse = torch.empty(B * n, H, device=q.device, dtype=torch.float32) if want_lse else None
+        _lib.check(lib.artab_buffer_attention_merge_ragged(
+            _lib.dtype_code(q.dtype), _lib.ptr(qr), _lib.ptr(kv) if Nb else None, B, H, Dh, Nb, n, _lib.ptr(lens),
+            Nb, _lib.ptr(o), _lib.ptr(l), splits, B * n, _lib.ptr(merged), _lib.ptr(lse), _lib.stream_ptr()))
+        outs.append(_unrows(merged, B, n))
+        if want_lse:
+            lses.append(lse.view(B, n, H).permute(0, 2, 1))
+    return torch.cat(outs, dim=2), (torch.cat(lses, dim=2) if want_lse else None)
+
+
+def pytorch_buffer_attention(q: Tensor, k_buf: Tensor, v_buf: Tensor, mask: Optional[Tensor] = None,
+                             scale: Optional[float] = None) -> Tuple[Tensor, Tensor]:
+    """Attention of q [B,H,Lq,Dh] over each stream's private K/V [B,H,Nb,Dh] -> out (q dtype),
+    lse [B,H,Lq] fp32.  ``mask``: one visible prefix per stream (ragged buffers); a query that
+    sees nothing gets out = 0 and lse = -inf, like the reference (triton_kernels.py:570-614).
+    The name is the reference's; the work runs in the buffer-pass kernel."""
+    B, H, Lq, Dh = q.shape
+    Nb = k_buf.shape[2]
+    lens = _stream_lengths(mask, B, H, Lq, Nb, q.device)
+    kv = _pack_buffer(k_buf.to(q.dtype), v_buf.to(q.dtype))
+
+    def no_context(qr, n):
+        return (torch.zeros(1, B * n, H, Dh, device=q.device, dtype=torch.float32),
+                torch.full((1, B * n, H), float("-inf"), device=q.device, dtype=torch.float32), 1)
+
+    out, lse = _buffer_merge(_scaled(q, scale), kv, lens, no_context, want_lse=True)
+    return out.to(q.dtype), lse
+
+
+def pytorch_context_attention(q: Tensor, k_ctx: Tensor, v_ctx: Tensor,
+                              scale: Optional[float] = None) -> Tuple[Tensor, Tensor]:
+    """The reference's eager form of the context attention (triton_kernels.py:532-567); here the
+    same kernel as ``triton_context_attention``."""
+    return triton_context_attention(q, k_ctx, v_ctx, scale=scale)
+
+
 def hybrid_attention(q: Tensor, k_ctx: Tensor, v_ctx: Tensor, k_buf: Tensor, v_buf: Tensor,
                      buf_mask: Optional[Tensor] = None, use_triton: bool = True) -> Tensor:
-    """Shared-context attention + private-buffer attention merged by log-sum-exp
-    (every query sees every buffer key).  Returns [B,H,Lq,Dh]."""
-    if buf_mask is not None:
-        raise NotImplementedError("arbitrary buffer masks are not supported; "
-                                  "use hybrid_teacher_forcing_attention for the block-causal pattern")
+    """Shared-context attention + private-buffer attention merged by log-sum-exp.  Every query
+    sees every buffer key of its stream, or with ``buf_mask`` the stream's visible prefix (ragged
+    buffer lengths).  Returns [B,H,Lq,Dh]."""
     B, H, Lq, Dh = q.shape
     Nb = k_buf.shape[2]
     if Nb == 0:
         return triton_context_attention(q, k_ctx, v_ctx)[0]
     lib = _lib.lib()
+    lens = _stream_lengths(buf_mask, B, H, Lq, Nb, q.device)
     k, v, Nc, Ncp = pack_context(k_ctx.to(q.dtype), v_ctx.to(q.dtype))
     kv = _pack_buffer(k_buf.to(q.dtype), v_buf.to(q.dtype))
-    outs = []
-    for j0 in range(0, Lq, 2):
-        n = min(2, Lq - j0)
-        qr = _rows(q[:, :, j0:j0 + n])
+
+    def context(qr, n):
         splits = lib.artab_plan_splits(_lib.dtype_code(q.dtype), B * n, n, 1, H, Nc)
         o, l = _context_partials(qr, k, v, Nc, Ncp, n, splits)
-        merged = torch.empty(B * n, H, Dh, device=q.device, dtype=torch.float32)
-        _lib.check(lib.artab_buffer_attention_merge(
-            _lib.dtype_code(q.dtype), _lib.ptr(qr), _lib.ptr(kv), B, H, Dh, Nb, 0, n, Nb, _lib.ptr(o), _lib.ptr(l),
-            splits, B * n, _lib.ptr(merged), _lib.stream_ptr()))
-        outs.append(_unrows(merged, B, n))
-    return torch.cat(outs, dim=2).to(q.dtype)
+        return o, l, splits
+
+    return _buffer_merge(q, kv, lens, context, want_lse=False)[0].to(q.dtype)
 
 
 def hybrid_teacher_forcing_attention(q: Tensor, k_ctx: Tensor, v_ctx: Tensor, k_buf: Tensor, v_buf: Tensor,

@@ -719,6 +719,37 @@ int artab_buffer_attention_merge(int dtype, const void* q, const void* kv_buf, i
   return launch_buf_merge(b, (cudaStream_t)stream);
 }
 
+int artab_buffer_attention_merge_ragged(int dtype, const void* q, const void* kv_buf, int n_streams, int n_heads,
+                                        int head_dim, int max_buf, int n_new, const int32_t* lens, int len_max,
+                                        const float* o_part, const float* lse_part, int n_splits, int rows,
+                                        float* out, float* lse_out, void* stream) {
+  ARTAB_REQUIRE(q && o_part && lse_part && out && n_splits >= 1, ARTAB_EINVAL,
+                "buffer_attention_merge_ragged: null pointer");
+  ARTAB_REQUIRE(kv_buf || len_max == 0, ARTAB_EINVAL, "buffer_attention_merge_ragged: kv_buf is null");
+  ARTAB_REQUIRE((n_new == 1 || n_new == 2) && len_max >= 0 && len_max <= max_buf && rows == n_streams * n_new,
+                ARTAB_EINVAL, "buffer_attention_merge_ragged: inconsistent sizes");
+  BufMergeArgs b;
+  memset(&b, 0, sizeof(b));
+  b.dtype = dtype;
+  b.q = q;
+  b.kv_buf = kv_buf;
+  b.n_heads = n_heads;
+  b.head_dim = head_dim;
+  b.max_buf = max_buf;
+  b.n_new = n_new;
+  b.len0 = len_max;
+  b.lens = lens;
+  b.lse_out = lse_out;
+  b.n_items = (long)n_streams * n_heads;
+  b.o_part = o_part;
+  b.lse_part = lse_part;
+  b.n_splits = n_splits;
+  b.rows = rows;
+  b.scale = 1.0f / sqrtf((float)head_dim);
+  b.out = out;
+  return launch_buf_merge(b, (cudaStream_t)stream);
+}
+
 int artab_kv_append(int dtype, void* kv_buf, const void* k_new, const void* v_new, int n_streams, int n_heads,
                     int head_dim, int max_buf, int pos, void* stream) {
   ARTAB_REQUIRE(kv_buf && k_new && v_new, ARTAB_EINVAL, "kv_append: null pointer");

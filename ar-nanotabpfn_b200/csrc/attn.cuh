@@ -27,6 +27,8 @@ struct BufMergeArgs {
   int mode_tf, nt, n_new, len0;  // mode_tf: 0 decode step, 1 teacher forcing, 2 per-token visible prefix
   const int32_t* visible;  // mode 2: [tps] token j of a stream sees buffer keys [0, visible[j])
   int tps;                 // mode 2: tokens per stream
+  const int32_t* lens;     // mode 0: [B] visible buffer rows of each stream, clamped to len0 (null: len0 for all)
+  float* lse_out;          // optional [rows][H]: natural-log LSE of the merged attention (-inf: nothing visible)
   long n_items;
   const float* o_part;    // [splits][rows][H][Dh]
   const float* lse_part;  // [splits][rows][H]

@@ -195,7 +195,7 @@ __global__ void __launch_bounds__(128, 6) buf_merge_kernel(const BufMergeArgs a)
   } else {
     b = item / a.n_heads;
     h = (int)(item - b * a.n_heads);
-    len = a.len0;
+    len = a.lens ? min(max(__ldg(a.lens + b), 0), a.len0) : a.len0;
     row_t = b * a.n_new + a.n_new - 1;
     row_b = a.n_new == 2 ? b * a.n_new : -1;
   }
@@ -357,6 +357,7 @@ __global__ void __launch_bounds__(128, 6) buf_merge_kernel(const BufMergeArgs a)
         o[e + 3] = fmaf(ws, v.w, o[e + 3]);
       }
     }
+    if (a.lse_out && lane == 0) a.lse_out[(size_t)r * a.n_heads + h] = wsum > 0.f ? top + logf(wsum) : -INFINITY;
     if (grp == 0) {
       const float inv = wsum > 0.f ? 1.0f / wsum : 0.f;
 #pragma unroll

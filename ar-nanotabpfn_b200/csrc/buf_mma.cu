@@ -84,7 +84,7 @@ __global__ void __launch_bounds__(WPB * 32, 6) buf_mma_kernel(const BufMergeArgs
   } else {
     b = item / a.n_heads;
     h = (int)(item - b * a.n_heads);
-    len = a.len0;
+    len = a.lens ? min(max(__ldg(a.lens + b), 0), a.len0) : a.len0;
     rows2[0] = b * a.n_new + a.n_new - 1;
     rows2[1] = a.n_new == 2 ? b * a.n_new : -1;
   }
@@ -231,6 +231,7 @@ __global__ void __launch_bounds__(WPB * 32, 6) buf_mma_kernel(const BufMergeArgs
       out[2 * j + 1] = fmaf(ws, v.y, out[2 * j + 1]);
     }
   }
+  if (a.lse_out && t4 == 0) a.lse_out[(size_t)r * a.n_heads + h] = wsum > 0.f ? top + logf(wsum) : -INFINITY;
   const float inv = wsum > 0.f ? 1.0f / wsum : 0.f;
 #pragma unroll
   for (int j = 0; j < 4; ++j) {

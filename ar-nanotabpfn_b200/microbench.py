@@ -1,7 +1,8 @@
 """Kernel micro-benchmarks through the C ABI (CUDA-event timed, one JSON line each).
 
     python ar-nanotabpfn_b200/microbench.py ctx     [--streams 1024 --heads 4 --ctx 4096 --lq 1 --splits 0]
-    python ar-nanotabpfn_b200/microbench.py buffer  [--streams 1024 --heads 4 --len 63 --uniform]
+    python ar-nanotabpfn_b200/microbench.py config2 [--streams 1024 --heads 4 --ctx 4096 --len 63]
+    python ar-nanotabpfn_b200/microbench.py buffer  [--streams 1024 --heads 4 --len 63]
     python ar-nanotabpfn_b200/microbench.py append  [--streams 4096 --heads 6 --max-buf 256]
     python ar-nanotabpfn_b200/microbench.py chain   [--streams 512 --ctx 1024 --targets 8]
     python ar-nanotabpfn_b200/microbench.py config4 [--datasets 64 --ctx 2048 --targets 256]
@@ -10,9 +11,10 @@
 ``ctx`` is the shared-context decode-attention micro-benchmark: bf16, head_dim 32,
 every stream carries ``lq`` queries against one shared context K/V ~ N(0,1); the
 tcgen05 context contraction is timed alone.  ``buffer`` times the warp-level pass
-over the private buffer K/V with the log-sum-exp merge (per-stream lengths are
-uniform in [0, len] with --uniform, the kernel is launched once per distinct
-length group otherwise all streams use ``len``).  ``append`` times the in-place
+over the private buffer K/V with the log-sum-exp merge (all streams at ``len`` keys).
+``config2`` is the whole decode attention of the second benchmark configuration: one query
+per stream, shared context, private buffers of ragged length (uniform in [0, len], one
+length per stream handed to the kernel) and the merge.  ``append`` times the in-place
 K/V append.  ``chain`` runs a short shared-context sampling job (6 layers, d_model 192,
 6 heads, d_ff 768, bf16 mode) and reports the serialised per-launch time of every kernel
 kind, the per-token dense chain among them.  ``config4`` times the teacher-forced joint
@@ -150,6 +152,53 @@ def bench_buffer(a):
         "kv_bytes": byts, "working_set_mb": kv.numel() * esz / 2 ** 20, "ms": ms, "gbs": ach, "peak_gbs": peak,
         "frac": ach / peak, "peak_source": "measured" if pk else "fallback",
         "max_abs_err": float((got - want).abs().max())}), flush=True)
+
+
+def bench_config2(a):
+    """The decode-attention configuration as one unit: tcgen05 context contraction + ragged
+    buffer pass (per-stream length uniform in [0, len]) + fp32 LSE merge, two launches."""
+    lib = _lib.lib()
+    dev = torch.device("cuda")
+    g = torch.Generator(device=dev).manual_seed(1)
+    B, H, Nc, Dh, Nb = a.streams, a.heads, a.ctx, 32, a.len
+    q = torch.randn(B, H, Dh, device=dev, generator=g).bfloat16()
+    k = torch.randn(H, Nc, Dh, device=dev, generator=g).bfloat16()
+    v = torch.randn(H, Nc, Dh, device=dev, generator=g).bfloat16()
+    kv = torch.randn(B, H, Nb, 2, Dh, device=dev, generator=g).bfloat16()
+    lens = torch.randint(0, Nb + 1, (B,), device=dev, generator=g).to(torch.int32)
+    kp, vp, _, Ncp = tk.pack_context(k, v)
+    splits = a.splits or lib.artab_plan_splits(_lib.BF16, B, 1, 1, H, Nc)
+    o = torch.empty(splits, B, H, Dh, device=dev)
+    l = torch.empty(splits, B, H, device=dev)
+    out = torch.empty(B, H, Dh, device=dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    st = _lib.stream_ptr()
+
+    def fn():
+        _lib.check(lib.artab_context_attention(_lib.BF16, _lib.ptr(q), _lib.ptr(kp), _lib.ptr(vp), B, B, 1, H, Dh, Nc,
+                                               Ncp, splits, _lib.ptr(o), _lib.ptr(l), _lib.ptr(status), st))
+        _lib.check(lib.artab_buffer_attention_merge_ragged(_lib.BF16, _lib.ptr(q), _lib.ptr(kv), B, H, Dh, Nb, 1,
+                                                           _lib.ptr(lens), Nb, _lib.ptr(o), _lib.ptr(l), splits, B,
+                                                           _lib.ptr(out), None, st))
+
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    ms = time_launches(fn, a.iters, a.warmup, flush)
+    # parity: fp32 softmax over [context | visible buffer keys] on the same bf16 tensors
+    qq = q.float().unsqueeze(2)                                               # [B,H,1,Dh]
+    kf = torch.cat([k.float().unsqueeze(0).expand(B, -1, -1, -1), kv[:, :, :, 0].float()], dim=2)
+    vf = torch.cat([v.float().unsqueeze(0).expand(B, -1, -1, -1), kv[:, :, :, 1].float()], dim=2)
+    vis = torch.arange(Nb, device=dev)[None, :] < lens[:, None]
+    full = torch.cat([torch.ones(B, Nc, dtype=torch.bool, device=dev), vis], dim=1)[:, None, None, :]
+    sc = (torch.matmul(qq, kf.transpose(-1, -2)) * Dh ** -0.5).masked_fill(~full, float("-inf"))
+    want = torch.matmul(torch.softmax(sc, -1), vf)[:, :, 0]
+    rel = (out - want).norm(dim=-1) / want.norm(dim=-1).clamp_min(1e-6)
+    flops = 4.0 * Dh * Nc * B * H
+    pk = peaks()
+    print(json.dumps({
+        "bench": "config2", "streams": B, "heads": H, "ctx": Nc, "buffer_len": f"uniform 0..{Nb}", "splits": splits,
+        "ms": ms, "ctx_tflops": flops / (ms * 1e-3) / 1e12, "buffer_bytes": float(lens.sum()) * H * 2 * Dh * 2,
+        "queries_per_s": B / (ms * 1e-3), "max_rel_err_out": float(rel.max()), "status": int(status.item()),
+        "peak_tflops": pk.get("bf16_tflops", 1590.0), "peak_source": "measured" if pk else "fallback"}), flush=True)
 
 
 def bench_append(a):
@@ -323,7 +372,7 @@ def bench_config5(a):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("which", choices=["ctx", "buffer", "append", "chain", "config4", "config5"])
+    ap.add_argument("which", choices=["ctx", "config2", "buffer", "append", "chain", "config4", "config5"])
     ap.add_argument("--datasets", type=int, default=64)
     ap.add_argument("--targets", type=int, default=None)
     ap.add_argument("--streams", type=int, default=None)
@@ -338,13 +387,13 @@ def main():
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     a = ap.parse_args()
-    defaults = {"ctx": dict(streams=1024, ctx=4096), "buffer": dict(streams=1024), "append": dict(streams=4096),
+    defaults = {"ctx": dict(streams=1024, ctx=4096), "config2": dict(streams=1024, ctx=4096), "buffer": dict(streams=1024), "append": dict(streams=4096),
                 "chain": dict(streams=512, ctx=1024, targets=8), "config4": dict(ctx=2048, targets=256),
                 "config5": dict(streams=4096, ctx=16384, targets=256)}[a.which]
     for k, v in defaults.items():
         if getattr(a, k) is None:
             setattr(a, k, v)
-    {"ctx": bench_ctx, "buffer": bench_buffer, "append": bench_append, "chain": bench_chain,
+    {"ctx": bench_ctx, "config2": bench_config2, "buffer": bench_buffer, "append": bench_append, "chain": bench_chain,
      "config4": bench_config4, "config5": bench_config5}[a.which](a)
 
 

@@ -259,6 +259,24 @@ ARTAB_API int artab_buffer_attention_merge(int dtype, const void* q, const void*
                                  const float* o_part, const float* lse_part, int n_splits, int rows,
                                  float* out, void* stream);
 
+/* The decode form of artab_buffer_attention_merge with RAGGED private buffers: stream b sees
+ * its first lens[b] buffer rows (int32 device array [B], values clamped to [0, len_max];
+ * NULL: len_max for every stream), the same for every head and for both queries of a stream.
+ * This is pytorch_buffer_attention's / hybrid_attention's `mask` argument when the mask is a
+ * per-stream length (the reference's own masked test case and the ragged 0..63-key buffers
+ * of its decode-attention micro-benchmark).  A query with no visible buffer row and no
+ * finite context partial gives out = 0.
+ *   lse_out [rows][H] fp32 (may be NULL): natural-log LSE of the merged attention, -inf when
+ *   nothing is visible; with one context partial of lse = -inf this is the buffer attention's
+ *   own LSE, which makes the call pytorch_buffer_attention.
+ * Replaces pytorch_buffer_attention with a mask, merge_attention_outputs
+ * (ar_tabpfn/model/triton_kernels.py:570-614, 478-524) and hybrid_attention's buf_mask
+ * (ar_tabpfn/model/triton_kernels.py:705-755). */
+ARTAB_API int artab_buffer_attention_merge_ragged(int dtype, const void* q, const void* kv_buf, int n_streams,
+                                        int n_heads, int head_dim, int max_buf, int n_new, const int32_t* lens,
+                                        int len_max, const float* o_part, const float* lse_part, int n_splits,
+                                        int rows, float* out, float* lse_out, void* stream);
+
 /* In-place append of one new K/V row per (stream, head) at position `pos`.
  *   k_new, v_new [B][H][Dh] (dtype).
  * Replaces the slice assignment into k_buf_cache / v_buf_cache

@@ -2,7 +2,7 @@
 
 Run once, in a container where the reference checkout is available:
 
-    python tests/golden/make_golden.py /path/to/reference [--forward-only]
+    python tests/golden/make_golden.py /path/to/reference [--forward-only | --ragged-only]
 
 It imports the reference's ``ar_tabpfn.model`` package under the alias
 ``ref_ar_tabpfn`` (so it cannot collide with the shipped drop-in package of
@@ -209,6 +209,26 @@ def forward_fixture(ref, root):
     return cases
 
 
+@torch.no_grad()
+def ragged_fixture(tk):
+    """Ragged private buffers: the reference's masked buffer attention and hybrid attention with
+    one visible prefix per stream (lengths include 0 = nothing visible and the full buffer)."""
+    g = torch.Generator().manual_seed(77)
+    cases = []
+    for (B, H, Lq, Nc, Dh, Nb) in [(9, 4, 1, 64, 32, 12), (5, 2, 2, 40, 16, 7), (6, 3, 1, 33, 64, 20),
+                                   (16, 4, 2, 128, 32, 63)]:
+        rn = lambda *s: torch.randn(*s, generator=g)
+        q, k, v = rn(B, H, Lq, Dh), rn(H, Nc, Dh), rn(H, Nc, Dh)
+        kb, vb = rn(B, H, Nb, Dh), rn(B, H, Nb, Dh)
+        lens = torch.randint(0, Nb + 1, (B,), generator=g)
+        lens[0], lens[-1] = 0, Nb
+        mask = (torch.arange(Nb)[None, :] < lens[:, None])[:, None, None, :].expand(B, H, Lq, Nb).contiguous()
+        o_b, l_b = tk.pytorch_buffer_attention(q, kb, vb, mask=mask)
+        cases.append(dict(q=q, k_ctx=k, v_ctx=v, k_buf=kb, v_buf=vb, lens=lens, mask=mask, out_buf=o_b, lse_buf=l_b,
+                          hybrid=tk.hybrid_attention(q, k, v, kb, vb, buf_mask=mask, use_triton=False)))
+    return cases
+
+
 def compact(o):
     """Clone every tensor so that no view drags a larger storage into the file."""
     if isinstance(o, torch.Tensor):
@@ -226,6 +246,10 @@ def main():
     root = sys.argv[1]
     ref, tk = import_reference(root)
     torch.set_num_threads(8)
+    if "--ragged-only" in sys.argv[2:]:       # leaves the other fixtures as they are
+        torch.save(compact(ragged_fixture(tk)), os.path.join(HERE, "ragged.pt"))
+        print("ragged.pt", os.path.getsize(os.path.join(HERE, "ragged.pt")))
+        return
     if "--forward-only" in sys.argv[2:]:      # leaves the other fixtures as they are
         torch.save(compact(forward_fixture(ref, root)), os.path.join(HERE, "forward.pt"))
         print("forward.pt", os.path.getsize(os.path.join(HERE, "forward.pt")))
@@ -248,7 +272,8 @@ def main():
         Nc=200, Nt=12, B=6, shared_data=True, variate_seed=11)
     torch.save(compact(h32), os.path.join(HERE, "dh32.pt"))
     torch.save(compact(forward_fixture(ref, root)), os.path.join(HERE, "forward.pt"))
-    for f in ("ops.pt", "config1.pt", "tiny_distinct.pt", "dh32.pt", "forward.pt"):
+    torch.save(compact(ragged_fixture(tk)), os.path.join(HERE, "ragged.pt"))
+    for f in ("ops.pt", "config1.pt", "tiny_distinct.pt", "dh32.pt", "forward.pt", "ragged.pt"):
         print(f, os.path.getsize(os.path.join(HERE, f)))
 
 

@@ -167,3 +167,52 @@ def test_embedder_and_head_vs_oracle():
     assert y3.shape == (B, T, 3, 1) and torch.isfinite(y3).all()
     torch.testing.assert_close(y3[:, :, 0, 0].cpu(), want, atol=1e-5, rtol=1e-5)
     assert not torch.equal(y3[:, :, 0], y3[:, :, 1])
+
+
+def test_ragged_buffers_fp32_golden(tk):
+    """Per-stream buffer lengths (0 .. Nb) through pytorch_buffer_attention's mask and
+    hybrid_attention's buf_mask, against the reference's outputs; head sizes 16 / 32 / 64."""
+    for c in load_golden("ragged.pt"):
+        out, lse = tk.pytorch_buffer_attention(cu(c["q"]), cu(c["k_buf"]), cu(c["v_buf"]), mask=cu(c["mask"]))
+        torch.testing.assert_close(out.cpu(), c["out_buf"], atol=1e-5, rtol=1e-5)
+        lse = lse.cpu()
+        assert torch.equal(torch.isinf(lse), torch.isinf(c["lse_buf"]))
+        fin = torch.isfinite(lse)
+        torch.testing.assert_close(lse[fin], c["lse_buf"][fin], atol=1e-5, rtol=1e-5)
+        # a [B,1,1,Nb] mask broadcasts like the reference's masked_fill
+        hyb = tk.hybrid_attention(cu(c["q"]), cu(c["k_ctx"]), cu(c["v_ctx"]), cu(c["k_buf"]), cu(c["v_buf"]),
+                                  buf_mask=cu(c["mask"][:, :1, :1]))
+        torch.testing.assert_close(hyb.cpu(), c["hybrid"], atol=1e-5, rtol=1e-5)
+    c = load_golden("ragged.pt")[0]
+    bad = c["mask"].clone()
+    bad[1, 0, 0, 0] = False                                # a hole in front of visible keys
+    bad[1, 0, 0, 1] = True
+    with pytest.raises(NotImplementedError):
+        tk.pytorch_buffer_attention(cu(c["q"]), cu(c["k_buf"]), cu(c["v_buf"]), mask=cu(bad))
+    # unmasked call: every key visible
+    o2, l2 = tk.pytorch_buffer_attention(cu(c["q"]), cu(c["k_buf"]), cu(c["v_buf"]))
+    w2, wl2 = orc.buffer_attention(c["q"], c["k_buf"], c["v_buf"])
+    torch.testing.assert_close(o2.cpu(), w2, atol=1e-5, rtol=1e-5)
+    torch.testing.assert_close(l2.cpu(), wl2, atol=1e-5, rtol=1e-5)
+
+
+def test_decode_attention_microbenchmark_shapes_bf16(tk):
+    """The decode-attention micro-benchmark configuration: bf16, seed 1, 4 heads, head_dim 32,
+    4096 shared context keys ~ N(0,1), 1024 streams with one query each and a private buffer of
+    0..63 keys (uniform), fp32 LSE merge.  Checked against fp32 softmax attention over
+    [context | visible buffer keys] on the same bf16 tensors: outputs within 1e-2 relative."""
+    g = torch.Generator().manual_seed(1)
+    B, H, Dh, Nc, Nb = 1024, 4, 32, 4096, 63
+    rn = lambda *s: torch.randn(*s, generator=g).to(torch.bfloat16)
+    q, k, v = rn(B, H, 1, Dh), rn(H, Nc, Dh), rn(H, Nc, Dh)
+    kb, vb = rn(B, H, Nb, Dh), rn(B, H, Nb, Dh)
+    lens = torch.randint(0, Nb + 1, (B,), generator=g)
+    mask = (torch.arange(Nb)[None, :] < lens[:, None])[:, None, None, :]
+    got = tk.hybrid_attention(cu(q), cu(k), cu(v), cu(kb), cu(vb), buf_mask=cu(mask)).float().cpu()
+    kf = torch.cat([k.float().unsqueeze(0).expand(B, -1, -1, -1), kb.float()], dim=2)
+    vf = torch.cat([v.float().unsqueeze(0).expand(B, -1, -1, -1), vb.float()], dim=2)
+    full = torch.cat([torch.ones(B, 1, 1, Nc, dtype=torch.bool), mask], dim=-1)
+    want, _ = ref_attention(q, kf, vf, mask=full)
+    rel = (got - want).norm(dim=-1) / want.norm(dim=-1).clamp_min(1e-6)
+    assert rel.max() <= 1e-2, rel.max()
+    assert (lens == 0).any() and (lens == Nb).any()

@@ -155,3 +155,17 @@ def test_row_mask_factory_matches_oracle():
     assert RowMask.teacher_forcing(8, 4).visible == [1, 2, 3, 4, 0, 1, 2, 3]
     with pytest.raises(ValueError):
         create_row_mask(num_rows=5, context_len=4, buffer_len=3)
+
+
+def test_ragged_buffer_attention_matches_reference():
+    """Masked buffer attention and hybrid attention with one visible prefix per stream
+    (lengths 0 .. Nb), against the reference's eager operators."""
+    for c in load("ragged.pt"):
+        out, lse = orc.buffer_attention(c["q"], c["k_buf"], c["v_buf"], mask=c["mask"])
+        torch.testing.assert_close(out, c["out_buf"], atol=1e-6, rtol=1e-6)
+        assert torch.equal(torch.isinf(lse), torch.isinf(c["lse_buf"]))
+        fin = torch.isfinite(lse)
+        torch.testing.assert_close(lse[fin], c["lse_buf"][fin], atol=1e-6, rtol=1e-6)
+        assert (out[c["lens"] == 0] == 0).all()          # nothing visible: zero output
+        hyb = orc.hybrid_attention(c["q"], c["k_ctx"], c["v_ctx"], c["k_buf"], c["v_buf"], buf_mask=c["mask"])
+        torch.testing.assert_close(hyb, c["hybrid"], atol=1e-6, rtol=1e-6)
