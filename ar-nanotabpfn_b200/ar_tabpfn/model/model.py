@@ -216,6 +216,29 @@ class ARTabPFN(nn.Module):
         self.head = MixtureGaussianHead(d_model, d_ff, dim_y=1, num_components=num_components)
         self.ar_tokens = nn.Parameter(torch.randn(buffer_size, d_model) * 0.02)
 
+    @classmethod
+    def from_checkpoint(cls, path_or_dict, n_heads: int, num_features: int = 10, map_location="cpu") -> "ARTabPFN":
+        """Build a model from a checkpoint of the reference's training script
+        (``torch.save({"step": ..., "model": model.state_dict()})``, train.py:340-342) or from a
+        plain state_dict.  The training script compiles ``embedder`` and ``head``, which prefixes
+        their keys with ``_orig_mod.``; the prefix is removed.  Every size but the head count
+        (not recoverable from the weights) and ``num_features`` (no weight depends on it) is read
+        from the tensor shapes."""
+        ck = torch.load(path_or_dict, map_location=map_location, weights_only=True) \
+            if isinstance(path_or_dict, (str, bytes)) or hasattr(path_or_dict, "__fspath__") else path_or_dict
+        sd = ck["model"] if isinstance(ck, dict) and "model" in ck and isinstance(ck["model"], dict) else ck
+        sd = {k.replace("_orig_mod.", ""): v for k, v in sd.items()}
+        S, D = sd["ar_tokens"].shape
+        L = 0
+        while f"backbone.layers.{L}.norm1.weight" in sd:
+            L += 1
+        if L == 0 or D % n_heads:
+            raise ValueError("checkpoint has no transformer layers or d_model is not divisible by n_heads")
+        m = cls(d_model=D, n_heads=n_heads, n_layers=L, d_ff=sd["backbone.layers.0.ff.0.weight"].shape[0],
+                num_features=num_features, buffer_size=S, num_components=sd["head.mean_bias"].numel())
+        m.load_state_dict(sd)
+        return m.eval()
+
     @torch.no_grad()
     def forward(self, x_context: Tensor, y_context: Tensor, x_buffer: Tensor, y_buffer: Tensor,
                 x_target: Tensor, mask_features, mask_rows, y_target: Optional[Tensor] = None):

@@ -58,3 +58,26 @@ def test_state_dict_is_reference_compatible():
     assert set(own) == set(fx["state_dict"])
     for k, v in fx["state_dict"].items():
         assert own[k].shape == v.shape, k
+
+
+def test_checkpoint_of_the_training_script_loads(tmp_path):
+    """{"step", "model"} files whose embedder / head keys carry torch.compile's ``_orig_mod.``
+    prefix load into the drop-in model with every size read from the shapes (host logic only)."""
+    import torch
+    import ar_tabpfn
+    src = ar_tabpfn.ARTabPFN(d_model=64, n_heads=4, n_layers=3, d_ff=128, num_features=10, buffer_size=32,
+                             num_components=20)
+    sd = {}
+    for k, v in src.state_dict().items():
+        head, _, rest = k.partition(".")
+        sd[f"{head}._orig_mod.{rest}" if head in ("embedder", "head") else k] = v.clone()
+    path = tmp_path / "step_10.pt"
+    torch.save({"step": 10, "model": sd}, path)
+    m = ar_tabpfn.ARTabPFN.from_checkpoint(str(path), n_heads=4)
+    assert (m.d_model, m.buffer_size, len(m.backbone.layers), m.head.num_components) == (64, 32, 3, 20)
+    for k, v in src.state_dict().items():
+        assert torch.equal(m.state_dict()[k], v)
+    assert not m.training
+    import pytest
+    with pytest.raises(ValueError):
+        ar_tabpfn.ARTabPFN.from_checkpoint(sd, n_heads=5)

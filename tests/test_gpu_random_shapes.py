@@ -11,7 +11,7 @@ import artab_oracle as orc
 pytestmark = pytest.mark.gpu
 
 CASES = [
-    # d_model, heads, layers, d_ff, F, Nc, Nt, B [, mixture components]
+    # d_model, heads, layers, d_ff, F, Nc, Nt, B [, mixture components [, AR position tokens]]
     (64, 2, 2, 128, 5, 9, 3, 4),        # Dh 32, one hidden tile (no pair), tiny
     (64, 4, 1, 256, 3, 131, 17, 7),     # Dh 16 (scalar attention), tensor-core chain with pairs
     (128, 4, 2, 256, 8, 64, 33, 5),     # Dh 32, buffer crosses two MMA blocks, context = half a key tile
@@ -27,6 +27,7 @@ CASES = [
     (128, 4, 1, 256, 4, 20, 125, 38),   # 9500 rows = 75 tiles: one CTA per tile
     (128, 4, 1, 256, 6, 70, 12, 3, 3),  # three mixture components
     (128, 4, 1, 256, 6, 70, 12, 3, 8),  # eight: 24 head outputs, beyond the tensor-core chain's 16 -> fp32 dense kernel
+    (64, 4, 12, 128, 10, 48, 40, 3, 20, 32),  # the reference training script's default model: 12 layers, 20 components, 32 AR tokens
 ]
 
 
@@ -54,12 +55,13 @@ def _problem(seed, cfg, Nc, Nt, B, shared):
     return m, sd, x[:, :Nc].contiguous(), y[:, :Nc].contiguous(), x[:, Nc:].contiguous(), y[:, Nc:].contiguous()
 
 
-@pytest.mark.parametrize("case", CASES, ids=lambda c: "d%d_h%d_l%d_ff%d_F%d_nc%d_nt%d_b%d" % c[:8] + ("_k%d" % c[8] if len(c) > 8 else ""))
+@pytest.mark.parametrize("case", CASES, ids=lambda c: "d%d_h%d_l%d_ff%d_F%d_nc%d_nt%d_b%d" % c[:8] + ("_k%d" % c[8] if len(c) > 8 else "") + ("_s%d" % c[9] if len(c) > 9 else ""))
 def test_joint_density_against_oracle(case):
     from ar_tabpfn.model import ARTabPFNPredictor
     D, H, L, Dff, F, Nc, Nt, B = case[:8]
     K = case[8] if len(case) > 8 else 5
-    cfg = dict(d_model=D, n_heads=H, n_layers=L, d_ff=Dff, num_features=F, buffer_size=8, num_components=K)
+    S = case[9] if len(case) > 9 else 8
+    cfg = dict(d_model=D, n_heads=H, n_layers=L, d_ff=Dff, num_features=F, buffer_size=S, num_components=K)
     for shared, backend in ((True, "triton_shared_context"), (False, "flex_attention")):
         m, sd, xc, yc, xt, yt = _problem(11 + D + Nc, cfg, Nc, Nt, B, shared)
         want = orc.OraclePredictor(sd, H).evaluate_joint_density(xc, yc, xt, yt, shared=shared)
