@@ -124,7 +124,7 @@ class ARTabPFNPredictor:
         if t is None or t.dtype != dtype or t.device != self._device or t.numel() < n:
             t = torch.zeros(max(n, 1), dtype=dtype, device=self._device)
             self._bufs[name] = t
-        return t[:n].view(*shape) if n else t[:0]
+        return t[:n].view(*shape)
 
     def _ensure_rows(self, rows: int) -> None:
         """Row workspaces (residual stream, queries, attention output, partials)."""

@@ -118,3 +118,20 @@ def test_forward_argument_errors():
     from ar_tabpfn.model import create_dense_mask
     assert m(c["xc"].cuda(), c["yc"].cuda(), c["xb"].cuda(), c["yb"].cuda(), c["xt"].cuda(),
              create_dense_mask(1), _mask(c)) is None
+
+
+def test_forward_without_buffer_rows():
+    """Nb = 0: every target sees the context only (no private cache is laid out at all)."""
+    from ar_tabpfn.model import ARTabPFNPredictor
+    c = load_golden("forward.pt")[2]
+    m, sd = build_model(c)
+    B, F = c["xt"].shape[0], c["xt"].shape[2]
+    xb, yb = torch.zeros(B, 0, F), torch.zeros(B, 0)
+    vis = [0] * c["xt"].shape[1]
+    for backend, shared in (("flex_attention", False), ("triton_shared_context", True)):
+        want = orc.OraclePredictor(sd, c["n_heads"]).forward_masked(c["xc"], c["yc"], xb, yb, c["xt"], c["yt"], vis,
+                                                                     shared=shared)
+        p = ARTabPFNPredictor.from_trained_model(m, backend=backend)
+        got = p.forward_masked(c["xc"].cuda(), c["yc"].cuda(), xb.cuda(), yb.cuda(), c["xt"].cuda(), c["yt"].cuda(),
+                               vis)
+        torch.testing.assert_close(got.cpu(), want, atol=2e-5, rtol=1e-5)
