@@ -62,6 +62,7 @@ class ARTabPFNPredictor:
         self._bufs = {}
         self.last_logdens: Optional[Tensor] = None
         self.last_components: Optional[Tensor] = None
+        self.last_h2d_bytes = 0
 
     @classmethod
     def from_trained_model(cls, model, backend: str = "flex_attention",
@@ -85,6 +86,24 @@ class ARTabPFNPredictor:
         if dtype in (torch.bfloat16, torch.float16):
             return torch.bfloat16
         return torch.float32
+
+    def _model_device(self) -> torch.device:
+        d = next(self.backbone.parameters()).device
+        return torch.device("cuda", torch.cuda.current_device()) if d.type == "cuda" and d.index is None else d
+
+    def _work_device(self, t: Tensor) -> torch.device:
+        """Inputs may live in host memory (pinned for asynchronous copies): the work then runs on
+        the model's device and only what the path reads is copied."""
+        return t.device if t.is_cuda else self._model_device()
+
+    def _dev32(self, t: Tensor, device) -> Tensor:
+        """fp32 contiguous copy of ``t`` on ``device``; host tensors are copied on the current
+        stream and counted in ``last_h2d_bytes``."""
+        t = t.detach()
+        if not t.is_cuda:
+            self.last_h2d_bytes += t.numel() * t.element_size()
+            t = t.to(device, non_blocking=True)
+        return t.to(torch.float32).contiguous()
 
     def init_kv_cache(self, batch_size: int, max_seq_len: int, device: Optional[torch.device] = None,
                       dtype: Optional[torch.dtype] = None) -> None:
@@ -189,17 +208,19 @@ class ARTabPFNPredictor:
         lib = _lib.lib()
         if self._device is None:
             raise RuntimeError("init_kv_cache must be called before prefill_context")
-        if x_context.device != self._device:
-            raise ValueError("inputs must live on the cache device")
+        if x_context.is_cuda and x_context.device != self._device:
+            raise ValueError("inputs must live on the cache device (or in host memory)")
         if self.shared:
+            # only batch element 0 is the shared context (inference.py:191-193): a host tensor is
+            # sliced before it is copied
             x_context, y_context = x_context[0:1], y_context[0:1]
         elif x_context.shape[0] != self._batch:
             raise ValueError("batch size differs from init_kv_cache")
         G, Nc, F = x_context.shape
         self._layout(Nc)
         self._ensure_rows(max(G * Nc, 2 * self._batch))
-        xc = x_context.detach().to(torch.float32).contiguous()
-        yc = y_context.detach().to(torch.float32).reshape(G, Nc).contiguous()
+        xc = self._dev32(x_context, self._device)
+        yc = self._dev32(y_context, self._device).reshape(G, Nc)
         pm = self._packed(self._device)
         _lib.check(lib.artab_prefill(pm.ref, C.byref(self._state), _lib.ptr(xc), _lib.ptr(yc), F,
                                      _lib.stream_ptr()))
@@ -275,24 +296,59 @@ class ARTabPFNPredictor:
         ``variates = (expo [Nt,B,K], normal [Nt,B])`` replays given random numbers;
         by default they are drawn from torch's generator in the reference's order.
         The log density of each drawn value and the chosen component are kept in
-        ``last_logdens`` / ``last_components`` ([B,Nt])."""
+        ``last_logdens`` / ``last_components`` ([B,Nt]).
+
+        The inputs may also be host tensors (pinned memory makes the copies asynchronous):
+        the work runs on the model's device, the result stays there, and only what the path
+        reads is copied - with the shared-context backend that is batch element 0 of the
+        context, not B copies of it (``last_h2d_bytes`` counts the bytes)."""
         lib = _lib.lib()
         B, Nc, F = x_context.shape
         Nt = x_target.shape[1]
-        device, dtype = x_context.device, x_context.dtype
+        device, dtype = self._work_device(x_context), x_context.dtype
+        self.last_h2d_bytes = 0
         if self.shared:
             self.init_kv_cache(B, Nt, device, dtype)
         else:
             self.init_kv_cache(B, Nc + Nt, device, dtype)
+        drawn = None
+        if variates is None:
+            # The draws depend on nothing the model computes, so their launches (two small fills per
+            # step) go to a side stream AFTER the prefill has been queued: the device runs the
+            # prefill while the host is still issuing fills.  Torch advances its generator when a
+            # fill is launched and the prefill draws nothing, so the values are those of the same
+            # fills issued anywhere else in this call.
+            main = torch.cuda.current_stream(device)
+            side = self._bufs.get("side_stream")
+            if side is None or side.device != device:
+                side = self._bufs["side_stream"] = torch.cuda.Stream(device=device)
+            K = int(self.head.num_components)
+            expo = torch.empty(Nt, B, K, device=device, dtype=torch.float32)     # owned by the main stream
+            normal = torch.empty(Nt, B, device=device, dtype=torch.float32)
+            fresh = main.record_event()      # whatever used this memory before has finished by here
         self.prefill_context(x_context, y_context)
         if variates is None:
-            variates = self.draw_variates(Nt, B, device, torch.float32)
+            side.wait_event(fresh)
+            drawn = {}
+
+            def issue_draws(t0):
+                """Fills of steps [t0, t0 + 16) on the side stream; decode step t0 waits for them."""
+                if t0 >= Nt or t0 in drawn:
+                    return
+                with torch.cuda.stream(side):
+                    for t in range(t0, min(t0 + 16, Nt)):
+                        expo[t].exponential_(1)
+                        normal[t].normal_()
+                    drawn[t0] = side.record_event()
+
+            issue_draws(0)
+            variates = (expo, normal)
         expo = variates[0].detach().to(device=device, dtype=torch.float32).contiguous()
         normal = variates[1].detach().to(device=device, dtype=torch.float32).contiguous()
         K = int(self.head.num_components)
         if expo.shape != (Nt, B, K) or normal.shape != (Nt, B):
             raise ValueError("variates must be (expo [Nt,B,K], normal [Nt,B])")
-        xt = x_target.detach().to(torch.float32).contiguous()
+        xt = self._dev32(x_target, device)
         samples = torch.zeros(B, Nt, device=device, dtype=torch.float32)
         logdens = torch.zeros(B, Nt, device=device, dtype=torch.float32)
         comp = torch.zeros(B, Nt, device=device, dtype=torch.int32)
@@ -300,6 +356,9 @@ class ARTabPFNPredictor:
         st = self._state
         stream = _lib.stream_ptr()
         for t in range(Nt):
+            if drawn is not None and t % 16 == 0:
+                issue_draws(t + 16)      # the host stays one chunk ahead of the decode steps it launches
+                torch.cuda.current_stream(device).wait_event(drawn[t])
             _lib.check(lib.artab_decode_step(pm.ref, C.byref(st), _lib.ptr(xt), F, Nt, t, _lib.ptr(samples),
                                              _lib.ptr(expo[t]), _lib.ptr(normal[t]), _lib.ptr(logdens),
                                              _lib.ptr(comp), stream))
@@ -317,7 +376,8 @@ class ARTabPFNPredictor:
         lib = _lib.lib()
         B, Nc, F = x_context.shape
         Nt = x_target.shape[1]
-        device, dtype = x_context.device, x_context.dtype
+        device, dtype = self._work_device(x_context), x_context.dtype
+        self.last_h2d_bytes = 0
         if self.shared:
             self.init_kv_cache(B, Nt, device, dtype)
         else:
@@ -325,8 +385,8 @@ class ARTabPFNPredictor:
             self.init_kv_cache(B, Nc + Nt, device, dtype)
         self.prefill_context(x_context, y_context)
         self._ensure_rows(2 * B * Nt)
-        xt = x_target.detach().to(torch.float32).contiguous()
-        yt = y_target.detach().to(torch.float32).reshape(B, Nt).contiguous()
+        xt = self._dev32(x_target, device)
+        yt = self._dev32(y_target, device).reshape(B, Nt)
         out = torch.empty(B, Nt, device=device, dtype=torch.float32)
         pm = self._packed(device)
         _lib.check(lib.artab_teacher_forcing(pm.ref, C.byref(self._state), _lib.ptr(xt), _lib.ptr(yt), F, Nt,
@@ -350,14 +410,15 @@ class ARTabPFNPredictor:
             raise ValueError(f"visible must list {Nb + Nt} counts (buffer rows, then target rows)")
         if Nb > self.ar_tokens.shape[0]:
             raise ValueError(f"{Nb} buffer rows but only {self.ar_tokens.shape[0]} AR position tokens")
-        device, dtype = x_context.device, x_context.dtype
+        device, dtype = self._work_device(x_context), x_context.dtype
+        self.last_h2d_bytes = 0
         if self.shared:
             self.init_kv_cache(B, Nb, device, dtype)
         else:
             self.init_kv_cache(B, Nc + Nb, device, dtype)
         self.prefill_context(x_context, y_context)
         self._ensure_rows(B * (Nb + Nt))
-        f32 = lambda t, *shape: t.detach().to(torch.float32).reshape(*shape).contiguous()
+        f32 = lambda t, *shape: self._dev32(t, device).reshape(*shape)
         xb, yb = f32(x_buffer, B, Nb, F), f32(y_buffer, B, Nb)
         xt, yt = f32(x_target, B, Nt, F), f32(y_target, B, Nt)
         vis = torch.tensor([int(v) for v in visible], dtype=torch.int32, device=device)

@@ -94,3 +94,57 @@ def test_weights_changed_under_a_live_predictor():
         m.load_state_dict({k: v.cuda() for k, v in sd.items()})
         again = p.evaluate_joint_density(c("xc"), c("yc"), c("xt"), c("yt"))
         torch.testing.assert_close(again, before, atol=1e-6, rtol=0)
+
+
+def test_host_resident_inputs():
+    """Inputs handed over in host memory (pinned or pageable) give the same results as device
+    tensors; the shared-context backend copies the context once, not once per stream."""
+    from ar_tabpfn.model import ARTabPFNPredictor
+    from util import build_model, load_golden
+    fx = load_golden("dh32.pt")
+    m, _ = build_model(fx)
+    xc, yc, xt, yt = fx["xc"], fx["yc"], fx["xt"], fx["yt"]
+    B, Nc, F = xc.shape
+    Nt = xt.shape[1]
+    var = (fx["expo"].cuda(), fx["normal"].cuda())
+    for backend in ("triton_shared_context", "flex_attention"):
+        p = ARTabPFNPredictor.from_trained_model(m, backend=backend)
+        want = p.sample_sequence(xc.cuda(), yc.cuda(), xt.cuda(), variates=var).clone()
+        assert p.last_h2d_bytes == 0
+        for pin in (True, False):
+            h = [t.pin_memory() if pin else t.clone() for t in (xc, yc, xt, yt)]
+            got = p.sample_sequence(h[0], h[1], h[2], variates=var)
+            assert got.is_cuda and torch.equal(got, want)
+            ctx_rows = Nc if backend == "triton_shared_context" else B * Nc
+            assert p.last_h2d_bytes == 4 * (ctx_rows * F + ctx_rows + B * Nt * F)
+            jd = p.evaluate_joint_density(h[0], h[1], h[2], h[3])
+            assert torch.equal(jd, p.evaluate_joint_density(xc.cuda(), yc.cuda(), xt.cuda(), yt.cuda()))
+
+
+def test_default_draws_follow_torchs_generator():
+    """Without ``variates`` the random numbers come from torch's CUDA generator in the reference's
+    order (per step Exp(1) [B,K], then N(0,1) [B]); they are drawn on a side stream beside the
+    prefill, which must not change them: re-seeding and replaying ``draw_variates`` gives the same
+    samples, and so does the reference's own consumption pattern written out by hand."""
+    from ar_tabpfn.model import ARTabPFNPredictor
+    fx = load_golden("config1.pt")
+    m, _ = build_model(fx)
+    p = ARTabPFNPredictor.from_trained_model(m, backend="triton_shared_context")
+    xc, yc, xt = fx["xc"].cuda(), fx["yc"].cuda(), fx["xt"].cuda()
+    B, Nt = xt.shape[:2]
+    K = m.head.num_components
+    for seed in (5, 6):
+        torch.manual_seed(seed)
+        a = p.sample_sequence(xc, yc, xt).clone()
+        torch.manual_seed(seed)
+        b = p.sample_sequence(xc, yc, xt, variates=p.draw_variates(Nt, B, xc.device))
+        assert torch.equal(a, b)
+        torch.manual_seed(seed)
+        ex, no = [], []
+        for _ in range(Nt):
+            ex.append(torch.empty(B, K, device="cuda").exponential_(1))
+            no.append(torch.randn(B, 1, 1, 1, device="cuda").view(B))
+        c = p.sample_sequence(xc, yc, xt, variates=(torch.stack(ex), torch.stack(no)))
+        assert torch.equal(a, c)
+    torch.manual_seed(5)
+    assert not torch.equal(a, p.sample_sequence(xc, yc, xt))
