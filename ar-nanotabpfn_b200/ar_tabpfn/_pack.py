@@ -63,7 +63,12 @@ def tile_weight(w: torch.Tensor, mode: str, force_lo: bool = False):
 
 
 class PackedModel:
+    """All packing arithmetic (transposes, the fold of the feature attention, hi / lo splits,
+    swizzled tiles) runs on the host in fp64, once per model version; the device sees two copies
+    (the fp32 buffer and the bf16 tile stream) and no packing kernels."""
+
     def __init__(self, embedder, backbone, head, ar_tokens, device: torch.device):
+        target, device = device, torch.device("cpu")
         layers = list(backbone.layers)
         attn0 = layers[0].attn_rows
         self.d_model = int(backbone.norm.weight.numel())
@@ -114,6 +119,7 @@ class PackedModel:
         flat = torch.zeros(total, dtype=torch.float32, device=device)
         for name, t in items:
             flat[offsets[name]:offsets[name] + t.numel()] = t.reshape(-1).to(torch.float32)
+        flat = flat.to(target)
         self.flat = flat
         base = flat.data_ptr()
 
@@ -133,12 +139,13 @@ class PackedModel:
             setattr(m, f, P(f))
         m.layers = C.cast(self._layers, C.POINTER(_lib.LayerWeights))
         self.struct = m
-        self._pack_tensor_core(embedder, backbone, head, device)
+        self._pack_tensor_core(embedder, backbone, head, target)
 
-    def _pack_tensor_core(self, embedder, backbone, head, device):
+    def _pack_tensor_core(self, embedder, backbone, head, target):
         """bf16 hi/lo tiles for the tcgen05 per-token chain (d_model in {64,128,192}, d_ff % 128 == 0,
         3K <= 16).  Other shapes keep the fp32 FMA chain (the tc_* pointers stay NULL)."""
         D, Dff = self.d_model, self.d_ff
+        device = torch.device("cpu")
         self.tc_flat = None
         if D not in (64, 128, 192) or Dff % 128 != 0 or Dff > 1024 or 3 * self.n_comp > 16:
             return
@@ -176,6 +183,7 @@ class PackedModel:
         flat = torch.zeros(tot, dtype=torch.bfloat16, device=device)
         for name, t in items:
             flat[offs[name]:offs[name] + t.numel()] = t
+        flat = flat.to(target)
         self.tc_flat = flat
         base = flat.data_ptr()
         for i in range(self.n_layers):

@@ -179,8 +179,11 @@ class MixtureGaussianHead(nn.Module):
         expo = torch.empty(B * T, self.num_components, device=z.device, dtype=z.dtype).exponential_(1)
         normal = torch.randn(B, T, 1, 1, device=z.device, dtype=z.dtype)
         y = torch.empty(B * T, device=z.device, dtype=torch.float32)
-        _lib.check(lib.artab_head_sample(C.byref(w.struct), _lib.ptr(zf), _lib.ptr(_f32(expo)),
-                                         _lib.ptr(_f32(normal).reshape(-1)), B * T, _lib.ptr(y), None, None,
+        # fp32 copies stay referenced until the launch is queued: a temporary released earlier could
+        # hand its memory to the next conversion before the kernel has read it
+        expo32, normal32 = _f32(expo), _f32(normal).reshape(-1)
+        _lib.check(lib.artab_head_sample(C.byref(w.struct), _lib.ptr(zf), _lib.ptr(expo32),
+                                         _lib.ptr(normal32), B * T, _lib.ptr(y), None, None,
                                          _lib.stream_ptr()))
         return y.view(B, T, 1, 1).to(z.dtype)
 

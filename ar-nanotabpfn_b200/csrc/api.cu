@@ -44,7 +44,12 @@ static int dependent_launch_default() {
   return !(e && e[0] == '0');
 }
 static std::atomic<int> g_dependent_launch{dependent_launch_default()};
-bool dependent_launch_enabled() { return g_dependent_launch.load(std::memory_order_relaxed) != 0; }
+static thread_local int g_plain_scope = 0;
+PlainLaunchScope::PlainLaunchScope() { ++g_plain_scope; }
+PlainLaunchScope::~PlainLaunchScope() { --g_plain_scope; }
+bool dependent_launch_enabled() {
+  return g_plain_scope == 0 && g_dependent_launch.load(std::memory_order_relaxed) != 0;
+}
 
 void prof_begin(int kind, cudaStream_t s) {
   if (!g_prof_on) return;
@@ -69,7 +74,7 @@ void prof_end(cudaStream_t s) {
 }
 
 int check_launch(const char* what) {
-  const cudaError_t e = cudaPeekAtLastError();
+  const cudaError_t e = cudaGetLastError();  // reads and clears: one failed launch does not poison later calls
   if (e != cudaSuccess) {
     set_error("%s: %s", what, cudaGetErrorString(e));
     return ARTAB_ELAUNCH;
@@ -659,6 +664,7 @@ int artab_forward_masked(const artab_model* m, artab_state* st, const float* xb,
 int artab_context_attention(int dtype, const void* q, const void* k_ctx, const void* v_ctx, int rows,
                             int rows_per_group, int n_groups, int n_heads, int head_dim, int n_ctx, int n_ctx_pad,
                             int n_splits, float* out, float* lse, int32_t* status, void* stream) {
+  PlainLaunchScope plain;  // the caller's earlier launches are unknown: see common.cuh
   ARTAB_REQUIRE(q && k_ctx && v_ctx && out && lse, ARTAB_EINVAL, "context_attention: null pointer");
   ARTAB_REQUIRE(rows >= 0 && n_groups >= 1 && n_heads >= 1 && n_ctx >= 1 && n_splits >= 1 && n_ctx_pad >= n_ctx,
                 ARTAB_EINVAL, "context_attention: bad sizes");
@@ -691,6 +697,7 @@ int artab_buffer_attention_merge(int dtype, const void* q, const void* kv_buf, i
                                  int head_dim, int max_buf, int mode_tf, int n_new_or_nt, int len0,
                                  const float* o_part, const float* lse_part, int n_splits, int rows, float* out,
                                  void* stream) {
+  PlainLaunchScope plain;  // the caller's earlier launches are unknown: see common.cuh
   ARTAB_REQUIRE(q && o_part && lse_part && out && n_splits >= 1, ARTAB_EINVAL, "buffer_attention_merge: null pointer");
   ARTAB_REQUIRE(kv_buf || (!mode_tf && len0 == 0), ARTAB_EINVAL, "buffer_attention_merge: kv_buf is null");
   ARTAB_REQUIRE(mode_tf ? (n_new_or_nt >= 1 && n_new_or_nt <= max_buf && rows == n_streams * 2 * n_new_or_nt)
@@ -723,6 +730,7 @@ int artab_buffer_attention_merge_ragged(int dtype, const void* q, const void* kv
                                         int head_dim, int max_buf, int n_new, const int32_t* lens, int len_max,
                                         const float* o_part, const float* lse_part, int n_splits, int rows,
                                         float* out, float* lse_out, void* stream) {
+  PlainLaunchScope plain;  // the caller's earlier launches are unknown: see common.cuh
   ARTAB_REQUIRE(q && o_part && lse_part && out && n_splits >= 1, ARTAB_EINVAL,
                 "buffer_attention_merge_ragged: null pointer");
   ARTAB_REQUIRE(kv_buf || len_max == 0, ARTAB_EINVAL, "buffer_attention_merge_ragged: kv_buf is null");
@@ -752,6 +760,7 @@ int artab_buffer_attention_merge_ragged(int dtype, const void* q, const void* kv
 
 int artab_kv_append(int dtype, void* kv_buf, const void* k_new, const void* v_new, int n_streams, int n_heads,
                     int head_dim, int max_buf, int pos, void* stream) {
+  PlainLaunchScope plain;  // the caller's earlier launches are unknown: see common.cuh
   ARTAB_REQUIRE(kv_buf && k_new && v_new, ARTAB_EINVAL, "kv_append: null pointer");
   ARTAB_REQUIRE(pos >= 0 && pos < max_buf, ARTAB_ECAPACITY,
                 "Shared-context buffer cache exceeded; increase max buffer length.");
@@ -761,6 +770,7 @@ int artab_kv_append(int dtype, void* kv_buf, const void* k_new, const void* v_ne
 
 int artab_embed(const artab_model* m, const float* x, const float* y, const int32_t* ar_idx, int rows, int n_feat,
                 int kind, float* out, void* stream) {
+  PlainLaunchScope plain;  // the caller's earlier launches are unknown: see common.cuh
   ARTAB_REQUIRE(m && x && out && n_feat > 0 && kind >= 0 && kind <= 2, ARTAB_EINVAL, "embed: bad argument");
   EmbedArgs e = embed_base(m);
   e.mode = EMB_ROWS;
@@ -791,6 +801,7 @@ static int head_common(const artab_model* m, const float* z, int rows, DenseArgs
 }
 
 int artab_head_logpdf(const artab_model* m, const float* z, const float* y, int rows, float* logdens, void* stream) {
+  PlainLaunchScope plain;  // the caller's earlier launches are unknown: see common.cuh
   ARTAB_REQUIRE(m && z && y && logdens, ARTAB_EINVAL, "head_logpdf: null pointer");
   DenseArgs d;
   head_common(m, z, rows, d);
@@ -802,6 +813,7 @@ int artab_head_logpdf(const artab_model* m, const float* z, const float* y, int 
 
 int artab_head_sample(const artab_model* m, const float* z, const float* expo, const float* normal, int rows,
                       float* y, float* logdens, int32_t* comp, void* stream) {
+  PlainLaunchScope plain;  // the caller's earlier launches are unknown: see common.cuh
   ARTAB_REQUIRE(m && z && expo && normal && y, ARTAB_EINVAL, "head_sample: null pointer");
   DenseArgs d;
   head_common(m, z, rows, d);

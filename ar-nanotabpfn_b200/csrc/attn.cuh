@@ -36,6 +36,10 @@ struct BufMergeArgs {
   float scale;
   float* out;  // [rows][H][Dh]
   int out_lane_major;  // write out in the lane-major layout instead
+  // Optional device word: when it is non-zero after the preceding kernel (a bounded wait of the
+  // context contraction gave up, so some partials were never written) the merged output is NaN
+  // instead of a plausible-looking mix of stale partials.
+  const int32_t* poison_if;
 };
 
 int launch_ctx_attn_simt(const CtxAttnArgs& a, cudaStream_t s);

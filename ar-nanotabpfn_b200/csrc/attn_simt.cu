@@ -359,7 +359,8 @@ __global__ void __launch_bounds__(128, 6) buf_merge_kernel(const BufMergeArgs a)
     }
     if (a.lse_out && lane == 0) a.lse_out[(size_t)r * a.n_heads + h] = wsum > 0.f ? top + logf(wsum) : -INFINITY;
     if (grp == 0) {
-      const float inv = wsum > 0.f ? 1.0f / wsum : 0.f;
+      float inv = wsum > 0.f ? 1.0f / wsum : 0.f;
+      if (a.poison_if && __ldcg(a.poison_if) != 0) inv = __int_as_float(0x7fc00000);
 #pragma unroll
       for (int e = 0; e < VEC; e += 4) {
         float* dst = a.out + (a.out_lane_major ? lane_major_index(r, h * DH + sub * VEC + e, a.n_heads * DH)
@@ -385,14 +386,13 @@ template <typename T>
 int launch_ctx_t(const CtxAttnArgs& a, cudaStream_t s) {
   const int rows_in_group = a.n_groups == 1 ? a.rows : a.rows_per_group;
   dim3 grid((rows_in_group + kQB - 1) / kQB, a.n_heads, a.n_groups * a.n_splits);
+  ARTAB_REQUIRE(a.head_dim == 16 || a.head_dim == 32 || a.head_dim == 64, ARTAB_EINVAL,
+                "context attention: head_dim %d not supported (16, 32, 64)", a.head_dim);
   prof_begin(PROF_CTX, s);
   switch (a.head_dim) {
     case 16: ctx_attn_simt_kernel<T, 16><<<grid, kWarps * 32, 0, s>>>(a); break;
     case 32: ctx_attn_simt_kernel<T, 32><<<grid, kWarps * 32, 0, s>>>(a); break;
-    case 64: ctx_attn_simt_kernel<T, 64><<<grid, kWarps * 32, 0, s>>>(a); break;
-    default:
-      set_error("context attention: head_dim %d not supported (16, 32, 64)", a.head_dim);
-      return ARTAB_EINVAL;
+    default: ctx_attn_simt_kernel<T, 64><<<grid, kWarps * 32, 0, s>>>(a); break;
   }
   prof_end(s);
   count_launch();
@@ -404,14 +404,13 @@ int launch_buf_t(const BufMergeArgs& a, cudaStream_t s) {
   const int wpb = 4;
   const unsigned grid = (unsigned)((a.n_items + wpb - 1) / wpb);
   cudaError_t le = cudaSuccess;
+  ARTAB_REQUIRE(a.head_dim == 16 || a.head_dim == 32 || a.head_dim == 64, ARTAB_EINVAL,
+                "buffer attention: head_dim %d not supported (16, 32, 64)", a.head_dim);
   prof_begin(PROF_BUF, s);
   switch (a.head_dim) {
     case 16: le = launch_dependent(buf_merge_kernel<T, 16>, dim3(grid), dim3(wpb * 32), 0, s, a); break;
     case 32: le = launch_dependent(buf_merge_kernel<T, 32>, dim3(grid), dim3(wpb * 32), 0, s, a); break;
-    case 64: le = launch_dependent(buf_merge_kernel<T, 64>, dim3(grid), dim3(wpb * 32), 0, s, a); break;
-    default:
-      set_error("buffer attention: head_dim %d not supported (16, 32, 64)", a.head_dim);
-      return ARTAB_EINVAL;
+    default: le = launch_dependent(buf_merge_kernel<T, 64>, dim3(grid), dim3(wpb * 32), 0, s, a); break;
   }
   prof_end(s);
   ARTAB_REQUIRE(le == cudaSuccess, ARTAB_ELAUNCH, "buf_merge_kernel: %s", cudaGetErrorString(le));

@@ -482,8 +482,35 @@ EncodeTiledFn encode_fn() {
   return fn;
 }
 
+// A tensor map depends only on (base, extents, pitch, box, swizzle): the decode loop asks for the same
+// few maps hundreds of times per call (q once per row count, K and V once per layer), so the encoded
+// descriptors are kept in a small per-thread table, replaced round-robin.
+struct MapKey {
+  const void* base;
+  uint64_t inner, outer, row_bytes;
+  uint32_t box_inner, box_outer;
+  int swz;
+  bool operator==(const MapKey& o) const {
+    return base == o.base && inner == o.inner && outer == o.outer && row_bytes == o.row_bytes &&
+           box_inner == o.box_inner && box_outer == o.box_outer && swz == o.swz;
+  }
+};
+constexpr int kMapCache = 64;
+struct MapCache {
+  MapKey key[kMapCache];
+  CUtensorMap map[kMapCache];
+  int used = 0, next = 0;
+};
+
 int make_map_2d(CUtensorMap* tm, const void* base, uint64_t inner, uint64_t outer, uint64_t row_bytes, uint32_t box_inner,
                 uint32_t box_outer, CUtensorMapSwizzle swz, const char* what) {
+  static thread_local MapCache cache;
+  const MapKey k{base, inner, outer, row_bytes, box_inner, box_outer, (int)swz};
+  for (int i = 0; i < cache.used; ++i)
+    if (cache.key[i] == k) {
+      *tm = cache.map[i];
+      return ARTAB_OK;
+    }
   EncodeTiledFn fn = encode_fn();
   ARTAB_REQUIRE(fn, ARTAB_EDRIVER, "cuTensorMapEncodeTiled is not available from the driver");
   const cuuint64_t dims[2] = {inner, outer};
@@ -495,6 +522,9 @@ int make_map_2d(CUtensorMap* tm, const void* base, uint64_t inner, uint64_t oute
                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   ARTAB_REQUIRE(r == CUDA_SUCCESS, ARTAB_EINVAL, "tensor map for %s refused (CUresult %d): base %p, dims %llu x %llu",
                 what, (int)r, base, (unsigned long long)inner, (unsigned long long)outer);
+  const int slot = cache.used < kMapCache ? cache.used++ : (cache.next = (cache.next + 1) % kMapCache);
+  cache.key[slot] = k;
+  cache.map[slot] = *tm;
   return ARTAB_OK;
 }
 
@@ -524,12 +554,11 @@ int launch_ctx_attn_tc(const CtxAttnArgs& a, cudaStream_t s) {
   // two CTAs per SM at most: each holds 256 of the SM's 512 TMEM columns
   const size_t smem = 100 * 1024;
   static_assert(sizeof(Smem) + 1024 <= 100 * 1024, "shared-memory plan exceeds the request");
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(ctx_attn_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  static SmemConfig configured;
+  {
+    const cudaError_t e = configured.ensure(ctx_attn_tc_kernel, smem);
     ARTAB_REQUIRE(e == cudaSuccess, ARTAB_ELAUNCH, "ctx_attn_tc_kernel: shared memory refused: %s",
                   cudaGetErrorString(e));
-    configured = true;
   }
   TcParams p;
   p.rows = a.rows;

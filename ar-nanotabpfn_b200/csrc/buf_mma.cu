@@ -232,7 +232,8 @@ __global__ void __launch_bounds__(WPB * 32, 6) buf_mma_kernel(const BufMergeArgs
     }
   }
   if (a.lse_out && t4 == 0) a.lse_out[(size_t)r * a.n_heads + h] = wsum > 0.f ? top + logf(wsum) : -INFINITY;
-  const float inv = wsum > 0.f ? 1.0f / wsum : 0.f;
+  float inv = wsum > 0.f ? 1.0f / wsum : 0.f;
+  if (a.poison_if && __ldcg(a.poison_if) != 0) inv = __int_as_float(0x7fc00000);
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
     const int col = h * DH + 8 * j + t4 * 2;

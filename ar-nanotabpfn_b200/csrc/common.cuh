@@ -27,10 +27,49 @@ void prof_end(cudaStream_t s);
 // kernel wrote and before it writes global memory; (2) it calls dep_trigger() only after its own
 // dep_wait(), so a dependent that starts early knows that everything older than its predecessor
 // has completed.  Without the launch attribute both calls are no-ops.
+//
+// What each kernel reads BEFORE its dep_wait() (the work it overlaps with its predecessor):
+//   embed_kernel            nothing
+//   dense_tc_kernel         weight tiles, LayerNorm vectors and biases (model constants)
+//   ctx_attn_tc_kernel      context K / V tiles, only when the caller says they are stable (kv_stable)
+//   buf_mma_kernel /
+//   buf_merge_kernel        q, the private K / V rows and the per-stream lengths
+// The last line is safe only where the launch BEFORE the predecessor produced q and the K / V rows,
+// which holds inside artab_prefill / artab_decode_step / artab_teacher_forcing / artab_forward_masked
+// (embed, dense chain, context contraction, buffer pass: the buffer pass's predecessor is the context
+// contraction, which waits before it triggers).  The single-operator entry points cannot know what
+// the caller launched before them, so they launch every kernel plainly (PlainLaunchScope): the
+// kernel then starts after everything earlier in the stream has completed and the rule is moot.
 __device__ __forceinline__ void dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void dep_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 bool dependent_launch_enabled();
+
+// While one of these lives on the calling thread, launch_dependent* issue plain launches.
+struct PlainLaunchScope {
+  PlainLaunchScope();
+  ~PlainLaunchScope();
+  PlainLaunchScope(const PlainLaunchScope&) = delete;
+  PlainLaunchScope& operator=(const PlainLaunchScope&) = delete;
+};
+
+// Largest dynamic shared-memory size a kernel has been configured for, per device: the opt-in is a
+// per-device attribute, so a process that uses several GPUs repeats it on each.
+constexpr int kMaxDevices = 64;
+struct SmemConfig {
+  size_t bytes[kMaxDevices] = {};
+  template <typename K>
+  cudaError_t ensure(K kernel, size_t smem) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev < 0 || dev >= kMaxDevices) return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (smem <= bytes[dev]) return cudaSuccess;
+    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e == cudaSuccess) bytes[dev] = smem;
+    return e;
+  }
+};
 
 // cluster_x > 1 launches thread-block clusters of that many CTAs along x (grid.x a multiple of it).
 template <typename... P, typename... A>

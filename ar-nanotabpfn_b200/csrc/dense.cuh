@@ -53,6 +53,9 @@ struct DenseArgs {
   int pair_slots;      // slots in pair_scratch; a pair uses 6: MLP exchange (0, 1), head exchange (2, 3), parking (4, 5)
   const void *tc_wa, *tc_wb;  // tensor-core tiles of the head matrices (null: fp32 chain)
   int tc_head_lo;
+#ifdef ARTAB_TIMELINE
+  int tl_slot;         // diagnostic builds: which timeline slot this launch stamps
+#endif
 };
 
 int launch_embed(const EmbedArgs& a, cudaStream_t s);

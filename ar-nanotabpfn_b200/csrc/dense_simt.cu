@@ -548,13 +548,11 @@ int launch_dense(const DenseArgs& a, cudaStream_t s) {
   const int wide = 3 * a.D > a.Dff ? 3 * a.D : a.Dff;
   const size_t smem = (size_t)kNBuf * kBufBytes + (size_t)kRows * (2 * a.D + wide + 3 * a.D) * sizeof(float) +
                       sizeof(Stream) + 128;
-  static size_t configured = 0;
-  if (smem > configured) {
-    cudaError_t e = cudaFuncSetAttribute(dense_chain_kernel<kRows>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         (int)smem);
+  static SmemConfig configured;
+  {
+    const cudaError_t e = configured.ensure(dense_chain_kernel<kRows>, smem);
     ARTAB_REQUIRE(e == cudaSuccess, ARTAB_ELAUNCH, "dense chain: %zu bytes of shared memory refused: %s", smem,
                   cudaGetErrorString(e));
-    configured = smem;
   }
   const int threads = T + 32;  // compute threads + the weight-streaming warp
   const int grid = (a.rows + kRows - 1) / kRows;

@@ -203,6 +203,15 @@ __device__ __forceinline__ float gelu_fast(float x) {
 }
 
 
+// Optional in-kernel timeline (diagnostic builds only, -DARTAB_TIMELINE): the first epilogue thread of
+// every CTA stamps clock64() at the phase boundaries of the launch; slot = launch counter mod 32.
+#ifdef ARTAB_TIMELINE
+__device__ long long g_tl[32][32][32];   // [launch slot][cta][mark]
+#define TL(id) do { if (tl_on) g_tl[a.tl_slot & 31][blockIdx.x & 31][id] = clock64(); } while (0)
+#else
+#define TL(id) do { } while (0)
+#endif
+
 struct __align__(1024) Smem {
   uint8_t ring[2][NSLOT][192 * 128];  // two weight rings (first / second MLP GEMM), slabs <= d_model * 128 bytes
   uint8_t ah[2][2][BM * 128];         // hidden tile operand [hi, lo][k-chunk][128 rows x 64 bf16], swizzled
@@ -716,6 +725,10 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const DenseArgs a
     // ---------------------------------- epilogue ----------------------------------
     Epilogue<D> e;
     constexpr int PART = Epilogue<D>::PART;
+#ifdef ARTAB_TIMELINE
+    const bool tl_on = threadIdx.x == 64;
+#endif
+    TL(0);
     e.sm = sm;
     e.row = 32 * (warp & 3) + lane;
     e.wg = (warp - 2) >> 2;
@@ -781,30 +794,40 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const DenseArgs a
       for (int i = threadIdx.x - 64; i < a.Dff; i += kEpi) sm->bias_h[i] = a.post_w.b1[i];
     // Everything above (and the weight producers' first tiles) needed nothing from the preceding
     // kernel; the activations do.
+    TL(1);
     dep_wait();
     dep_trigger();
+    TL(2);
     if (a.do_post) {
       load_lm(a.attn);
       e.publish_ax(v);
+      TL(3);
       load_lm(a.x1_in);                          // residual
       e.wait_acc();
+      TL(4);
       e.sync_groups();                           // the staged vectors are complete
       e.add_acc(v);
       e.layer_norm(v, sm->vec[0], sm->vec[1]);   // v = x2
       e.publish_ax(v);
+      TL(5);
       // x2 is the residual of the last LayerNorm; it waits in this thread's own slice of a workspace
       // so that the MLP epilogue has the registers: the x1 workspace (free until the next layer
       // writes it), or, in a CTA pair, this CTA's own slot of the pair scratch — the peer reads its
       // residual input from the x1 workspace at its own pace.
       float* park = csize > 1 ? a.pair_scratch + (size_t)(4 + crank) * a.pair_slot_stride : a.x1_out;
       store_lm(park);
+      TL(6);
       {
         int jl = 0;
-        for (int j = crank; j < nt; j += csize, ++jl) e.hidden_tile(jl, j, sm->bias_h);
+        for (int j = crank; j < nt; j += csize, ++jl) {
+          e.hidden_tile(jl, j, sm->bias_h);
+          TL(7 + (jl < 5 ? jl : 5));
+        }
       }
       load_lm(park);
       e.wait_acc();
       e.drain_free();
+      TL(13);
 #pragma unroll
       for (int i = 0; i < PART; ++i) v[i] += sm->vec[2][e.col0 + i];
       if (csize > 1)
@@ -812,8 +835,10 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const DenseArgs a
                        a.pair_scratch + (size_t)(crank ^ 1u) * a.pair_slot_stride, lm0);
       else
         e.add_acc(v);
+      TL(14);
       e.layer_norm(v, sm->vec[3], sm->vec[4]);   // v = x3
       if (a.x_out && crank == 0) store_row(a.x_out);
+      TL(15);
     } else {
       load_row(a.x_in);
       e.sync_groups();                           // the staged vectors are complete
@@ -834,6 +859,7 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const DenseArgs a
       }
       e.wait_acc();
       e.drain_free();
+      TL(24);
       // 16 raw head outputs per row, held by the first column group; a pair adds its two partials
       // (second exchange of the launch: slots 2 and 3 of the scratch, barrier phase 1)
       uint32_t r[16];
@@ -871,11 +897,15 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const DenseArgs a
       }
     } else if (a.do_pre) {
       e.publish_ax(v);
+      TL(16);
       e.wait_acc();
+      TL(17);
       e.add_acc(v);
       e.layer_norm(v, sm->vec[5], sm->vec[6]);     // v = x1
       e.publish_ax(v);       // the Q projection's MMAs start on this ...
+      TL(18);
       store_lm(a.x1_out);    // ... while the residual for the next launch drains to memory
+      TL(19);
       // q, k, v projections, one accumulator round each.  Destinations of this row's K / V are
       // resolved once (no per-element division): context cache rows during prefill, the private
       // buffer slot (in-place append) otherwise.
@@ -909,6 +939,7 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const DenseArgs a
       const int tid_e = threadIdx.x - 64;
       for (int t = t_begin; t < t_end; ++t) {
         e.wait_acc();
+        TL(20 + 2 * (t - t_begin));
         uint32_t r[Epilogue<D>::NCH][16];
 #pragma unroll
         for (int c = 0; c < Epilogue<D>::NCH; ++c) tmem_ld16(e.t_row + kAccA + e.col0 + 16 * c, r[c]);
@@ -954,6 +985,7 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const DenseArgs a
             }
           }
           e.sync_groups();  // the staging tile is reused by the next projection
+          TL(21 + 2 * (t - t_begin));
         } else {
           // prefill: context K rows and the transposed hi|lo context V, written straight from registers
 #pragma unroll
@@ -987,6 +1019,7 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const DenseArgs a
       }
     }
     if (!e.ok && threadIdx.x == 64 && a.status) atomicExch(a.status, 3);
+    TL(26);
   }
 
   tc_fence_before();
@@ -1023,28 +1056,23 @@ int launch_dense_tc(const DenseArgs& a, cudaStream_t s) {
       (allow_pair && a.pair_scratch && a.pair_slots >= 6 && 2 * tiles <= kPairMaxCtas && a.Dff / HT >= 2) ? 2u : 1u;
   const int grid = tiles * (int)csize;
   cudaError_t e = cudaSuccess;
-  static bool configured[3] = {false, false, false};
+  static SmemConfig configured[3];
+#ifdef ARTAB_TIMELINE
+  static int tl_next = 0;
+  const_cast<DenseArgs&>(a).tl_slot = tl_next++ & 31;
+#endif
   prof_begin(PROF_DENSE, s);
   switch (a.D) {
     case 64:
-      if (!configured[0]) {
-        e = cudaFuncSetAttribute(dense_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        configured[0] = e == cudaSuccess;
-      }
+      e = configured[0].ensure(dense_tc_kernel<64>, smem);
       if (e == cudaSuccess) e = launch_dependent_cluster(dense_tc_kernel<64>, dim3(grid), dim3(kThreads), smem, s, csize, a);
       break;
     case 128:
-      if (!configured[1]) {
-        e = cudaFuncSetAttribute(dense_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        configured[1] = e == cudaSuccess;
-      }
+      e = configured[1].ensure(dense_tc_kernel<128>, smem);
       if (e == cudaSuccess) e = launch_dependent_cluster(dense_tc_kernel<128>, dim3(grid), dim3(kThreads), smem, s, csize, a);
       break;
     default:
-      if (!configured[2]) {
-        e = cudaFuncSetAttribute(dense_tc_kernel<192>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        configured[2] = e == cudaSuccess;
-      }
+      e = configured[2].ensure(dense_tc_kernel<192>, smem);
       if (e == cudaSuccess) e = launch_dependent_cluster(dense_tc_kernel<192>, dim3(grid), dim3(kThreads), smem, s, csize, a);
       break;
   }
@@ -1055,3 +1083,10 @@ int launch_dense_tc(const DenseArgs& a, cudaStream_t s) {
 }
 
 }  // namespace artab
+
+#ifdef ARTAB_TIMELINE
+// diagnostic builds: copy the timeline stamps [32 launch slots][32 CTAs][32 marks] to host memory
+extern "C" __attribute__((visibility("default"))) int artab_debug_timeline(long long* host_dst) {
+  return (int)cudaMemcpyFromSymbol(host_dst, artab::g_tl, sizeof(long long) * 32 * 32 * 32);
+}
+#endif

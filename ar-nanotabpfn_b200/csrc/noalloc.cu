@@ -19,7 +19,6 @@ namespace {
 constexpr size_t kScratchFloats = 2u << 20;
 static __device__ __align__(256) float g_noalloc_scratch[kScratchFloats + 64];  // + status word
 
-constexpr int kMaxDevices = 64;
 float* g_scratch_ptr[kMaxDevices] = {nullptr};
 
 // The array's name is only a host-side handle; kernels need its device address.
@@ -48,6 +47,7 @@ extern "C" ARTAB_API int artab_context_attention_noalloc(int dtype, const void* 
                                                          const void* v_ctx, int rows, int rows_per_group,
                                                          int n_groups, int n_heads, int head_dim, int n_ctx,
                                                          int n_ctx_pad, int n_splits, float* out, void* stream) {
+  PlainLaunchScope plain;  // the caller's earlier launches are unknown: see common.cuh
   ARTAB_REQUIRE(q && k_ctx && v_ctx && out, ARTAB_EINVAL, "context_attention_noalloc: null pointer");
   ARTAB_REQUIRE(rows >= 1 && n_groups >= 1 && n_heads >= 1 && n_ctx >= 1 && n_splits >= 1 && n_ctx_pad >= n_ctx,
                 ARTAB_EINVAL, "context_attention_noalloc: bad sizes");
@@ -110,5 +110,6 @@ extern "C" ARTAB_API int artab_context_attention_noalloc(int dtype, const void* 
   b.rows = rows;
   b.scale = c.scale;
   b.out = out;
+  b.poison_if = status;  // a wait that gave up in the contraction turns the whole output into NaN
   return launch_buf_merge(b, s);
 }

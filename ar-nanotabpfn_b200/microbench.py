@@ -259,36 +259,6 @@ def bench_chain(a):
     print(json.dumps(out), flush=True)
 
 
-def _model(num_features, seed, dev):
-    import ar_tabpfn
-    torch.manual_seed(seed)
-    m = ar_tabpfn.ARTabPFN(d_model=192, n_heads=6, n_layers=6, d_ff=768, num_features=num_features, buffer_size=8,
-                           num_components=5).eval()
-    with torch.no_grad():
-        for mod in m.modules():
-            if isinstance(mod, torch.nn.Linear):
-                torch.nn.init.xavier_uniform_(mod.weight)
-        for p in m.parameters():
-            p.copy_(p.to(torch.bfloat16).float())
-    return m.to(dev)
-
-
-def _dataset(g, n_rows, n_feat, hidden, noise, product_frac=0.0):
-    """x ~ N(0,1) (optionally a fraction of columns replaced by products of two others),
-    standardised; y = tanh-MLP(F -> hidden -> hidden -> 1) + N(0, noise^2)."""
-    x = torch.randn(n_rows, n_feat, generator=g)
-    n_prod = int(product_frac * n_feat)
-    for j in range(n_prod):
-        a, b = torch.randint(n_prod, n_feat, (2,), generator=g).tolist()
-        x[:, j] = x[:, a] * x[:, b]
-    x = (x - x.mean(0)) / x.std(0)
-    w1 = torch.randn(n_feat, hidden, generator=g) / n_feat ** 0.5
-    w2 = torch.randn(hidden, hidden, generator=g) / hidden ** 0.5
-    w3 = torch.randn(hidden, 1, generator=g) / hidden ** 0.5
-    y = (torch.tanh(torch.tanh(x @ w1) @ w2) @ w3)[:, 0] + noise * torch.randn(n_rows, generator=g)
-    return x, y
-
-
 def _event_time(fn, iters, warmup):
     for _ in range(warmup):
         fn()
@@ -305,13 +275,11 @@ def _event_time(fn, iters, warmup):
 def bench_config4(a):
     import ar_tabpfn
     dev = torch.device("cuda")
-    model = _model(20, 3, dev)
+    import synthetic as syn
+    model = syn.config4_model().to(dev)
     pred = ar_tabpfn.ARTabPFNPredictor.from_trained_model(model, backend="flex_attention", precision=a.dtype)
-    g = torch.Generator().manual_seed(3)
     B, Nc, Nt = a.datasets, a.ctx, a.targets
-    xs, ys = zip(*[_dataset(g, Nc + Nt, 20, 32, 0.1) for _ in range(B)])
-    x, y = torch.stack(xs).to(dev), torch.stack(ys).to(dev)
-    xc, yc, xt, yt = x[:, :Nc].contiguous(), y[:, :Nc].contiguous(), x[:, Nc:].contiguous(), y[:, Nc:].contiguous()
+    xc, yc, xt, yt = (t.to(dev) for t in syn.config4_workload(B, Nc, Nt))
     out = {}
 
     def fn():
@@ -334,14 +302,13 @@ def bench_config5(a):
     dev = torch.device("cuda", local)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
-    model = _model(100, 4, dev)
+    import synthetic as syn
+    model = syn.config5_model().to(dev)
     pred = ar_tabpfn.ARTabPFNPredictor.from_trained_model(model, backend="triton_shared_context", precision=a.dtype)
-    g = torch.Generator().manual_seed(4)
     B, Nc, Nt = a.streams // world, a.ctx, a.targets
-    x, y = _dataset(g, Nc + Nt, 100, 64, 0.05, product_frac=0.2)
-    x, y = x.to(dev), y.to(dev)
-    xc, yc = x[:Nc].expand(B, -1, -1), y[:Nc].expand(B, -1)   # shared context: only stream 0's copy is read
-    xt = x[Nc:].expand(B, -1, -1).contiguous()
+    xcr, ycr, xtr, _ = syn.config5_rows(Nc, Nt)
+    xc, yc = xcr.to(dev).expand(B, -1, -1), ycr.to(dev).expand(B, -1)   # shared context: only stream 0's copy is read
+    xt = xtr.to(dev).expand(B, -1, -1).contiguous()
     gd = torch.Generator(device=dev).manual_seed(4)
     expo = torch.empty(Nt, a.streams, 5, device=dev).exponential_(1.0, generator=gd)
     normal = torch.randn(Nt, a.streams, device=dev, generator=gd)

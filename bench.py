@@ -1,16 +1,18 @@
 """Benchmark of the AR sampling hot path (one JSON line on stdout).
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--precision bf16|fp32]
+                    [--no-cpu-baseline] [--no-scaleout]
 
 Workload ("config3"): the 6-layer d_model 192 / 6 heads / MLP 768 model, random
 init with Xavier-uniform Linear weights rounded to bf16-representable values, one
 synthetic dataset of 1024 context rows x 20 features (tanh-MLP generator), 128
 target rows decoded autoregressively by 512 sample streams that share one context
-KV cache.  One "step" is one complete ``sample_sequence`` call (prefill + 128
-decode steps + samples and log densities).  With N GPUs every rank runs its own
-512 streams (weak scaling: streams are independent, the context KV is prefilled
-locally on every rank) and the results are all-gathered with NCCL at the end of
-each step.
+KV cache (synthetic.py builds the model and the rows; the parity tests use the same).
+One "step" is one complete ``sample_sequence`` call (prefill + 128 decode steps +
+samples and log densities).  With N GPUs every rank runs its own 512 streams (weak
+scaling: streams are independent, the context KV is prefilled locally on every rank)
+and the results are gathered with NCCL at the end of each step
+(``ar_tabpfn.sharding.sharded_call``).
 
 Metric: AR targets decoded per second, whole job.
   value : inputs and pre-drawn variates already resident in HBM;
@@ -18,10 +20,14 @@ Metric: AR targets decoded per second, whole job.
           what the path reads inside the timed region: the shared context once, every
           stream's targets), random numbers drawn inside the call, samples and log
           densities read back to the host (D2H inside the timed region).
+  scaleout : the scale-out configuration ("config5": 16384 context rows x 100 features,
+          256 targets, 4096 sample streams in total) split evenly over the N ranks
+          (strong scaling), a few steps after the headline measurement.
 
-``--impl reference`` times the CPU restatement of the reference algorithm (the
-oracle; the reference project is Python and cannot travel to the GPU box) on the
-host cores, on a bounded sample of the same workload.
+``--impl reference`` times the reference's own CPU path on the host cores, on a bounded
+sample of the same workload: the unmodified reference package when it is installed under
+``baseline/_ref`` (imported under an alias, CUDA hidden from that process so that it takes
+the CPU route), otherwise the CPU restatement of its algorithm (the oracle).
 """
 from __future__ import annotations
 
@@ -37,51 +43,28 @@ sys.path.insert(0, os.path.join(ROOT, "ar-nanotabpfn_b200"))
 
 import torch  # noqa: E402
 
-CFG = dict(d_model=192, n_heads=6, n_layers=6, d_ff=768, num_features=20, buffer_size=8, num_components=5)
-NC, NT, STREAMS, SEED = 1024, 128, 512, 2
-# DRAM bytes (read + write) of one decode-step launch of the tensor-core dense chain at this
-# workload, from the ncu capture of that kernel summarised under profiles/
-DENSE_TC_DRAM_BYTES_PER_LAUNCH = 3.657e6   # 1024-row decode launch (8 row tiles, 16 CTAs); weight tiles dominate
+import synthetic as syn  # noqa: E402
+
+CFG = dict(syn.MODEL_6L, num_features=syn.CONFIG3["num_features"])
+NC, NT, STREAMS, SEED = syn.CONFIG3["n_ctx"], syn.CONFIG3["n_targets"], syn.CONFIG3["streams"], syn.CONFIG3["seed"]
+# DRAM bytes (read + write) of one 1024-row decode-step launch of the tensor-core dense chain: a constant
+# taken from one ncu capture of that kernel (dram__bytes_read.sum + dram__bytes_write.sum), not measured
+# in this run; the weight tiles dominate it
+DENSE_TC_DRAM_BYTES_PER_LAUNCH = 3.657e6
 CPU_SAMPLE = dict(streams=128, targets=16)  # bounded CPU sample of the same workload
 WORKLOAD_CONFIG = {"workload": "config3: 6L d192 h6 ff768, ctx 1024x20, 128 targets, 512 streams/GPU, "
                                "shared context KV, prefill included in every step",
                    "streams_per_gpu": STREAMS, "targets": NT, "context_rows": NC,
                    "l2": "256 MB buffer written between timed iterations; KV working set 288 MiB > L2"}
-
-
-def make_dataset(seed, n_rows, n_feat, hidden=32, noise=0.1):
-    """x ~ N(0,1) standardised per column, y = tanh-MLP(F->32->32->1) + N(0, noise^2)."""
-    g = torch.Generator().manual_seed(seed)
-    x = torch.randn(n_rows, n_feat, generator=g)
-    x = (x - x.mean(0)) / x.std(0)
-    w1 = torch.randn(n_feat, hidden, generator=g) / n_feat ** 0.5
-    w2 = torch.randn(hidden, hidden, generator=g) / hidden ** 0.5
-    w3 = torch.randn(hidden, 1, generator=g) / hidden ** 0.5
-    y = (torch.tanh(torch.tanh(x @ w1) @ w2) @ w3)[:, 0] + noise * torch.randn(n_rows, generator=g)
-    return x, y
+SCALEOUT = dict(streams=syn.CONFIG5["streams"], targets=syn.CONFIG5["n_targets"], ctx=syn.CONFIG5["n_ctx"])
 
 
 def build_model():
-    import ar_tabpfn
-    torch.manual_seed(SEED)
-    m = ar_tabpfn.ARTabPFN(**CFG).eval()
-    with torch.no_grad():
-        for mod in m.modules():
-            if isinstance(mod, torch.nn.Linear):
-                torch.nn.init.xavier_uniform_(mod.weight)
-        for p in m.parameters():
-            p.copy_(p.to(torch.bfloat16).float())  # bf16-representable weights (bf16-mode protocol)
-            p.requires_grad_(False)
-    return m
+    return syn.config3_model()
 
 
-def workload(streams):
-    x, y = make_dataset(SEED, NC + NT, CFG["num_features"])
-    x, y = x.to(torch.bfloat16).float(), y.to(torch.bfloat16).float()
-    xc = x[:NC].expand(streams, -1, -1).contiguous()
-    yc = y[:NC].expand(streams, -1).contiguous()
-    xt = x[NC:].expand(streams, -1, -1).contiguous()
-    return xc, yc, xt
+def workload(streams, n_targets=None):
+    return syn.config3_workload(streams, n_targets)
 
 
 class ClockSampler:
@@ -132,46 +115,181 @@ class ClockSampler:
                            "samples": len(sm)}
 
 
-def cpu_reference_rate(steps, warmup):
-    """targets/s of the CPU restatement of the reference on a bounded sample, all host threads."""
+def _cpu_sample_inputs():
+    B, Nt = CPU_SAMPLE["streams"], CPU_SAMPLE["targets"]
+    xc, yc, xt = workload(B, Nt)
+    return B, Nt, xc, yc, xt
+
+
+def _time_calls(fn, steps, warmup):
+    times = []
+    for i in range(warmup + steps):
+        t0 = time.perf_counter()
+        fn()
+        if i >= warmup:
+            times.append(time.perf_counter() - t0)
+    return sum(times) / len(times)
+
+
+def cpu_port_rate(steps, warmup):
+    """targets/s of the CPU restatement of the reference (the oracle) on the bounded sample."""
     sys.path.insert(0, os.path.join(ROOT, "oracle"))
     import artab_oracle as orc
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
     m = build_model()
     sd = {k: v.detach().clone() for k, v in m.state_dict().items()}
-    B, Nt = CPU_SAMPLE["streams"], CPU_SAMPLE["targets"]
-    xc, yc, xt = workload(B)
-    xt = xt[:, :Nt].contiguous()
+    B, Nt, xc, yc, xt = _cpu_sample_inputs()
     expo, normal = orc.draw_variates(SEED, Nt, B, CFG["num_components"])
     pred = orc.OraclePredictor(sd, CFG["n_heads"])
-    times = []
     with torch.no_grad():
-        for i in range(warmup + steps):
-            t0 = time.perf_counter()
-            pred.sample_sequence(xc, yc, xt, expo, normal, shared=True)
-            if i >= warmup:
-                times.append(time.perf_counter() - t0)
-    per = sum(times) / len(times)
-    sample = (f"{B} streams x {Nt} targets of config3 (context {NC} rows, same model), "
-              f"full prefill + decode, torch CPU fp32, {cores} threads")
-    return B * Nt / per, per, cores, sample
+        per = _time_calls(lambda: pred.sample_sequence(xc, yc, xt, expo, normal, shared=True), steps, warmup)
+    sample = (f"{B} streams x {Nt} targets of config3 (context {NC} rows, same model), full prefill + decode, "
+              f"CPU restatement of the reference (oracle), torch CPU fp32, {cores} threads, "
+              f"{steps} timed calls after {warmup} warm-up")
+    return {"value": B * Nt / per, "unit": "targets/s", "cores": cores, "kind": "port", "sample": sample}, per
+
+
+def cpu_reference_rate(steps, warmup):
+    """targets/s of the UNMODIFIED reference package (baseline/_ref/ar_tabpfn, imported under an
+    alias) on the bounded sample: ARTabPFNPredictor(backend="triton_shared_context") on CPU tensors,
+    which takes the reference's eager pytorch_context_attention route.  Raises when the package is
+    not there or does not run."""
+    import importlib
+    import types
+    root = os.path.join(ROOT, "baseline", "_ref", "ar_tabpfn")
+    if not os.path.isdir(root):
+        raise FileNotFoundError("baseline/_ref/ar_tabpfn is not installed")
+    pkg = types.ModuleType("ref_ar_tabpfn")
+    pkg.__path__ = [root]
+    sys.modules["ref_ar_tabpfn"] = pkg
+    ref = importlib.import_module("ref_ar_tabpfn.model")
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    ours = build_model()
+    m = ref.ARTabPFN(**CFG).eval()
+    m.load_state_dict(ours.state_dict())
+    m = m.cpu().float()
+    pred = ref.ARTabPFNPredictor.from_trained_model(m, backend="triton_shared_context")
+    B, Nt, xc, yc, xt = _cpu_sample_inputs()
+    torch.manual_seed(SEED)
+    with torch.no_grad():
+        per = _time_calls(lambda: pred.sample_sequence(xc, yc, xt), steps, warmup)
+    sample = (f"{B} streams x {Nt} targets of config3 (context {NC} rows, same weights), full prefill + decode, "
+              f"the reference package itself (triton_shared_context backend on CPU tensors = its eager path), "
+              f"torch CPU fp32, {cores} threads, {steps} timed calls after {warmup} warm-up")
+    return {"value": B * Nt / per, "unit": "targets/s", "cores": cores, "kind": "reference", "sample": sample}, per
+
+
+def cpu_baseline(steps, warmup, allow_reference=True):
+    """(cpu_baseline dict, seconds per call): the reference itself when it runs here, else the port."""
+    why = None
+    if allow_reference:
+        try:
+            return cpu_reference_rate(steps, warmup)
+        except Exception as e:  # noqa: BLE001  (any failure of the foreign package falls back to the port)
+            why = f"{type(e).__name__}: {e}"[:200]
+    base, per = cpu_port_rate(steps, warmup)
+    if why:
+        base["sample"] += f"; reference package not used ({why})"
+    return base, per
+
+
+def cpu_baseline_child(steps=3):
+    """The reference arm in a child process with the GPUs hidden; returns its cpu_baseline object."""
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="", ARTAB_REF_CHILD="1", RANK="0", WORLD_SIZE="1")
+    out = subprocess.run([sys.executable, os.path.abspath(__file__), "--impl", "reference", "--steps", str(steps)],
+                         env=env, stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+    for ln in reversed(out.stdout.strip().splitlines()):
+        if ln.startswith("{"):
+            return json.loads(ln)["cpu_baseline"]
+    raise RuntimeError("the CPU baseline child printed no JSON line (exit code %d)" % out.returncode)
 
 
 def run_reference_arm(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    rate, per, cores, sample = cpu_reference_rate(max(1, min(args.steps, 3)), 1)
+    # The reference decides between its Triton and its eager route by looking for CUDA: hide the GPUs
+    # from this arm (a child process, because torch is already imported here) so that it times the CPU path.
+    if os.environ.get("ARTAB_REF_CHILD") != "1" and os.environ.get("CUDA_VISIBLE_DEVICES", None) != "":
+        env = dict(os.environ, CUDA_VISIBLE_DEVICES="", ARTAB_REF_CHILD="1")
+        raise SystemExit(subprocess.call([sys.executable, os.path.abspath(__file__)] + sys.argv[1:], env=env))
+    steps, warmup = max(1, min(args.steps, 3)), 1
+    base, per = cpu_baseline(steps, warmup)
+    cfg = dict(WORKLOAD_CONFIG)
+    cfg["workload"] = ("config3 BOUNDED CPU SAMPLE: %d streams x %d targets of the %d x %d job, same model and context"
+                       % (CPU_SAMPLE["streams"], CPU_SAMPLE["targets"], STREAMS, NT))
+    cfg["streams_per_gpu"], cfg["targets"] = CPU_SAMPLE["streams"], CPU_SAMPLE["targets"]
+    cfg["l2"] = "n/a (host cores)"
     line = {
-        "impl": "reference", "metric": "ar_targets_decoded_per_sec", "value": rate, "unit": "targets/s",
-        "n_gpus": args.gpus, "steps": max(1, min(args.steps, 3)), "warmup": 1, "ms_per_step": per * 1e3,
+        "impl": "reference", "metric": "ar_targets_decoded_per_sec", "value": base["value"], "unit": "targets/s",
+        "n_gpus": args.gpus, "steps": steps, "warmup": warmup, "ms_per_step": per * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": WORKLOAD_CONFIG,
-        "cpu_baseline": {"value": rate, "unit": "targets/s", "cores": cores, "kind": "port", "sample": sample},
-        "e2e": {"value": rate, "unit": "targets/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "config": cfg, "cpu_baseline": base,
+        "e2e": {"value": base["value"], "unit": "targets/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line), flush=True)
+
+
+def run_scaleout(dev, world, rank, precision, steps=2, warmup=1):
+    """The scale-out configuration (4096 sample streams over a 16384-row x 100-feature shared context,
+    256 targets) split evenly over the ranks: strong scaling, every rank prefills the context locally,
+    samples and log densities gathered with NCCL.  Returns the dict printed under "scaleout"."""
+    import torch.distributed as dist
+    import ar_tabpfn
+    from ar_tabpfn.sharding import sharded_call, shard_bounds
+    B, Nt, Nc = SCALEOUT["streams"], SCALEOUT["targets"], SCALEOUT["ctx"]
+    model = syn.config5_model().to(dev)
+    pred = ar_tabpfn.ARTabPFNPredictor.from_trained_model(model, backend="triton_shared_context", precision=precision)
+    xcr, ycr, xtr, _ = (t.to(dev) for t in syn.config5_rows())
+    # one dataset repeated over the streams: stride-0 views describe the whole job without copies
+    full = (xcr.expand(B, -1, -1), ycr.expand(B, -1), xtr.expand(B, -1, -1))
+    expo, normal = syn.variates(syn.CONFIG5["seed"], Nt, B, CFG["num_components"], dev)
+
+    def run_shard(xc_s, yc_s, xt_s, expo_s, normal_s):
+        ys = pred.sample_sequence(xc_s, yc_s, xt_s, variates=(expo_s, normal_s))
+        return ys, pred.last_logdens
+
+    def sync():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    out = None
+    for _ in range(warmup):
+        out = sharded_call(run_shard, full, variates=(expo, normal))
+    sync()
+    evs = []
+    for _ in range(steps):
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        out = sharded_call(run_shard, full, variates=(expo, normal))
+        e.record()
+        evs.append((s, e))
+    sync()
+    ms = torch.tensor([sum(s.elapsed_time(e) for s, e in evs) / steps], device=dev, dtype=torch.float64)
+    # the context prefill alone (it is repeated on every rank and does not shrink with N)
+    lo, hi = shard_bounds(B, world, rank)
+    pred.init_kv_cache(hi - lo, Nt, dev, torch.float32)
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record()
+    pred.prefill_context(full[0][lo:hi], full[1][lo:hi])
+    e.record()
+    torch.cuda.synchronize()
+    pre = torch.tensor([s.elapsed_time(e)], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        dist.all_reduce(pre, op=dist.ReduceOp.MAX)
+    ys, ld = out
+    return {"workload": "config5: 6L d192 h6 ff768, shared context 16384x100, 256 targets, 4096 streams in total "
+                        "split evenly over the GPUs, context prefilled locally on every rank, results gathered",
+            "streams_total": B, "streams_per_gpu": B // world, "targets": Nt, "context_rows": Nc, "n_gpus": world,
+            "scaling": "strong", "steps": steps, "warmup": warmup, "ms_per_step": float(ms.item()),
+            "targets_per_s": B * Nt / (float(ms.item()) * 1e-3), "prefill_ms": float(pre.item()),
+            "finite": bool(torch.isfinite(ys).all() and torch.isfinite(ld).all()),
+            "device_status": int(pred._bufs["status"].item())}
 
 
 def main():
@@ -182,6 +300,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--precision", default="bf16", choices=["bf16", "fp32"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-scaleout", action="store_true")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)
@@ -191,6 +310,7 @@ def main():
     import torch.distributed as dist
     import ar_tabpfn
     from ar_tabpfn import _lib
+    from ar_tabpfn.sharding import sharded_call
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -206,39 +326,38 @@ def main():
     model = build_model().to(dev)
     pred = ar_tabpfn.ARTabPFNPredictor.from_trained_model(model, backend="triton_shared_context",
                                                           precision=args.precision)
-    xc_h, yc_h, xt_h = (t.pin_memory() for t in workload(STREAMS))
-    xc, yc, xt = xc_h.to(dev), yc_h.to(dev), xt_h.to(dev)
     K = CFG["num_components"]
-    # every rank draws the full-job variates and keeps its shard: results do not depend on N
-    g = torch.Generator(device=dev).manual_seed(SEED)
-    expo = torch.empty(NT, world * STREAMS, K, device=dev).exponential_(1.0, generator=g)
-    normal = torch.randn(NT, world * STREAMS, device=dev, generator=g)
-    var = (expo[:, rank * STREAMS:(rank + 1) * STREAMS].contiguous(),
-           normal[:, rank * STREAMS:(rank + 1) * STREAMS].contiguous())
+    # Full-job tensors, stream axis first, as sharded_call wants them: every rank holds the whole job's
+    # inputs and variates and decodes its own slice, so the results do not depend on N.
+    job = world * STREAMS
+    full_h = tuple(t.pin_memory() for t in workload(job))
+    full = tuple(t.to(dev) for t in full_h)
+    expo, normal = syn.variates(SEED, NT, job, K, dev)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)  # > 126 MB of L2
-    gathered = [torch.empty(world * STREAMS, NT, device=dev) for _ in range(2)] if world > 1 else None
+
+    def run_shard(xc_s, yc_s, xt_s, expo_s, normal_s):
+        ys = pred.sample_sequence(xc_s, yc_s, xt_s, variates=(expo_s, normal_s))
+        return ys, pred.last_logdens
 
     def step_device():
-        ys = pred.sample_sequence(xc, yc, xt, variates=var)
-        ld = pred.last_logdens
-        if world > 1:
-            dist.all_gather_into_tensor(gathered[0], ys.contiguous())
-            dist.all_gather_into_tensor(gathered[1], ld.contiguous())
-        return ys, ld
+        return sharded_call(run_shard, full, variates=(expo, normal))
 
     out_h = [torch.empty(STREAMS, NT).pin_memory() for _ in range(2)]
 
     e2e_bytes = {"h2d": 0}
 
-    def step_e2e():
-        ys = pred.sample_sequence(xc_h, yc_h, xt_h)   # pinned host tensors: the predictor copies what the path reads
+    lo = rank * STREAMS
+
+    def run_shard_host(xc_s, yc_s, xt_s):
+        # pinned host tensors: the predictor copies what the path reads and draws its own random numbers
+        ys = pred.sample_sequence(xc_s, yc_s, xt_s)
         e2e_bytes["h2d"] = pred.last_h2d_bytes
-        ld = pred.last_logdens
-        if world > 1:
-            dist.all_gather_into_tensor(gathered[0], ys.contiguous())
-            dist.all_gather_into_tensor(gathered[1], ld.contiguous())
-        out_h[0].copy_(ys, non_blocking=True)
-        out_h[1].copy_(ld, non_blocking=True)
+        return ys, pred.last_logdens
+
+    def step_e2e():
+        ys, ld = sharded_call(run_shard_host, full_h)
+        out_h[0].copy_(ys[lo:lo + STREAMS], non_blocking=True)
+        out_h[1].copy_(ld[lo:lo + STREAMS], non_blocking=True)
 
     def timed(fn, steps, warmup):
         for _ in range(warmup):
@@ -277,6 +396,11 @@ def main():
     prof = _lib.profile_read()
     lib.artab_profile_enable(0)
     status = int(pred._bufs["status"].item()) if "status" in pred._bufs else 0
+    scaleout = None
+    if not args.no_scaleout:
+        del flush
+        torch.cuda.empty_cache()
+        scaleout = run_scaleout(dev, world, rank, args.precision)
 
     if rank == 0:
         peaks = {}
@@ -302,10 +426,12 @@ def main():
             roof = {"kernel": "dense_tc_kernel" if tc else "dense_chain_kernel", "bound": "tensor",
                     "achieved": ach, "peak": peak, "unit": "TFLOP/s", "frac": ach / peak,
                     "traffic": DENSE_TC_DRAM_BYTES_PER_LAUNCH if tc else None,
-                    "note": ("tcgen05 chain, 8 row tiles of 128 rows (16 CTAs in pairs) per decode launch: bound by the "
-                             "latency of the dependent GEMM/LayerNorm chain of a row tile, not by the tensor pipe"
-                             if tc else "fp32 FMA kernel measured against the bf16 tensor peak")
-                            + (" (of measured)" if peaks else " (of fallback)")}
+                    "traffic_source": "constant: DRAM bytes of one 1024-row decode launch in an ncu capture, "
+                                      "not measured in this run" if tc else None,
+                    "peak_source": "measured" if peaks else "fallback",
+                    "note": ("tcgen05 chain, 8 row tiles of 128 rows per decode launch: bound by the latency of the "
+                             "dependent GEMM / LayerNorm chain of a row tile, not by the tensor pipe"
+                             if tc else "fp32 FMA kernel measured against the bf16 tensor peak")}
         elif dom == "context_attention":
             q_rows = STREAMS * (1 + 2 * (NT - 1)) + NC
             flops = 4.0 * 32 * NC * q_rows * H * L
@@ -313,14 +439,14 @@ def main():
             ach = flops / (shares[dom]["ms"] * 1e-3) / 1e12
             roof = {"kernel": "ctx_attn_tc_kernel", "bound": "tensor", "achieved": ach, "peak": peak,
                     "unit": "TFLOP/s", "frac": ach / peak, "traffic": None,
-                    "note": "of measured" if peaks else "of fallback"}
+                    "peak_source": "measured" if peaks else "fallback"}
         else:
             esz = 2 if args.precision == "bf16" else 4
             byts = sum(range(1, NT)) * STREAMS * H * 32 * 2 * esz * L * 1.0
             peak = peaks.get("hbm_gbs", 6650.0)
             ach = byts / (shares[dom]["ms"] * 1e-3) / 1e9
             roof = {"kernel": "buf_mma_kernel" if args.precision == "bf16" else "buf_merge_kernel", "bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s",
-                    "frac": ach / peak, "traffic": None, "note": "of measured" if peaks else "of fallback"}
+                    "frac": ach / peak, "traffic": None, "peak_source": "measured" if peaks else "fallback"}
         line = {
             "metric": "ar_targets_decoded_per_sec", "value": targets / (ms_dev * 1e-3), "unit": "targets/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_dev,
@@ -333,10 +459,10 @@ def main():
             "gpu_launches": launches, "clocks": clk.result, "roofline": roof, "kernel_shares": shares,
             "device_status": status,
         }
+        if scaleout is not None:
+            line["scaleout"] = scaleout
         if not args.no_cpu_baseline and world == 1:
-            rate, per, cores, sample = cpu_reference_rate(1, 1)
-            line["cpu_baseline"] = {"value": rate, "unit": "targets/s", "cores": cores, "kind": "port",
-                                    "sample": sample}
+            line["cpu_baseline"] = cpu_baseline_child()
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()

@@ -4,8 +4,13 @@
  *
  * Conventions
  *   - Every entry point returns 0 on success or a negative ARTAB_E* code; it never
- *     throws, never synchronises the device and never allocates device memory
- *     (all buffers and workspaces are passed in by the caller).
+ *     throws, never synchronises the device and never allocates device memory.
+ *     Buffers and workspaces are passed in by the caller, with one exception:
+ *     artab_context_attention_noalloc keeps its partials in an array inside the library.
+ *   - The whole-path entry points (artab_prefill, artab_decode_step, artab_decode_embedded,
+ *     artab_teacher_forcing, artab_forward_masked) overlap their own kernels with programmatic
+ *     dependent launch; the single-operator entry points launch plainly, because they cannot know
+ *     what the caller enqueued before them.
  *   - All data pointers are device pointers unless a comment says "host".
  *   - Work is enqueued on `stream` (a cudaStream_t passed as void*).
  *   - Token rows are row-major [rows][d_model]; per-head tensors use the
@@ -237,7 +242,10 @@ ARTAB_API int artab_context_attention(int dtype, const void* q, const void* k_ct
  * The first call on each device looks the array's device address up (a host-side, one-off
  * set-up step): make that first call outside any stream capture.  All calls on a device share
  * the one array: calls whose kernels may overlap on the GPU (different streams) race on it;
- * serialise them.  Every GPU that loads the library holds the 8 MiB until the process exits. */
+ * serialise them.  Every GPU that loads the library holds the 8 MiB until the process exits.
+ * The status word of the bounded waits also lives in the array, out of the caller's reach: if a
+ * wait of the contraction gives up, every element of `out` is NaN (never a mix of stale partials),
+ * which is how such a call reports the failure. */
 ARTAB_API int artab_context_attention_noalloc(int dtype, const void* q, const void* k_ctx, const void* v_ctx,
                                               int rows, int rows_per_group, int n_groups, int n_heads,
                                               int head_dim, int n_ctx, int n_ctx_pad, int n_splits, float* out,

@@ -236,10 +236,15 @@ class Emulation:
 
     qkv: round q, k, v after projection (tensor-core operands / KV cache);
     p:   round softmax numerators before the P.V product and K/V reads;
-    act: round the activation entering every weight matmul."""
+    act: round the activation entering every weight matmul;
+    jitter: non-zero seed: instead of rounding, multiply q, k, v (and the softmax numerators when
+         ``p`` is set) by 1 + d with d uniform in +-2^-9, the relative error bound of bf16
+         rounding.  Several seeds give several realisations of the same rounding noise, which
+         is how the tests estimate how strongly one target amplifies it."""
     qkv: bool = False
     p: bool = False
     act: bool = False
+    jitter: int = 0
 
 
 def layer_count(sd: Dict[str, Tensor]) -> int:
@@ -270,6 +275,11 @@ class OraclePredictor:
         self.v_ctx = []
         self.k_buf = []
         self.v_buf = []
+        self._jit = torch.Generator().manual_seed(self.emu.jitter) if self.emu.jitter else None
+
+    def _jitter(self, t: Tensor) -> Tensor:
+        d = (torch.rand(t.shape, generator=self._jit, dtype=torch.float32) * 2.0 - 1.0) * 2.0 ** -9
+        return t * (1.0 + d.to(t.dtype))
 
     # -- dense pieces ------------------------------------------------------
     def _a(self, x):
@@ -287,7 +297,9 @@ class OraclePredictor:
         q = linear(xa, sd[p + "attn_rows.q_proj.weight"])
         k = linear(xa, sd[p + "attn_rows.k_proj.weight"])
         v = linear(xa, sd[p + "attn_rows.v_proj.weight"])
-        if self.emu.qkv:
+        if self._jit is not None:
+            q, k, v = self._jitter(q), self._jitter(k), self._jitter(v)
+        elif self.emu.qkv:
             q, k, v = _bf16_round(q), _bf16_round(k), _bf16_round(v)
         return x1, q, k, v
 
@@ -316,7 +328,8 @@ class OraclePredictor:
             top = scores.max(dim=-1, keepdim=True).values
             top = torch.where(torch.isinf(top), torch.zeros_like(top), top)
             e = torch.exp(scores - top)
-            p = _bf16_round(e) / e.sum(dim=-1, keepdim=True).clamp_min(1e-38)
+            num = self._jitter(e) if self._jit is not None else _bf16_round(e)
+            p = num / e.sum(dim=-1, keepdim=True).clamp_min(1e-38)
         if dead is not None:
             p = torch.where(dead.unsqueeze(-1), torch.zeros_like(p), p)
         return torch.matmul(p, v)
@@ -364,7 +377,7 @@ class OraclePredictor:
         return layer_norm(x, self.sd["backbone.norm.weight"], self.sd["backbone.norm.bias"])
 
     # -- prefill -------------------------------------------------------------
-    def prefill(self, xc: Tensor, yc: Tensor, shared: bool = True) -> None:
+    def prefill(self, xc: Tensor, yc: Tensor, shared: bool = True, q_chunk: int = 2048) -> None:
         """Populate the context K/V of every layer (inference.py:181-223,
         633-685).  The final backbone norm is not applied here."""
         if shared:
@@ -377,7 +390,11 @@ class OraclePredictor:
             qh, kh, vh = self._heads(q), self._heads(k), self._heads(v)
             self.k_ctx.append(kh)   # [G,H,Nc,Dh], G = 1 when shared
             self.v_ctx.append(vh)
-            a = self._softmax_pv(torch.matmul(qh, kh.transpose(-2, -1)) * (self.Dh ** -0.5), vh)
+            # query rows in chunks: a row's arithmetic does not depend on the chunking, and a
+            # 16384-row context never materialises its 16384 x 16384 score matrix
+            a = torch.cat([self._softmax_pv(torch.matmul(qh[:, :, c0:c0 + q_chunk], kh.transpose(-2, -1))
+                                            * (self.Dh ** -0.5), vh)
+                           for c0 in range(0, qh.shape[2], q_chunk)], dim=2)
             x = self._post(l, x1, self._unheads(a))
         self.k_buf = [None] * self.L
         self.v_buf = [None] * self.L

@@ -71,30 +71,30 @@ def test_joint_density_against_oracle(case):
         want64 = orc.OraclePredictor({k: d(v) for k, v in sd.items()}, H).evaluate_joint_density(
             d(xc), d(yc), d(xt), d(yt), shared=shared)
         noise32 = (want.double() - want64).abs().float()
-        emu = orc.OraclePredictor(sd, H, orc.Emulation(qkv=True, p=True)).evaluate_joint_density(
-            xc, yc, xt, yt, shared=shared)
-        inherent = (emu - want).abs()
+        # How strongly each target amplifies bf16 rounding of q / k / v and of the softmax numerators:
+        # the root mean square, per target, of the oracle's own deviation over five realisations of
+        # that rounding (round-to-nearest, and four draws of a relative error uniform in +-2^-9).
+        devs = [orc.OraclePredictor(sd, H, orc.Emulation(qkv=True, p=True, jitter=seed)).evaluate_joint_density(
+            xc, yc, xt, yt, shared=shared) - want for seed in (0, 1, 2, 3, 4)]
+        sens = torch.stack(devs).pow(2).mean(0).sqrt()
         mc = m.cuda()
         for prec in ("fp32", "bf16"):
             p = ARTabPFNPredictor.from_trained_model(mc, backend=backend, precision=prec)
             got = p.evaluate_joint_density(xc.cuda(), yc.cuda(), xt.cuda(), yt.cuda()).cpu()
             assert int(p._bufs["status"].item()) == 0
             err = (got - want).abs()
-            if prec == "fp32":
-                bound = 1e-5 + 2 * noise32
-            else:
-                # 2e-3 is the bar on well-conditioned targets; where rounding q / k / v and P to bf16
-                # moves the oracle itself further than that, the device may follow it
-                bound = 2e-3 + 2 * inherent
-            frac = float((err <= bound).float().mean())
-            info = (prec, backend, frac, float(err.max()), float(err.median()), float(inherent.max()))
-            if prec == "fp32":
-                assert frac >= 0.97 and float(err.max()) <= 3 * float(bound.max()), info
-            else:
-                # bf16 rounding noise is amplified differently per target and per rounding pattern (the
-                # CPU emulation is one realisation, the device another): most targets sit inside the
-                # bound, the median far inside, and nothing is off by more than a few bf16 ulps of y
-                assert frac >= 0.9 and float(err.median()) <= 1e-3 and float(err.max()) <= 2e-2, info
+            # EVERY target is held to its own bound, none is excused: the bar of the mode plus a
+            # multiple of what the same arithmetic costs the oracle on that very target
+            # (fp32: distance of the fp32 oracle from its fp64 evaluation; bf16: `sens` above).
+            bound = 1e-5 + 4 * noise32 if prec == "fp32" else 2e-3 + 4 * sens
+            worst = int((err / bound).flatten().argmax())
+            info = dict(prec=prec, backend=backend, worst_target=worst, err=float(err.flatten()[worst]),
+                        bound=float(bound.flatten()[worst]), want=float(want.flatten()[worst]),
+                        over_bar=int((err > (1e-5 if prec == "fp32" else 2e-3)).sum()), targets=err.numel(),
+                        max_err=float(err.max()), median_err=float(err.median()))
+            print(info)
+            assert bool((err <= bound).all()), info
+            assert float(err.median()) <= (1e-5 if prec == "fp32" else 1e-3), info
         # sampling: the device's own log density of its draws equals its teacher-forced density
         # of those draws once the AR-token index convention is aligned
         with torch.no_grad():
@@ -105,7 +105,7 @@ def test_joint_density_against_oracle(case):
         jd = p.evaluate_joint_density(xc.cuda(), yc.cuda(), xt.cuda(), ys)
         assert torch.isfinite(ys).all()
         gap = (jd - ld).abs()
-        lim = 4e-3 + 4 * float(inherent.max())
+        lim = 4e-3 + 4 * float(sens.max())
         assert float(gap.median()) <= lim / 4 and float((gap <= lim).float().mean()) >= 0.97, (float(gap.max()), lim)
 
 
