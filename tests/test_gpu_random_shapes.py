@@ -86,7 +86,10 @@ def test_joint_density_against_oracle(case):
             # EVERY target is held to its own bound, none is excused: the bar of the mode plus a
             # multiple of what the same arithmetic costs the oracle on that very target
             # (fp32: distance of the fp32 oracle from its fp64 evaluation; bf16: `sens` above).
-            bound = 1e-5 + 4 * noise32 if prec == "fp32" else 2e-3 + 4 * sens
+            # One fp32-vs-fp64 difference is a single draw of that target's rounding noise and can be
+            # small by accident, so it is floored by the root mean square over the target's stream.
+            noise = torch.maximum(noise32, noise32.pow(2).mean(1, keepdim=True).sqrt())
+            bound = 1e-5 + 4 * noise if prec == "fp32" else 2e-3 + 4 * sens
             worst = int((err / bound).flatten().argmax())
             info = dict(prec=prec, backend=backend, worst_target=worst, err=float(err.flatten()[worst]),
                         bound=float(bound.flatten()[worst]), want=float(want.flatten()[worst]),
