@@ -162,6 +162,7 @@ __device__ __forceinline__ float fast_exp2(float x) {  // MUFU ex2: relative err
 // ---------------------------------------------------------------------------
 template <typename T, int DH>
 __global__ void __launch_bounds__(128, 6) buf_merge_kernel(const BufMergeArgs a) {
+  dep_trigger();  // the dependent dense chain reads only model constants before its wait (see buf_mma_kernel)
   constexpr int VEC = Vec16<T>::N;
   constexpr int LPK = DH / VEC;   // lanes per key
   constexpr int KPI = 32 / LPK;   // keys per warp iteration
@@ -320,7 +321,6 @@ __global__ void __launch_bounds__(128, 6) buf_merge_kernel(const BufMergeArgs a)
   // The buffer pass above read only what kernels older than the preceding one wrote (q and the
   // buffer rows); the context partials come from the preceding kernel.
   dep_wait();
-  dep_trigger();
 
   // log-sum-exp merge with the context partials, all in registers
 #pragma unroll

@@ -64,6 +64,11 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 __global__ void __launch_bounds__(WPB * 32, 6) buf_mma_kernel(const BufMergeArgs a) {
   __shared__ __align__(16) uint8_t vs[WPB][NR][KB * PITCH];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  // The dependent of this kernel is always a dense chain, which reads nothing but model constants
+  // before its own wait: it may become resident (barriers, tensor-memory allocation, first weight
+  // tiles) while this kernel is still walking the private buffers.  Its wait still covers everything
+  // older, because this grid only completes after its own wait below.
+  dep_trigger();
   const long item = (long)blockIdx.x * WPB + warp;
   if (item >= a.n_items) return;  // warp-uniform; the kernel has no CTA-wide barrier
   const int g = lane >> 2;   // fragment row: query index (rows 0, 1) / key inside an 8-key tile
@@ -196,7 +201,6 @@ __global__ void __launch_bounds__(WPB * 32, 6) buf_mma_kernel(const BufMergeArgs
   // The pass above read only what kernels older than the preceding one wrote (q and the buffer
   // rows); the context partials come from the preceding kernel.
   dep_wait();
-  dep_trigger();
 
   if (g >= 2 || rows2[g & 1] < 0) return;
   const long r = rows2[g];

@@ -26,7 +26,10 @@ void prof_end(cudaStream_t s);
 // Rules every such kernel follows: (1) it calls dep_wait() before it reads anything an earlier
 // kernel wrote and before it writes global memory; (2) it calls dep_trigger() only after its own
 // dep_wait(), so a dependent that starts early knows that everything older than its predecessor
-// has completed.  Without the launch attribute both calls are no-ops.
+// has completed.  One exception to (2): the buffer-pass kernels trigger at their start, because
+// their dependent is always a dense chain, which touches only model constants before its own wait
+// (and that wait still covers everything older: a buffer-pass grid completes only after its own
+// wait).  Without the launch attribute both calls are no-ops.
 //
 // What each kernel reads BEFORE its dep_wait() (the work it overlaps with its predecessor):
 //   embed_kernel            nothing

@@ -166,6 +166,12 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* r) {
       : "r"(taddr)
       : "memory");
 }
+__device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t* r) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+               : "r"(taddr)
+               : "memory");
+}
 __device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t* r) {
   asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"r"(taddr), "r"(r[0]),
                "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
@@ -183,6 +189,37 @@ __device__ __forceinline__ void split2(float a, float b, uint32_t& hi, uint32_t&
   hi = pack_bf16(a, b);
   lo = pack_bf16(a - __uint_as_float(hi << 16), b - __uint_as_float(hi & 0xffff0000u));
 }
+
+// Two fp32 operations per issued instruction (fma / add / mul .f32x2 on a register pair): the epilogue
+// phases are bound by instruction issue on one SM, not by the fp32 pipe.
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
+  float2 d;
+  asm("{\n\t.reg .b64 ra, rb, rc, rd;\n\t"
+      "mov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\tmov.b64 rc, {%6, %7};\n\t"
+      "fma.rn.f32x2 rd, ra, rb, rc;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+      : "=f"(d.x), "=f"(d.y)
+      : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y), "f"(c.x), "f"(c.y));
+  return d;
+}
+__device__ __forceinline__ float2 add2(float2 a, float2 b) {
+  float2 d;
+  asm("{\n\t.reg .b64 ra, rb, rd;\n\t"
+      "mov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\t"
+      "add.rn.f32x2 rd, ra, rb;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+      : "=f"(d.x), "=f"(d.y)
+      : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+  return d;
+}
+__device__ __forceinline__ float2 mul2(float2 a, float2 b) {
+  float2 d;
+  asm("{\n\t.reg .b64 ra, rb, rd;\n\t"
+      "mov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\t"
+      "mul.rn.f32x2 rd, ra, rb;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+      : "=f"(d.x), "=f"(d.y)
+      : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+  return d;
+}
+__device__ __forceinline__ float2 splat2(float a) { return make_float2(a, a); }
 
 // GELU with erf(z) = 1 - 2^q(z) for z >= 0, q a degree-8 polynomial fitted to log2(erfc) on [0, 4]
 // (|erf error| < 4e-6, below the 2^-17 of the hi + lo operand split): one MUFU op per element.
@@ -208,9 +245,35 @@ __device__ __forceinline__ float gelu_fast(float x) {
 #ifdef ARTAB_TIMELINE
 __device__ long long g_tl[32][32][32];   // [launch slot][cta][mark]
 #define TL(id) do { if (tl_on) g_tl[a.tl_slot & 31][blockIdx.x & 31][id] = clock64(); } while (0)
+__device__ __forceinline__ long long gtimer() { long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
+#define TLG(id) do { if (tl_on) g_tl[a.tl_slot & 31][blockIdx.x & 31][id] = gtimer(); } while (0)
 #else
 #define TL(id) do { } while (0)
+#define TLG(id) do { } while (0)
 #endif
+
+// The same for two neighbouring columns at once, on packed pairs (same operations, same rounding as
+// gelu_fast; sign(x) * (1 - e) * x / 2 is written (1 - e) * |x| / 2, which is the same product).
+__device__ __forceinline__ float2 gelu_fast2(float2 x) {
+  const float2 ax = make_float2(fabsf(x.x), fabsf(x.y));
+  float2 z = mul2(ax, splat2(0.70710678118654752f));
+  z.x = fminf(z.x, 6.0f);
+  z.y = fminf(z.y, 6.0f);
+  float2 q = fma2(splat2(-1.2271906e-06f), z, splat2(-2.4917551e-06f));
+  q = fma2(q, z, splat2(0.00038366718f));
+  q = fma2(q, z, splat2(-0.0049292254f));
+  q = fma2(q, z, splat2(0.03347154f));
+  q = fma2(q, z, splat2(-0.15211754f));
+  q = fma2(q, z, splat2(-0.9171586f));
+  q = fma2(q, z, splat2(-1.6280657f));
+  q = mul2(q, z);
+  float2 e;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e.x) : "f"(q.x));
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e.y) : "f"(q.y));
+  const float2 t = fma2(e, splat2(-1.0f), splat2(1.0f));   // 1 - e, exact like the subtraction
+  const float2 h = mul2(x, splat2(0.5f));
+  return fma2(t, mul2(ax, splat2(0.5f)), h);               // 0.5 x (1 + erf)
+}
 
 struct __align__(1024) Smem {
   uint8_t ring[2][NSLOT][192 * 128];  // two weight rings (first / second MLP GEMM), slabs <= d_model * 128 bytes
@@ -448,6 +511,23 @@ struct Epilogue {
     }
     done();
   }
+  // v <- hi + lo of this thread's columns of the activation operand: what publish_ax stored, i.e. the
+  // published values to 2^-18 relative.  The MLP's residual x2 is read back this way after the MLP
+  // (the operand stays in tensor memory until the next publish) instead of waiting in a workspace.
+  __device__ void load_ax(float* v) {
+#pragma unroll
+    for (int c = 0; c < NCH; ++c) {
+      uint32_t hi[8], lo[8];
+      tmem_ld8(t_row + kAxHi + (col0 >> 1) + 8 * c, hi);
+      tmem_ld8(t_row + kAxLo + (col0 >> 1) + 8 * c, lo);
+      tmem_wait_ld();
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        v[16 * c + 2 * i] = __uint_as_float(hi[i] << 16) + __uint_as_float(lo[i] << 16);
+        v[16 * c + 2 * i + 1] = __uint_as_float(hi[i] & 0xffff0000u) + __uint_as_float(lo[i] & 0xffff0000u);
+      }
+    }
+  }
   __device__ void done() {
     tmem_wait_st();
     tc_fence_before();
@@ -465,22 +545,30 @@ struct Epilogue {
     for (int g = 0; g < NWG; ++g) tot += sm->xs[ph][g][row];
     return tot;
   }
-  // LayerNorm over the full row (NWG threads, one per column group)
+  // LayerNorm over the full row (NWG threads, one per column group); pairs of columns go through the
+  // packed fp32 instructions, gamma / beta come as 16-byte shared-memory loads
   __device__ void layer_norm(float* v, const float* gamma, const float* beta) {
-    float s = 0.f;
+    float2 s2 = make_float2(0.f, 0.f);
 #pragma unroll
-    for (int i = 0; i < PART; ++i) s += v[i];
-    const float mean = row_total(s) / (float)D;
-    float ss = 0.f;
+    for (int i = 0; i < PART; i += 2) s2 = add2(s2, make_float2(v[i], v[i + 1]));
+    const float mean = row_total(s2.x + s2.y) / (float)D;
+    const float2 nm = splat2(-mean);
+    float2 ss2 = make_float2(0.f, 0.f);
 #pragma unroll
-    for (int i = 0; i < PART; ++i) {
-      const float d = v[i] - mean;
-      ss = fmaf(d, d, ss);
+    for (int i = 0; i < PART; i += 2) {
+      const float2 d = add2(make_float2(v[i], v[i + 1]), nm);
+      ss2 = fma2(d, d, ss2);
     }
-    const float var = row_total(ss) / (float)D;
-    const float rstd = 1.0f / sqrtf(var + 1e-5f);
+    const float var = row_total(ss2.x + ss2.y) / (float)D;
+    const float2 rstd = splat2(1.0f / sqrtf(var + 1e-5f));
 #pragma unroll
-    for (int i = 0; i < PART; ++i) v[i] = (v[i] - mean) * rstd * gamma[col0 + i] + beta[col0 + i];
+    for (int i = 0; i < PART; i += 4) {
+      const float4 g = *reinterpret_cast<const float4*>(gamma + col0 + i);
+      const float4 b = *reinterpret_cast<const float4*>(beta + col0 + i);
+      const float2 y0 = fma2(mul2(add2(make_float2(v[i], v[i + 1]), nm), rstd), make_float2(g.x, g.y), make_float2(b.x, b.y));
+      const float2 y1 = fma2(mul2(add2(make_float2(v[i + 2], v[i + 3]), nm), rstd), make_float2(g.z, g.w), make_float2(b.z, b.w));
+      v[i] = y0.x; v[i + 1] = y0.y; v[i + 2] = y1.x; v[i + 3] = y1.y;
+    }
   }
   // hidden tile j: act(ACC_H + bias) -> split -> swizzled shared-memory operand
   // (jl counts this CTA's tiles, j is the tile's index in the MLP)
@@ -496,11 +584,14 @@ struct Epilogue {
     mbar_arrive(&sm->acch_free);  // the accumulator is in registers: the next tile's GEMM may overwrite it
     uint32_t hi[16], lo[16];
 #pragma unroll
-    for (int i = 0; i < 16; ++i) {
-      const float2 bb = *reinterpret_cast<const float2*>(bias + j * HT + HPART * wg + 2 * i);
-      const float x0 = gelu_fast(__uint_as_float(r[i >> 3][(2 * i) & 15]) + bb.x);
-      const float x1 = gelu_fast(__uint_as_float(r[i >> 3][(2 * i + 1) & 15]) + bb.y);
-      split2(x0, x1, hi[i], lo[i]);
+    for (int i = 0; i < 16; i += 2) {
+      const float4 bb = *reinterpret_cast<const float4*>(bias + j * HT + HPART * wg + 2 * i);
+      const float2 a0 = make_float2(__uint_as_float(r[i >> 3][(2 * i) & 15]), __uint_as_float(r[i >> 3][(2 * i + 1) & 15]));
+      const float2 a1 = make_float2(__uint_as_float(r[i >> 3][(2 * i + 2) & 15]), __uint_as_float(r[i >> 3][(2 * i + 3) & 15]));
+      const float2 g0 = gelu_fast2(add2(a0, make_float2(bb.x, bb.y)));
+      const float2 g1 = gelu_fast2(add2(a1, make_float2(bb.z, bb.w)));
+      split2(g0.x, g0.y, hi[i], lo[i]);
+      split2(g1.x, g1.y, hi[i + 1], lo[i + 1]);
     }
     if (jl >= 1) {  // the previous tile's second GEMM must have finished reading the operand buffer
       ok = mbar_wait(&sm->ah_free, free_count & 1, &sm->abort_flag) && ok;
@@ -729,6 +820,7 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const DenseArgs a
     const bool tl_on = threadIdx.x == 64;
 #endif
     TL(0);
+    TLG(29);
     e.sm = sm;
     e.row = 32 * (warp & 3) + lane;
     e.wg = (warp - 2) >> 2;
@@ -798,6 +890,7 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const DenseArgs a
     dep_wait();
     dep_trigger();
     TL(2);
+    TLG(30);
     if (a.do_post) {
       load_lm(a.attn);
       e.publish_ax(v);
@@ -806,16 +899,15 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const DenseArgs a
       e.wait_acc();
       TL(4);
       e.sync_groups();                           // the staged vectors are complete
+      TL(27);
       e.add_acc(v);
+      TL(28);
       e.layer_norm(v, sm->vec[0], sm->vec[1]);   // v = x2
+      TL(25);
       e.publish_ax(v);
       TL(5);
-      // x2 is the residual of the last LayerNorm; it waits in this thread's own slice of a workspace
-      // so that the MLP epilogue has the registers: the x1 workspace (free until the next layer
-      // writes it), or, in a CTA pair, this CTA's own slot of the pair scratch — the peer reads its
-      // residual input from the x1 workspace at its own pace.
-      float* park = csize > 1 ? a.pair_scratch + (size_t)(4 + crank) * a.pair_slot_stride : a.x1_out;
-      store_lm(park);
+      // x2 is the residual of the last LayerNorm.  The MLP epilogue needs the registers, and x2 sits in
+      // tensor memory anyway as the hi + lo operand just published: it is read back from there.
       TL(6);
       {
         int jl = 0;
@@ -824,7 +916,7 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const DenseArgs a
           TL(7 + (jl < 5 ? jl : 5));
         }
       }
-      load_lm(park);
+      e.load_ax(v);
       e.wait_acc();
       e.drain_free();
       TL(13);
@@ -1020,6 +1112,7 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const DenseArgs a
     }
     if (!e.ok && threadIdx.x == 64 && a.status) atomicExch(a.status, 3);
     TL(26);
+    TLG(31);
   }
 
   tc_fence_before();
