@@ -278,7 +278,7 @@ __device__ __forceinline__ float2 gelu_fast2(float2 x) {
 struct __align__(1024) Smem {
   uint8_t ring[2][NSLOT][192 * 128];  // two weight rings (first / second MLP GEMM), slabs <= d_model * 128 bytes
   uint8_t ah[2][2][BM * 128];         // hidden tile operand [hi, lo][k-chunk][128 rows x 64 bf16], swizzled
-  float xs[2][NWG][BM];               // LayerNorm partial sums exchanged between the column groups
+  float xs[2 * NWG][BM];              // LayerNorm partial statistics (mean, M2) exchanged between the column groups
   float bias_h[1024];                 // hidden bias of the current MLP (b1 / head.0 bias), d_ff <= 1024
   float vec[8][192];                  // ln2 g,b | b2 | ln3 g,b | (ln1 | final) g,b | spare
   __nv_bfloat16* rowdst[BM];          // private-buffer K slot of each row's token (null: not cached)
@@ -288,6 +288,8 @@ struct __align__(1024) Smem {
   uint32_t tmem_base;
   int abort_flag;
 };
+
+static_assert(sizeof(Smem) + 1024 <= 227 * 1024, "shared-memory plan exceeds what one CTA may request");
 
 __device__ __forceinline__ bool direct_mode(int mode) { return mode == KV_PREFILL; }
 
@@ -475,6 +477,9 @@ struct Epilogue {
   static constexpr int NCH = PART / 16;    // 16-column chunks
   static constexpr int HPART = HT / NWG;   // hidden-tile columns owned by one thread (16)
   Smem* sm;
+#ifdef ARTAB_TIMELINE
+  int tl_slot;
+#endif
   uint32_t t_row;                          // TMEM address of this thread's lane
   int row, wg, col0;
   int acc_phase, xs_phase;
@@ -482,6 +487,8 @@ struct Epilogue {
   bool ok;
 
   __device__ void sync_groups() { asm volatile("bar.sync 3, %0;" ::"n"(kEpi) : "memory"); }
+  // only the four warps that own this row quadrant (one per column group) meet
+  __device__ void quadrant_sync() { asm volatile("bar.sync %0, 128;" ::"r"(4 + (row >> 5)) : "memory"); }
 
   __device__ void wait_acc() {
     ok = mbar_wait(&sm->acc_full, acc_phase & 1, &sm->abort_flag) && ok;
@@ -533,34 +540,43 @@ struct Epilogue {
     tc_fence_before();
     mbar_arrive(&sm->ep_done);
   }
-  // sum of one value per column group of this row, added in a fixed order (deterministic)
-  __device__ float row_total(float part) {
-    const int ph = xs_phase & 1;
-    ++xs_phase;
-    sm->xs[ph][wg][row] = part;
-    // only the four warps that own this row quadrant (one per column group) need to meet
-    asm volatile("bar.sync %0, 128;" ::"r"(4 + (row >> 5)) : "memory");
-    float tot = 0.f;
-#pragma unroll
-    for (int g = 0; g < NWG; ++g) tot += sm->xs[ph][g][row];
-    return tot;
-  }
-  // LayerNorm over the full row (NWG threads, one per column group); pairs of columns go through the
-  // packed fp32 instructions, gamma / beta come as 16-byte shared-memory loads
+  // LayerNorm over the full row (NWG threads, one per column group).  Every thread takes the mean and
+  // the sum of squared deviations of its own columns (two local passes, no cancellation); the groups
+  // are then combined with the pairwise-variance update after ONE exchange through shared memory, in a
+  // fixed order (deterministic).  Pairs of columns go through the packed fp32 instructions, gamma /
+  // beta come as 16-byte shared-memory loads.
   __device__ void layer_norm(float* v, const float* gamma, const float* beta) {
     float2 s2 = make_float2(0.f, 0.f);
 #pragma unroll
     for (int i = 0; i < PART; i += 2) s2 = add2(s2, make_float2(v[i], v[i + 1]));
-    const float mean = row_total(s2.x + s2.y) / (float)D;
-    const float2 nm = splat2(-mean);
+    const float lmean = (s2.x + s2.y) * (1.0f / (float)PART);
+    const float2 nl = splat2(-lmean);
     float2 ss2 = make_float2(0.f, 0.f);
 #pragma unroll
     for (int i = 0; i < PART; i += 2) {
-      const float2 d = add2(make_float2(v[i], v[i + 1]), nm);
+      const float2 d = add2(make_float2(v[i], v[i + 1]), nl);
       ss2 = fma2(d, d, ss2);
     }
-    const float var = row_total(ss2.x + ss2.y) / (float)D;
-    const float2 rstd = splat2(1.0f / sqrtf(var + 1e-5f));
+    // The exchange buffer is single: two LayerNorms of one launch are always separated by an
+    // accumulator wait that every epilogue thread passes (so nobody still reads the old statistics),
+    // except the final LayerNorm, which follows the last layer's directly: quadrant_sync() before it.
+    sm->xs[wg][row] = lmean;
+    sm->xs[NWG + wg][row] = ss2.x + ss2.y;
+    quadrant_sync();
+    float msum = 0.f, m2 = 0.f, gm[NWG];
+#pragma unroll
+    for (int g = 0; g < NWG; ++g) {
+      gm[g] = sm->xs[g][row];
+      msum += gm[g];
+      m2 += sm->xs[NWG + g][row];
+    }
+    const float mean = msum * (1.0f / (float)NWG);
+    float dev = 0.f;
+#pragma unroll
+    for (int g = 0; g < NWG; ++g) dev = fmaf(gm[g] - mean, gm[g] - mean, dev);
+    const float var = fmaf((float)PART, dev, m2) * (1.0f / (float)D);
+    const float2 rstd = splat2(rsqrtf(var + 1e-5f));
+    const float2 nm = splat2(-mean);
 #pragma unroll
     for (int i = 0; i < PART; i += 4) {
       const float4 g = *reinterpret_cast<const float4*>(gamma + col0 + i);
@@ -576,6 +592,9 @@ struct Epilogue {
     ok = mbar_wait(&sm->h_full, h_count & 1, &sm->abort_flag) && ok;
     ++h_count;
     tc_fence_after();
+#ifdef ARTAB_TIMELINE
+    if (jl == 1 && threadIdx.x == 64) g_tl[tl_slot & 31][blockIdx.x & 31][10] = clock64();
+#endif
     uint32_t r[2][16];
 #pragma unroll
     for (int c = 0; c < 2; ++c) tmem_ld16(t_row + kAccH + HPART * wg + 16 * c, r[c]);
@@ -593,10 +612,16 @@ struct Epilogue {
       split2(g0.x, g0.y, hi[i], lo[i]);
       split2(g1.x, g1.y, hi[i + 1], lo[i + 1]);
     }
+#ifdef ARTAB_TIMELINE
+    if (jl == 1 && threadIdx.x == 64) g_tl[tl_slot & 31][blockIdx.x & 31][11] = clock64();
+#endif
     if (jl >= 1) {  // the previous tile's second GEMM must have finished reading the operand buffer
       ok = mbar_wait(&sm->ah_free, free_count & 1, &sm->abort_flag) && ok;
       ++free_count;
     }
+#ifdef ARTAB_TIMELINE
+    if (jl == 1 && threadIdx.x == 64) g_tl[tl_slot & 31][blockIdx.x & 31][12] = clock64();
+#endif
     // this thread's 32 hidden columns sit in k-chunk wg / 2, 16-byte chunks 4 * (wg % 2) .. + 3 of the
     // 128-byte row; chunk c of row r lives at chunk position c ^ (r % 8)
     uint8_t* base_hi = sm->ah[0][wg >> 1] + row * 128;
@@ -767,7 +792,9 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const DenseArgs a
         p.mlp_first(a.tc_wa, a.tc_head_lo & 1, NKC, nt, h_first, h_step);
       } else if (a.do_pre) {
         p.matrix(a.pre_w.tc_wf, NKC, lo_pre & 8, kSlab);
-        p.matrix_range(a.pre_w.tc_wqkv, t_begin * NKC, t_end * NKC, lo_pre & 16, kSlab);
+        // this CTA's projections alternate between the two rings (the second ring is idle once the
+        // MLP is over), so the next projection's weights are resident before its MMAs can start
+        for (int t = t_begin; t < t_end; t += 2) p.matrix_range(a.pre_w.tc_wqkv, t * NKC, (t + 1) * NKC, lo_pre & 16, kSlab);
       }
     }
   } else if (warp == 19) {
@@ -777,6 +804,8 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const DenseArgs a
       if (a.do_post) p.mlp_second(a.post_w.tc_w2, lo_post & 4, kSlab, nt, crank, csize);
       if (a.do_head) {
         p.mlp_second(a.tc_wb, a.tc_head_lo & 2, 16 * 128, nt, h_first, h_step);
+      } else if (a.do_pre) {
+        for (int t = t_begin + 1; t < t_end; t += 2) p.matrix_range(a.pre_w.tc_wqkv, t * NKC, (t + 1) * NKC, lo_pre & 16, kSlab);
       }
     }
   } else if (warp == 1) {
@@ -798,9 +827,13 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const DenseArgs a
         m.gemm_full_ts(kAccA, D, NKC, lo_pre & 8);
         umma_commit(&sm->acc_full);
         m.wait_epilogue();                               // A_x = x1
+        // second ring, continued where the second issuer left it (the MLP's second GEMM of this launch)
+        Issuer mb{sm, tmem, 1, a.do_post ? n_mine * 2 * ((lo_post & 4) ? 2 : 1) : 0, 0, 0, 0, true};
         for (int t = t_begin; t < t_end; ++t) {
           if (t > t_begin) m.wait_epilogue();            // previous projection drained from ACC_A
-          m.gemm_full_ts(kAccA, D, NKC, lo_pre & 16);
+          Issuer& g = ((t - t_begin) & 1) ? mb : m;
+          g.ok = g.ok && m.ok;
+          g.gemm_full_ts(kAccA, D, NKC, lo_pre & 16);
           umma_commit(&sm->acc_full);
         }
       }
@@ -818,6 +851,7 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const DenseArgs a
     constexpr int PART = Epilogue<D>::PART;
 #ifdef ARTAB_TIMELINE
     const bool tl_on = threadIdx.x == 64;
+    e.tl_slot = a.tl_slot;
 #endif
     TL(0);
     TLG(29);
@@ -936,6 +970,7 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const DenseArgs a
       e.sync_groups();                           // the staged vectors are complete
     }
     if (a.do_final) {
+      e.quadrant_sync();                                       // the previous LayerNorm's statistics have been read
       e.layer_norm(v, sm->vec[5], sm->vec[6]);                 // v = z
       if (a.z_out && crank == 0) store_row(a.z_out);
     }
