@@ -13,6 +13,8 @@ from typing import Optional
 import torch
 
 F32, BF16 = 0, 1
+ETIMEOUT = -5
+DEBUG_WAIT_CYCLES, DEBUG_DROP_SCORE_COMMITS = 0, 1
 MARK_TARGET, MARK_CONTEXT, MARK_BUFFER = 0, 1, 2
 MAX_SPLITS = 16
 
@@ -62,6 +64,7 @@ _SIGNATURES = {
     "artab_plan_splits": (_i, [_i, _i, _i, _i, _i, _i]),
     "artab_profile_enable": (None, [_i]),
     "artab_set_dependent_launch": (None, [_i]),
+    "artab_debug_set": (_i, [_i, C.c_longlong]),
     "artab_profile_read": (_i, [C.POINTER(C.c_double), C.POINTER(C.c_int64), _i]),
     "artab_launch_count": (C.c_int64, []),
     "artab_launch_count_reset": (None, []),

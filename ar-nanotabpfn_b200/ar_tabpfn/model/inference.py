@@ -63,6 +63,8 @@ class ARTabPFNPredictor:
         self.last_logdens: Optional[Tensor] = None
         self.last_components: Optional[Tensor] = None
         self.last_h2d_bytes = 0
+        self._status_host: Optional[Tensor] = None
+        self._status_event = None
 
     @classmethod
     def from_trained_model(cls, model, backend: str = "flex_attention",
@@ -200,6 +202,40 @@ class ARTabPFNPredictor:
             layer.k_buf_cache = kv[l, :, :, :, 0]
             layer.v_buf_cache = kv[l, :, :, :, 1]
 
+    # ---------------------------------------------------------------- status
+    def _mirror_status(self) -> None:
+        """Queue a copy of the device status word (non-zero: a bounded device-side wait gave up and
+        the results of that call are void) into pinned host memory behind the work just enqueued."""
+        st = self._bufs.get("status")
+        if st is None:
+            return
+        if self._status_host is None:
+            self._status_host = torch.zeros(1, dtype=torch.int32).pin_memory()
+        self._status_host.copy_(st, non_blocking=True)
+        self._status_event = torch.cuda.current_stream(st.device).record_event()
+
+    def last_status(self, wait: bool = True) -> int:
+        """Status word of the most recent whole-path call: 0, or the code of the kernel whose wait ran
+        out.  ``wait=False`` returns -1 while that call is still running instead of blocking."""
+        if self._status_event is None:
+            return 0
+        if not wait and not self._status_event.query():
+            return -1
+        self._status_event.synchronize()
+        return int(self._status_host.item())
+
+    def _raise_if_timed_out(self) -> None:
+        """Called at the start of every whole-path call: if the previous call has finished and one of
+        its waits ran out, raise (ARTAB_ETIMEOUT) instead of silently continuing; never blocks."""
+        if self.last_status(wait=False) > 0:
+            code = int(self._status_host.item())
+            self._status_event = None
+            st = self._bufs.get("status")
+            if st is not None:
+                st.zero_()
+            raise _lib.ArtabError(f"artab error {_lib.ETIMEOUT}: a bounded device-side wait gave up in the previous "
+                                  f"call (status {code}); its results are void")
+
     # --------------------------------------------------------------- prefill
     @torch.no_grad()
     def prefill_context(self, x_context: Tensor, y_context: Tensor) -> None:
@@ -303,6 +339,7 @@ class ARTabPFNPredictor:
         reads is copied - with the shared-context backend that is batch element 0 of the
         context, not B copies of it (``last_h2d_bytes`` counts the bytes)."""
         lib = _lib.lib()
+        self._raise_if_timed_out()
         B, Nc, F = x_context.shape
         Nt = x_target.shape[1]
         device, dtype = self._work_device(x_context), x_context.dtype
@@ -366,6 +403,7 @@ class ARTabPFNPredictor:
         self.seq_len = self.context_len + self.buffer_len
         self.last_logdens = logdens
         self.last_components = comp
+        self._mirror_status()
         return samples.to(dtype)
 
     # ------------------------------------------------------- teacher forcing
@@ -374,6 +412,7 @@ class ARTabPFNPredictor:
                                y_target: Tensor) -> Tensor:
         """Teacher-forced log density of every target, [B,Nt], in one block-causal pass."""
         lib = _lib.lib()
+        self._raise_if_timed_out()
         B, Nc, F = x_context.shape
         Nt = x_target.shape[1]
         device, dtype = self._work_device(x_context), x_context.dtype
@@ -393,6 +432,7 @@ class ARTabPFNPredictor:
                                              _lib.ptr(out), _lib.stream_ptr()))
         self.buffer_len = int(self._state.buffer_len)
         self.seq_len = self.context_len + self.buffer_len
+        self._mirror_status()
         return out.to(dtype)
 
     # -------------------------------------------------------- masked forward
@@ -404,6 +444,7 @@ class ARTabPFNPredictor:
         [Buffer_0..Buffer_{Nb-1}, Target_0..Target_{Nt-1}] sees the context plus the first
         ``visible[j]`` buffer rows (``RowMask.visible`` of ``create_row_mask``)."""
         lib = _lib.lib()
+        self._raise_if_timed_out()
         B, Nc, F = x_context.shape
         Nb, Nt = x_buffer.shape[1], x_target.shape[1]
         if len(visible) != Nb + Nt:
@@ -429,4 +470,5 @@ class ARTabPFNPredictor:
                                             _lib.stream_ptr()))
         self.buffer_len = int(self._state.buffer_len)
         self.seq_len = self.context_len + self.buffer_len
+        self._mirror_status()
         return out.to(dtype)

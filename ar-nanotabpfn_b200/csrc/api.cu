@@ -44,6 +44,11 @@ static int dependent_launch_default() {
   return !(e && e[0] == '0');
 }
 static std::atomic<int> g_dependent_launch{dependent_launch_default()};
+static std::atomic<long long> g_debug_wait_cycles{0};
+static std::atomic<int> g_debug_drop_score_commits{0};
+long long debug_wait_cycles() { return g_debug_wait_cycles.load(std::memory_order_relaxed); }
+int debug_drop_score_commits() { return g_debug_drop_score_commits.load(std::memory_order_relaxed); }
+
 static thread_local int g_plain_scope = 0;
 PlainLaunchScope::PlainLaunchScope() { ++g_plain_scope; }
 PlainLaunchScope::~PlainLaunchScope() { --g_plain_scope; }
@@ -376,6 +381,21 @@ int artab_plan_splits(int dtype, int rows, int rows_per_group, int n_groups, int
 }
 
 void artab_profile_enable(int on) { g_prof_on = on != 0; }
+
+int artab_debug_set(int key, long long value) {
+  switch (key) {
+    case ARTAB_DEBUG_WAIT_CYCLES:
+      ARTAB_REQUIRE(value >= 0, ARTAB_EINVAL, "debug_set: the wait limit must be >= 0 cycles");
+      g_debug_wait_cycles.store(value, std::memory_order_relaxed);
+      return ARTAB_OK;
+    case ARTAB_DEBUG_DROP_SCORE_COMMITS:
+      g_debug_drop_score_commits.store(value != 0, std::memory_order_relaxed);
+      return ARTAB_OK;
+    default:
+      set_error("debug_set: unknown key %d", key);
+      return ARTAB_EINVAL;
+  }
+}
 
 void artab_set_dependent_launch(int on) { g_dependent_launch.store(on != 0, std::memory_order_relaxed); }
 

@@ -40,6 +40,14 @@ constexpr uint32_t kColO = 128;  // O tile: 64 fp32 columns = P.V_hi | P.V_lo
 constexpr uint32_t kColP = 192;  // P: 128 bf16 = 64 packed columns (A operand of P.V)
 constexpr long long kWaitCycles = 2000000000LL;  // about one second
 
+// Abort flag of the CTA and, right behind it, the limit of every bounded wait in SM clock cycles (a
+// launch parameter): a wait site hands over the flag's address and finds the limit next to it.
+struct WaitCtl {
+  int abort_flag;
+  int pad;
+  long long limit;
+};
+
 struct __align__(1024) Smem {
   uint8_t q[BM * 64];               // [128 rows][32 bf16], 64-byte swizzle
   uint8_t k[NSTAGE][BN * 64];       // [128 keys][32 bf16], 64-byte swizzle
@@ -50,7 +58,8 @@ struct __align__(1024) Smem {
   float xmax[2][2][BM];             // row maxima exchanged between the two softmax warpgroups
   float xsum[BM];                   // row sum of the second warpgroup (epilogue)
   uint32_t tmem_base;
-  int abort_flag;
+  uint32_t pad_;
+  WaitCtl ctl;
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -78,11 +87,12 @@ __device__ __forceinline__ bool mbar_try(uint64_t* b, uint32_t parity) {
 // Bounded wait: false when the CTA is aborting (this wait or another one gave up).
 __device__ __forceinline__ bool mbar_wait(uint64_t* b, uint32_t parity, volatile int* abort_flag) {
   if (mbar_try(b, parity)) return true;
+  const long long limit = reinterpret_cast<volatile WaitCtl*>(abort_flag)->limit;
   const long long t0 = clock64();
   for (;;) {
     if (mbar_try(b, parity)) return true;
     if (*abort_flag) return false;
-    if (clock64() - t0 > kWaitCycles) {
+    if (clock64() - t0 > limit) {
       *abort_flag = 1;
       return false;
     }
@@ -174,6 +184,8 @@ struct TcParams {
   float* out;
   float* lse;
   int32_t* status;
+  long long wait_cycles;  // limit of every mbarrier wait, in SM clock cycles
+  int drop_score_commits; // diagnostics only: the MMA thread never signals "scores ready", so the waits run out
 };
 
 // Softmax of this thread's half (64 columns) of one 128 x 128 score tile row.  The two
@@ -286,7 +298,8 @@ ctx_attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       mbar_init(&sm->kv_full[s], 1);
       mbar_init(&sm->kv_empty[s], 1);
     }
-    sm->abort_flag = 0;
+    sm->ctl.abort_flag = 0;
+    sm->ctl.limit = p.wait_cycles;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
@@ -299,7 +312,7 @@ ctx_attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = sm->tmem_base;
-  volatile int* abort_flag = &sm->abort_flag;
+  volatile int* abort_flag = &sm->ctl.abort_flag;
   if (warp != 0) {  // the producer waits after its early K/V prefetch
     dep_wait();
     dep_trigger();
@@ -333,12 +346,12 @@ ctx_attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       if (*abort_flag) {  // drain our own copies before the CTA may exit
         {
           const long long t0 = clock64();
-          while (!mbar_try(&sm->q_full, 0) && clock64() - t0 < kWaitCycles) {
+          while (!mbar_try(&sm->q_full, 0) && clock64() - t0 < p.wait_cycles) {
           }
         }
         for (int j = max(0, issued - NSTAGE); j < issued; ++j) {
           const long long t0 = clock64();
-          while (!mbar_try(&sm->kv_full[j % NSTAGE], (j / NSTAGE) & 1) && clock64() - t0 < kWaitCycles) {
+          while (!mbar_try(&sm->kv_full[j % NSTAGE], (j / NSTAGE) & 1) && clock64() - t0 < p.wait_cycles) {
           }
         }
       }
@@ -360,7 +373,7 @@ ctx_attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         for (int ks = 0; ks < 2; ++ks)
           umma_ss(tmem + kColS, make_desc(q_addr + 32 * ks, 512, kLayoutSw64),
                   make_desc(k_addr + 32 * ks, 512, kLayoutSw64), idesc_qk, ks);
-        umma_commit(&sm->s_full);
+        if (!p.drop_score_commits) umma_commit(&sm->s_full);
         return true;
       };
       ok = ok && issue_qk(0);
@@ -460,7 +473,7 @@ ctx_attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
   }
-  if (threadIdx.x == 0 && sm->abort_flag && p.status) atomicExch(p.status, 1);
+  if (threadIdx.x == 0 && sm->ctl.abort_flag && p.status) atomicExch(p.status, 1);
 }
 
 // ---------------------------------- host side ----------------------------------
@@ -574,6 +587,8 @@ int launch_ctx_attn_tc(const CtxAttnArgs& a, cudaStream_t s) {
   p.out = a.out;
   p.lse = a.lse;
   p.status = a.status;
+  p.wait_cycles = debug_wait_cycles() > 0 ? debug_wait_cycles() : kWaitCycles;
+  p.drop_score_commits = debug_drop_score_commits();
   const int rows_in_group = a.n_groups == 1 ? a.rows : a.rows_per_group;
   dim3 grid((rows_in_group + BM - 1) / BM, a.n_heads, a.n_groups * a.n_splits);
   prof_begin(PROF_CTX, s);

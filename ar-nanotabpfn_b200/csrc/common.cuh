@@ -47,6 +47,10 @@ __device__ __forceinline__ void dep_wait() { asm volatile("griddepcontrol.wait;"
 __device__ __forceinline__ void dep_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 bool dependent_launch_enabled();
+// diagnostics set through artab_debug_set: limit of the bounded waits (0: the built-in second or so) and
+// the switch that makes the context kernel's waits run out (see artab.h)
+long long debug_wait_cycles();
+int debug_drop_score_commits();
 
 // While one of these lives on the calling thread, launch_dependent* issue plain launches.
 struct PlainLaunchScope {

@@ -331,6 +331,19 @@ ARTAB_API int artab_profile_read(double* ms_per_kind, int64_t* launches_per_kind
  * reference. */
 ARTAB_API void artab_set_dependent_launch(int on);
 
+/* Diagnostics of the bounded device-side waits (process-wide, off by default; no counterpart in
+ * the reference).  Every mbarrier wait inside the tensor-core kernels gives up after a limit, the
+ * CTA then writes nothing more, frees what it holds, sets the status word and returns.
+ *   ARTAB_DEBUG_WAIT_CYCLES        value = limit in SM clock cycles for the context contraction's waits
+ *                                  (0 restores the built-in limit of about one second)
+ *   ARTAB_DEBUG_DROP_SCORE_COMMITS value != 0: the context contraction's MMA thread never signals
+ *                                  "scores ready", so its softmax threads' waits run out.  This is how
+ *                                  the tests exercise the give-up path without faulting anything:
+ *                                  the kernel returns normally, status is non-zero, `out` untouched. */
+#define ARTAB_DEBUG_WAIT_CYCLES 0
+#define ARTAB_DEBUG_DROP_SCORE_COMMITS 1
+ARTAB_API int artab_debug_set(int key, long long value);
+
 /* Kernels launched by this library on the calling thread since the last reset
  * (a host-side counter for benchmarks). */
 ARTAB_API int64_t artab_launch_count(void);
