@@ -334,7 +334,8 @@ BufMergeArgs buf_base(const artab_model* m, const artab_state* st, int rows) {
   return b;
 }
 
-int decode_common(const artab_model* m, artab_state* st, int n_new, const DenseArgs& last_proto, cudaStream_t s) {
+int decode_common(const artab_model* m, artab_state* st, int n_new, const DenseArgs& last_proto, bool x_lane_major,
+                  cudaStream_t s) {
   const int rows = st->n_streams * n_new;
   ARTAB_REQUIRE(rows <= st->max_rows, ARTAB_ECAPACITY, "decode: %d rows exceed the workspace (%d)", rows,
                 st->max_rows);
@@ -354,6 +355,7 @@ int decode_common(const artab_model* m, artab_state* st, int n_new, const DenseA
   d0.do_pre = 1;
   d0.pre_w = m->layers[0];
   d0.kv = kv;
+  d0.x_in_lane_major = x_lane_major;
   set_kv(m, st, 0, d0.kv);
   int rc = launch_dense(d0, s);
   if (rc) return rc;
@@ -443,6 +445,7 @@ int artab_prefill(const artab_model* m, artab_state* st, const float* xc, const 
   e.x = xc;
   e.y = yc;
   e.out = st->x;
+  e.out_lane_major = chain_on_tc(m, st);
   rc = launch_embed(e, s);
   if (rc) return rc;
 
@@ -456,6 +459,7 @@ int artab_prefill(const artab_model* m, artab_state* st, const float* xc, const 
   d0.do_pre = 1;
   d0.pre_w = m->layers[0];
   d0.kv = kv;
+  d0.x_in_lane_major = chain_on_tc(m, st);   // written by the embedder above
   set_kv(m, st, 0, d0.kv);
   rc = launch_dense(d0, s);
   if (rc) return rc;
@@ -501,6 +505,7 @@ int artab_decode_step(const artab_model* m, artab_state* st, const float* xt, in
   e.t = t;
   e.n_new = n_new;
   e.out = st->x;
+  e.out_lane_major = chain_on_tc(m, st);
   rc = launch_embed(e, s);
   if (rc) return rc;
   DenseArgs last = dense_base(m, st, rows);
@@ -517,7 +522,7 @@ int artab_decode_step(const artab_model* m, artab_state* st, const float* xt, in
   last.y_out = samples;
   last.ld_out = logdens;
   last.comp_out = comp;
-  rc = decode_common(m, st, n_new, last, s);
+  rc = decode_common(m, st, n_new, last, chain_on_tc(m, st), s);
   if (rc) return rc;
   st->buffer_len += n_new - 1;
   return ARTAB_OK;
@@ -542,7 +547,7 @@ int artab_decode_embedded(const artab_model* m, artab_state* st, const float* x_
   last.do_post = 1;
   last.do_final = 1;
   last.z_out = z_out;
-  rc = decode_common(m, st, n_new, last, s);
+  rc = decode_common(m, st, n_new, last, /*x_lane_major=*/false, s);
   if (rc) return rc;
   st->buffer_len += commit;
   return ARTAB_OK;
@@ -571,6 +576,7 @@ int artab_teacher_forcing(const artab_model* m, artab_state* st, const float* xt
   e.yt = yt;
   e.Nt = Nt;
   e.out = st->x;
+  e.out_lane_major = chain_on_tc(m, st);
   rc = launch_embed(e, s);
   if (rc) return rc;
   KvDest kv;
@@ -586,6 +592,7 @@ int artab_teacher_forcing(const artab_model* m, artab_state* st, const float* xt
   d0.do_pre = 1;
   d0.pre_w = m->layers[0];
   d0.kv = kv;
+  d0.x_in_lane_major = chain_on_tc(m, st);   // written by the embedder above
   set_kv(m, st, 0, d0.kv);
   rc = launch_dense(d0, s);
   if (rc) return rc;
@@ -640,6 +647,7 @@ int artab_forward_masked(const artab_model* m, artab_state* st, const float* xb,
   e.xt = xt;
   e.Nt = n_targets;
   e.out = st->x;
+  e.out_lane_major = chain_on_tc(m, st);
   rc = launch_embed(e, s);
   if (rc) return rc;
   KvDest kv;
@@ -655,6 +663,7 @@ int artab_forward_masked(const artab_model* m, artab_state* st, const float* xb,
   d0.do_pre = 1;
   d0.pre_w = m->layers[0];
   d0.kv = kv;
+  d0.x_in_lane_major = chain_on_tc(m, st);   // written by the embedder above
   set_kv(m, st, 0, d0.kv);
   rc = launch_dense(d0, s);
   if (rc) return rc;

@@ -23,6 +23,7 @@ struct EmbedArgs {
   const float* yb;       // [B][Nb]
   int Nb;
   float* out;            // [rows][D]
+  int out_lane_major;    // write `out` in the lane-major layout the tensor-core chain reads (padded workspace)
 };
 
 struct DenseArgs {
@@ -30,6 +31,7 @@ struct DenseArgs {
   int do_post, do_final, do_head, do_pre;
   artab_layer_weights post_w, pre_w;
   int lane_major;      // tensor-core chain: attn and the x1 workspace use the lane-major layout
+  int x_in_lane_major; // tensor-core chain: x_in was written in that layout too (by the embedder)
   const float* attn;   // [rows][D]  post input
   const float* x1_in;  // [rows][D]  post residual input
   const float* x_in;   // [rows][D]  chain input when !do_post

@@ -509,7 +509,7 @@ __global__ void __launch_bounds__(128) embed_kernel(const EmbedArgs a) {
     if (has_y) e += fmaf(yv, __ldg(a.wy + d), __ldg(a.by + d));
     e += __ldg(a.marker + kind * a.D + d);
     if (ar >= 0) e += __ldg(a.ar_tokens + ar * a.D + d);
-    a.out[(size_t)row * a.D + d] = e;
+    a.out[a.out_lane_major ? lane_major_index(row, d, a.D) : (size_t)row * a.D + d] = e;
   }
 }
 

@@ -108,6 +108,10 @@ __device__ __forceinline__ uint32_t cluster_size() {
   asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r));
   return r;
 }
+// split form: arrive right after the own barriers are initialised, wait only before the first access to
+// the peer's shared memory (by then the peer has arrived long ago, so the wait costs nothing)
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
 __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
@@ -284,7 +288,9 @@ struct __align__(1024) Smem {
   __nv_bfloat16* rowdst[BM];          // private-buffer K slot of each row's token (null: not cached)
   uint64_t w_full[2][NSLOT], w_empty[2][NSLOT];
   uint64_t ep_done, acc_full, h_full, acch_free, ah_ready, ah_free;
-  uint64_t x_full;   // CTA pair: the peer's MLP partial sums have been written to the global scratch
+  uint64_t x_full;   // CTA pair: the peer's partial sums have arrived (MLP: in this CTA's landing zone; head: in the global scratch)
+  uint64_t x_ready;  // CTA pair: the peer's landing zone (its second weight ring + hidden-operand buffers) is idle
+  uint64_t x_done;   // CTA pair: every epilogue thread has read the landing zone: the second weight ring may be refilled
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -643,29 +649,42 @@ struct Epilogue {
     ++free_count;
   }
   // CTA pair: v[i] += (own MLP partial + the peer's).  Each CTA holds the second GEMM's sum over its
-  // half of the hidden tiles in ACC_A.  The partials cross through a global scratch (lane-major like
-  // the other row workspaces, so both directions are coalesced float4 streams that stay in L2): write
-  // own partial, release-arrive on the peer's barrier, acquire-wait on ours, read the peer's.
+  // half of the hidden tiles in ACC_A.  The partials cross through distributed shared memory: once a
+  // CTA's own second GEMM is complete, its second weight ring and hidden-operand buffers are idle
+  // and serve as the landing zone (96 KB, float4 column groups outermost, the 128 rows innermost, so
+  // a warp's stores and loads are contiguous 512-byte spans).  Hand-shake: tell the peer that this
+  // CTA's zone is free, wait for the peer's word, store the own partial into the PEER's zone,
+  // release-arrive on the peer's barrier, acquire-wait on the own one, read the own zone.
   // a + b == b + a exactly, so both CTAs end up with the same bits.  Called after wait_acc().
-  __device__ void exchange_add(float* v, uint32_t peer, float* mine, const float* theirs, size_t lm0) {
+  // Remote arrivals are single transactions on the cluster network, so they are kept few: one per
+  // CTA for "zone free" (the accumulator wait every thread has passed is a CTA-wide event), one per
+  // warp for "partial delivered" (__syncwarp orders the warp's stores before lane 0's release).
+  __device__ void exchange_add(float* v, uint32_t peer) {
+    if (wg == 0 && row == 0) mbar_arrive_remote(map_to_rank(smem_u32(&sm->x_ready), peer));
+    ok = mbar_wait_cluster(&sm->x_ready, 0, &sm->abort_flag) && ok;
+    const uint32_t zone_peer = map_to_rank(smem_u32(&sm->ring[1][0][0]), peer);
     uint32_t r[16];
 #pragma unroll
     for (int c = 0; c < NCH; ++c) {
       tmem_ld16(t_row + kAccA + col0 + 16 * c, r);
       tmem_wait_ld();
 #pragma unroll
-      for (int q = 0; q < 4; ++q)
-        *reinterpret_cast<float4*>(mine + lm0 + (size_t)(4 * c + q) * 128) =
-            make_float4(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]), __uint_as_float(r[4 * q + 2]),
-                        __uint_as_float(r[4 * q + 3]));
+      for (int q = 0; q < 4; ++q) {
+        const uint32_t dst = zone_peer + (uint32_t)((((col0 >> 2) + 4 * c + q) * BM + row) * 16);
+        asm volatile("st.shared::cluster.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(r[4 * q]), "r"(r[4 * q + 1]),
+                     "r"(r[4 * q + 2]), "r"(r[4 * q + 3])
+                     : "memory");
+      }
     }
-    mbar_arrive_remote(map_to_rank(smem_u32(&sm->x_full), peer));  // releases the stores above
+    __syncwarp();
+    if ((threadIdx.x & 31) == 0) mbar_arrive_remote(map_to_rank(smem_u32(&sm->x_full), peer));  // releases the warp's stores
     ok = mbar_wait_cluster(&sm->x_full, 0, &sm->abort_flag) && ok;
+    const float4* zone = reinterpret_cast<const float4*>(&sm->ring[1][0][0]);
 #pragma unroll
     for (int c = 0; c < NCH; ++c) {
       float4 t[4];
 #pragma unroll
-      for (int q = 0; q < 4; ++q) t[q] = __ldcg(reinterpret_cast<const float4*>(theirs + lm0 + (size_t)(4 * c + q) * 128));
+      for (int q = 0; q < 4; ++q) t[q] = zone[((col0 >> 2) + 4 * c + q) * BM + row];
       tmem_ld16(t_row + kAccA + col0 + 16 * c, r);
       tmem_wait_ld();
 #pragma unroll
@@ -676,6 +695,7 @@ struct Epilogue {
         v[16 * c + 4 * q + 3] += __uint_as_float(r[4 * q + 3]) + t[q].w;
       }
     }
+    mbar_arrive(&sm->x_done);  // the values above are in registers: the zone may be overwritten
   }
 };
 
@@ -734,6 +754,12 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const DenseArgs a
   extern __shared__ uint8_t smem_raw[];
   Smem* sm = reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+#ifdef ARTAB_TIMELINE
+  if (threadIdx.x == 64) {
+    g_tl[a.tl_slot & 31][blockIdx.x & 31][29] = gtimer();
+    g_tl[a.tl_slot & 31][blockIdx.x & 31][28] = clock64();
+  }
+#endif
   constexpr int NKC = D / 64;
   constexpr uint32_t kSlab = D * 128;
   const int nt = a.Dff / HT;
@@ -757,7 +783,9 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const DenseArgs a
     mbar_init(&sm->acch_free, kEpi);
     mbar_init(&sm->ah_ready, kEpi);
     mbar_init(&sm->ah_free, 1);
-    mbar_init(&sm->x_full, kEpi);
+    mbar_init(&sm->x_full, kEpi / 32);   // one remote arrival per epilogue warp
+    mbar_init(&sm->x_ready, 1);          // one remote arrival per CTA
+    mbar_init(&sm->x_done, kEpi);
     sm->abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -770,7 +798,11 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const DenseArgs a
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  if (csize > 1) cluster_sync_all();  // the peer's barriers exist before anyone arrives on them
+  // The peer's barriers must exist before anyone arrives on them.  Every thread arrives here; the
+  // epilogue threads wait just before the MLP exchange (the first remote access of a launch), all
+  // other threads, and the epilogue threads of a launch without an exchange, at the end.
+  if (csize > 1) cluster_arrive();
+  bool cluster_waited = false;
   const uint32_t tmem = sm->tmem_base;
 
   const int lo_post = a.post_w.tc_lo, lo_pre = a.pre_w.tc_lo;
@@ -802,6 +834,9 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const DenseArgs a
     if (lane == 0) {
       Producer p{sm, 1, 0, true};
       if (a.do_post) p.mlp_second(a.post_w.tc_w2, lo_post & 4, kSlab, nt, crank, csize);
+      // a pair uses this ring as the landing zone of the MLP exchange: nothing more goes into it
+      // until every epilogue thread has read the zone
+      if (a.do_post && csize > 1 && !mbar_wait(&sm->x_done, 0, &sm->abort_flag)) p.ok = false;
       if (a.do_head) {
         p.mlp_second(a.tc_wb, a.tc_head_lo & 2, 16 * 128, nt, h_first, h_step);
       } else if (a.do_pre) {
@@ -854,7 +889,6 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const DenseArgs a
     e.tl_slot = a.tl_slot;
 #endif
     TL(0);
-    TLG(29);
     e.sm = sm;
     e.row = 32 * (warp & 3) + lane;
     e.wg = (warp - 2) >> 2;
@@ -898,26 +932,44 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const DenseArgs a
         *reinterpret_cast<float4*>(dst + goff + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
     };
 
-    // Small per-column vectors -> shared memory (read by every epilogue thread, many times).  The
-    // loads are issued now and consumed behind the first GEMM: their latency hides under it.
-    for (int i = threadIdx.x - 64; i < D; i += kEpi) {
-      if (a.do_post) {
-        sm->vec[0][i] = a.post_w.ln2_g[i];
-        sm->vec[1][i] = a.post_w.ln2_b[i];
-        sm->vec[2][i] = a.post_w.b2[i];
-        sm->vec[3][i] = a.post_w.ln3_g[i];
-        sm->vec[4][i] = a.post_w.ln3_b[i];
+    // Small per-column vectors -> shared memory (read by every epilogue thread, many times).  All
+    // loads are issued before the first store (read-only path: the compiler may not assume that the
+    // shared-memory stores leave the global vectors alone, and would otherwise wait for every load in
+    // turn); their latency then hides under the first GEMM.
+    {
+      const int i = threadIdx.x - 64;
+      float t[7];
+      float bh[(1024 + kEpi - 1) / kEpi];
+      const bool col = i < D;
+#pragma unroll
+      for (int k = 0; k < 7; ++k) t[k] = 0.f;
+      if (col && a.do_post) {
+        t[0] = __ldg(a.post_w.ln2_g + i);
+        t[1] = __ldg(a.post_w.ln2_b + i);
+        t[2] = __ldg(a.post_w.b2 + i);
+        t[3] = __ldg(a.post_w.ln3_g + i);
+        t[4] = __ldg(a.post_w.ln3_b + i);
       }
-      if (a.do_final) {
-        sm->vec[5][i] = a.lnf_g[i];
-        sm->vec[6][i] = a.lnf_b[i];
-      } else if (a.do_pre) {
-        sm->vec[5][i] = a.pre_w.ln1_g[i];
-        sm->vec[6][i] = a.pre_w.ln1_b[i];
+      if (col && a.do_final) {
+        t[5] = __ldg(a.lnf_g + i);
+        t[6] = __ldg(a.lnf_b + i);
+      } else if (col && a.do_pre) {
+        t[5] = __ldg(a.pre_w.ln1_g + i);
+        t[6] = __ldg(a.pre_w.ln1_b + i);
+      }
+#pragma unroll
+      for (int k = 0; k < (1024 + kEpi - 1) / kEpi; ++k)
+        bh[k] = (a.do_post && i + k * kEpi < a.Dff) ? __ldg(a.post_w.b1 + i + k * kEpi) : 0.f;
+      if (col) {
+#pragma unroll
+        for (int k = 0; k < 7; ++k) sm->vec[k][i] = t[k];
+      }
+      if (a.do_post) {
+#pragma unroll
+        for (int k = 0; k < (1024 + kEpi - 1) / kEpi; ++k)
+          if (i + k * kEpi < a.Dff) sm->bias_h[i + k * kEpi] = bh[k];
       }
     }
-    if (a.do_post)
-      for (int i = threadIdx.x - 64; i < a.Dff; i += kEpi) sm->bias_h[i] = a.post_w.b1[i];
     // Everything above (and the weight producers' first tiles) needed nothing from the preceding
     // kernel; the activations do.
     TL(1);
@@ -933,9 +985,7 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const DenseArgs a
       e.wait_acc();
       TL(4);
       e.sync_groups();                           // the staged vectors are complete
-      TL(27);
       e.add_acc(v);
-      TL(28);
       e.layer_norm(v, sm->vec[0], sm->vec[1]);   // v = x2
       TL(25);
       e.publish_ax(v);
@@ -956,17 +1006,19 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const DenseArgs a
       TL(13);
 #pragma unroll
       for (int i = 0; i < PART; ++i) v[i] += sm->vec[2][e.col0 + i];
-      if (csize > 1)
-        e.exchange_add(v, crank ^ 1u, a.pair_scratch + (size_t)crank * a.pair_slot_stride,
-                       a.pair_scratch + (size_t)(crank ^ 1u) * a.pair_slot_stride, lm0);
-      else
+      if (csize > 1) {
+        cluster_wait();
+        cluster_waited = true;
+        e.exchange_add(v, crank ^ 1u);
+      } else {
         e.add_acc(v);
+      }
       TL(14);
       e.layer_norm(v, sm->vec[3], sm->vec[4]);   // v = x3
       if (a.x_out && crank == 0) store_row(a.x_out);
       TL(15);
     } else {
-      load_row(a.x_in);
+      if (a.x_in_lane_major) load_lm(a.x_in); else load_row(a.x_in);
       e.sync_groups();                           // the staged vectors are complete
     }
     if (a.do_final) {
@@ -977,7 +1029,19 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const DenseArgs a
     if (a.do_head) {
       // the hidden bias buffer now takes the head's first-layer bias (every thread is past the MLP)
       e.sync_groups();
-      for (int i = threadIdx.x - 64; i < a.Dff; i += kEpi) sm->bias_h[i] = a.ba[i];
+      {
+        float bh[(1024 + kEpi - 1) / kEpi];
+#pragma unroll
+        for (int k = 0; k < (1024 + kEpi - 1) / kEpi; ++k) {
+          const int i = threadIdx.x - 64 + k * kEpi;
+          bh[k] = i < a.Dff ? __ldg(a.ba + i) : 0.f;
+        }
+#pragma unroll
+        for (int k = 0; k < (1024 + kEpi - 1) / kEpi; ++k) {
+          const int i = threadIdx.x - 64 + k * kEpi;
+          if (i < a.Dff) sm->bias_h[i] = bh[k];
+        }
+      }
       e.sync_groups();
       e.publish_ax(v);
       {
@@ -998,6 +1062,10 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const DenseArgs a
         tmem_wait_ld();
       }
       if (head_pair) {
+        if (!cluster_waited) {  // a launch whose first remote access is this one
+          cluster_wait();
+          cluster_waited = true;
+        }
         float* mine = a.pair_scratch + (size_t)(2 + crank) * a.pair_slot_stride + (size_t)grow * 16;
         const float* theirs = a.pair_scratch + (size_t)(2 + (crank ^ 1u)) * a.pair_slot_stride + (size_t)grow * 16;
         if (e.wg == 0) {
@@ -1005,7 +1073,8 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const DenseArgs a
           for (int q = 0; q < 4; ++q)
             reinterpret_cast<uint4*>(mine)[q] = make_uint4(r[4 * q], r[4 * q + 1], r[4 * q + 2], r[4 * q + 3]);
         }
-        mbar_arrive_remote(map_to_rank(smem_u32(&sm->x_full), crank ^ 1u));
+        __syncwarp();
+        if (lane == 0) mbar_arrive_remote(map_to_rank(smem_u32(&sm->x_full), crank ^ 1u));
         e.ok = mbar_wait_cluster(&sm->x_full, a.do_post ? 1 : 0, &sm->abort_flag) && e.ok;
         if (e.wg == 0) {
 #pragma unroll
@@ -1062,7 +1131,10 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const DenseArgs a
       // (conflict-free 16-byte accesses), in the hidden-operand buffer, which is idle in this phase.
       constexpr int kStageRow = D * 2 + 16;
       uint8_t* stage = &sm->ah[0][0][0];
-      const bool direct = a.kv.mode == KV_PREFILL;   // context cache: direct stores are already coalesced
+      // K / V go straight from registers to the cache during prefill (context cache: a row's store is
+      // already a coalesced span) and in a decode step (one buffer row per stream: 16-byte pieces that
+      // no staging could merge); teacher forcing stages them (consecutive positions of a stream)
+      const bool direct = a.kv.mode == KV_PREFILL || a.kv.mode == KV_DECODE;
       const int tid_e = threadIdx.x - 64;
       for (int t = t_begin; t < t_end; ++t) {
         e.wait_acc();
@@ -1129,6 +1201,17 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const DenseArgs a
                     pack_bf16(__uint_as_float(r[c][8 * i + 4]), __uint_as_float(r[c][8 * i + 5])),
                     pack_bf16(__uint_as_float(r[c][8 * i + 6]), __uint_as_float(r[c][8 * i + 7])));
               }
+            } else if (t == 2 && v_dst) {
+#pragma unroll
+              for (int i = 0; i < 2; ++i) {
+                const int col = cbase + 8 * i;
+                const int h = col >> dh_shift, d = col & (Dh - 1);
+                *reinterpret_cast<uint4*>(v_dst + (size_t)h * k_hstride + d) = make_uint4(
+                    pack_bf16(__uint_as_float(r[c][8 * i]), __uint_as_float(r[c][8 * i + 1])),
+                    pack_bf16(__uint_as_float(r[c][8 * i + 2]), __uint_as_float(r[c][8 * i + 3])),
+                    pack_bf16(__uint_as_float(r[c][8 * i + 4]), __uint_as_float(r[c][8 * i + 5])),
+                    pack_bf16(__uint_as_float(r[c][8 * i + 6]), __uint_as_float(r[c][8 * i + 7])));
+              }
             } else if (t == 2 && vt_dst) {
 #pragma unroll
               for (int i = 0; i < 16; ++i) {
@@ -1156,7 +1239,10 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const DenseArgs a
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
   }
-  if (csize > 1) cluster_sync_all();  // neither CTA leaves while the other could still address its shared memory
+  if (csize > 1) {
+    if (!cluster_waited) cluster_wait();
+    cluster_sync_all();  // neither CTA leaves while the other could still address its shared memory
+  }
 }
 
 }  // namespace

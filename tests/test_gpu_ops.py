@@ -169,6 +169,54 @@ def test_embedder_and_head_vs_oracle():
     assert not torch.equal(y3[:, :, 0], y3[:, :, 1])
 
 
+def test_config2_against_the_reference_triton_kernel(tk):
+    """The same configuration against the reference's OWN kernels on identical bf16 tensors: its Triton
+    shared-context kernel (triton_context_attention) and its hybrid_attention (Triton context pass +
+    eager buffer pass + merge).  Needs the unmodified reference package under baseline/_ref and a
+    working Triton; skipped with the reason otherwise."""
+    from util import reference_kernels
+    ref = reference_kernels()
+    if ref is None:
+        pytest.skip("the reference package is not installed under baseline/_ref")
+    if not getattr(ref, "HAS_TRITON", False):
+        pytest.skip("the reference found no Triton on this box")
+    g = torch.Generator().manual_seed(1)
+    B, H, Dh, Nc, Nb = 1024, 4, 32, 4096, 63
+    rn = lambda *s: torch.randn(*s, generator=g).to(torch.bfloat16)
+    q, k, v = cu(rn(B, H, 1, Dh)), cu(rn(H, Nc, Dh)), cu(rn(H, Nc, Dh))
+    kb, vb = cu(rn(B, H, Nb, Dh)), cu(rn(B, H, Nb, Dh))
+    lens = torch.randint(0, Nb + 1, (B,), generator=g)
+    mask = cu((torch.arange(Nb)[None, :] < lens[:, None])[:, None, None, :])
+    try:
+        want_c, want_l = ref.triton_context_attention(q, k, v)
+        want_h = ref.hybrid_attention(q, k, v, kb, vb, buf_mask=mask)
+        torch.cuda.synchronize()
+    except Exception as e:  # noqa: BLE001
+        pytest.skip(f"the reference's Triton kernel did not run here: {type(e).__name__}: {e}"[:300])
+    got_c, got_l = tk.triton_context_attention(q, k, v)
+    got_h = tk.hybrid_attention(q, k, v, kb, vb, buf_mask=mask)
+    assert got_c.dtype == want_c.dtype and got_c.shape == want_c.shape and got_l.shape == want_l.shape
+    # exact (fp32) attention on the same bf16 tensors: the common yardstick of both implementations
+    kc, vc = k.float().unsqueeze(0).expand(B, -1, -1, -1), v.float().unsqueeze(0).expand(B, -1, -1, -1)
+    true_c, true_l = ref_attention(q, kc, vc)
+    full = torch.cat([torch.ones(B, 1, 1, Nc, dtype=torch.bool, device=q.device), mask], dim=-1)
+    true_h, _ = ref_attention(q, torch.cat([kc, kb.float()], dim=2), torch.cat([vc, vb.float()], dim=2), mask=full)
+    rel = lambda a, b: float(((a.float() - b.float()).norm(dim=-1) / b.float().norm(dim=-1).clamp_min(1e-6)).max())
+    info = dict(ctx_ours_vs_ref=rel(got_c, want_c), ctx_ours_vs_exact=rel(got_c, true_c), ctx_ref_vs_exact=rel(want_c, true_c),
+                hybrid_ours_vs_ref=rel(got_h, want_h), hybrid_ours_vs_exact=rel(got_h, true_h),
+                hybrid_ref_vs_exact=rel(want_h, true_h),
+                lse_ours_vs_ref=float((got_l - want_l).abs().max()), lse_ours_vs_exact=float((got_l - true_l).abs().max()),
+                lse_ref_vs_exact=float((want_l - true_l).abs().max()))
+    print("against the reference Triton path:", info)
+    # 1e-2 relative against the exact result and against the reference's own kernel; where the
+    # reference itself (bf16 outputs, eager bf16 buffer pass) sits further than that from the exact
+    # result, its own distance is what separates the two
+    assert info["ctx_ours_vs_exact"] <= 1e-2 and info["hybrid_ours_vs_exact"] <= 1e-2, info
+    assert info["ctx_ours_vs_ref"] <= 1e-2, info
+    assert info["hybrid_ours_vs_ref"] <= 1e-2 + info["hybrid_ref_vs_exact"], info
+    assert info["lse_ours_vs_exact"] <= 2e-3 and info["lse_ours_vs_ref"] <= 2e-3 + info["lse_ref_vs_exact"], info
+
+
 def test_ragged_buffers_fp32_golden(tk):
     """Per-stream buffer lengths (0 .. Nb) through pytorch_buffer_attention's mask and
     hybrid_attention's buf_mask, against the reference's outputs; head sizes 16 / 32 / 64."""

@@ -29,3 +29,23 @@ def ref_attention(q, k, v, mask=None):
     if mask is not None:
         s = s.masked_fill(~mask, float("-inf"))
     return torch.matmul(torch.softmax(s, dim=-1), v.float()), torch.logsumexp(s, dim=-1)
+
+
+def reference_kernels():
+    """The reference's own ``ar_tabpfn.model.triton_kernels`` module, when the unmodified reference
+    package is installed under ``baseline/_ref`` (imported under the alias ``ref_ar_tabpfn`` so that it
+    cannot collide with the shipped package of the same name); None otherwise."""
+    import importlib
+    import sys
+    import types
+    root = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "baseline", "_ref", "ar_tabpfn")
+    if not os.path.isdir(root):
+        return None
+    if "ref_ar_tabpfn" not in sys.modules:
+        pkg = types.ModuleType("ref_ar_tabpfn")
+        pkg.__path__ = [root]
+        sys.modules["ref_ar_tabpfn"] = pkg
+    try:
+        return importlib.import_module("ref_ar_tabpfn.model.triton_kernels")
+    except Exception:  # noqa: BLE001  (a foreign package that does not import is the same as an absent one)
+        return None
