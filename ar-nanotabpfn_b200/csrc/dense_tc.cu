@@ -159,6 +159,10 @@ __device__ __forceinline__ void umma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
                : "memory");
 }
+__device__ __forceinline__ void umma_commit_addr(uint32_t cluster_addr) {  // a barrier of any CTA of the cluster
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_addr)
+               : "memory");
+}
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* r) {
@@ -381,26 +385,9 @@ struct Issuer {
     ++ep_phase;
     tc_fence_after();
   }
-  // ACC[acc_col] = A_x . W^T with W streamed as `nkc` slabs of [n_out rows][64 k]
-  __device__ void gemm_full_ts(uint32_t acc_col, int n_out, int nkc, bool has_lo) {
-    const uint32_t idesc = make_idesc(n_out);
-    const uint32_t acc = tmem + acc_col;
-    uint32_t ahi = tmem + kAxHi, alo = tmem + kAxLo;
-    for (int kc = 0; kc < nkc; ++kc, ahi += 32, alo += 32) {
-      const uint64_t bd = make_desc(slab_wait());
-#pragma unroll
-      for (int ks = 0; ks < 4; ++ks) umma_ts(acc, ahi + ks * 8, desc_step(bd, 32 * ks), idesc, (kc | ks) != 0);
-#pragma unroll
-      for (int ks = 0; ks < 4; ++ks) umma_ts(acc, alo + ks * 8, desc_step(bd, 32 * ks), idesc, 1);
-      slab_release();
-      if (has_lo) {
-        const uint64_t ld = make_desc(slab_wait());
-#pragma unroll
-        for (int ks = 0; ks < 4; ++ks) umma_ts(acc, ahi + ks * 8, desc_step(ld, 32 * ks), idesc, 1);
-        slab_release();
-      }
-    }
-  }
+  // ACC[acc_col] = A_x . W^T with W streamed as `nkc` slabs of [n_out rows][64 k].
+  // One out-of-line copy serves every call site (see gemm_full_ts_shared below).
+  __device__ void gemm_full_ts(uint32_t acc_col, int n_out, int nkc, bool has_lo, long long* stamp = nullptr);
   // ACC_H (128 columns) = A_x . W_tile^T; the tile arrives as nkc slabs of [128 rows][64 k] per part,
   // ordered hi part (all k-chunks) then lo part
   __device__ void gemm_tile_ts(int nkc, bool has_lo) {
@@ -475,6 +462,51 @@ struct Issuer {
     tc_fence_after();
   }
 };
+
+// The issuing thread walks this code alone: every inlined copy of it would be a stretch of cold
+// instructions (thousands of cycles of fetch stalls per GEMM were measured with one copy per call
+// site).  So there is ONE copy, entered with everything in registers; it returns the new ring count,
+// or -1 - count when a wait gave up.
+__device__ __noinline__ int gemm_full_ts_shared(Smem* sm, uint32_t tmem, int ring, int consumed, uint32_t acc_col,
+                                                int n_out, int nkc, int has_lo, long long* stamp) {
+  const uint32_t idesc = make_idesc(n_out);
+  const uint32_t acc = tmem + acc_col;
+  uint32_t ahi = tmem + kAxHi, alo = tmem + kAxLo;
+  bool ok = true;
+  for (int kc = 0; kc < nkc; ++kc, ahi += 32, alo += 32) {
+    int buf = consumed % NSLOT;
+    ok = ok && mbar_wait(&sm->w_full[ring][buf], (consumed / NSLOT) & 1, &sm->abort_flag);
+    tc_fence_after();
+    if (stamp && kc == 0) stamp[0] = clock64();
+    const uint64_t bd = make_desc(smem_u32(sm->ring[ring][buf]));
+#pragma unroll
+    for (int ks = 0; ks < 4; ++ks) umma_ts(acc, ahi + ks * 8, desc_step(bd, 32 * ks), idesc, (kc | ks) != 0);
+#pragma unroll
+    for (int ks = 0; ks < 4; ++ks) umma_ts(acc, alo + ks * 8, desc_step(bd, 32 * ks), idesc, 1);
+    umma_commit(&sm->w_empty[ring][buf]);
+    ++consumed;
+    if (has_lo) {
+      buf = consumed % NSLOT;
+      ok = ok && mbar_wait(&sm->w_full[ring][buf], (consumed / NSLOT) & 1, &sm->abort_flag);
+      tc_fence_after();
+      const uint64_t ld = make_desc(smem_u32(sm->ring[ring][buf]));
+#pragma unroll
+      for (int ks = 0; ks < 4; ++ks) umma_ts(acc, ahi + ks * 8, desc_step(ld, 32 * ks), idesc, 1);
+      umma_commit(&sm->w_empty[ring][buf]);
+      ++consumed;
+    }
+  }
+  return ok ? consumed : -1 - consumed;
+}
+__device__ __forceinline__ void Issuer::gemm_full_ts(uint32_t acc_col, int n_out, int nkc, bool has_lo, long long* stamp) {
+  const int r = gemm_full_ts_shared(sm, tmem, ring, consumed, acc_col, n_out, nkc, has_lo ? 1 : 0, stamp);
+  if (r < 0) {
+    ok = false;
+    consumed = -1 - r;
+  } else {
+    consumed = r;
+  }
+}
 
 // ------------------------------------------------------------------ epilogue
 template <int D>
@@ -598,9 +630,6 @@ struct Epilogue {
     ok = mbar_wait(&sm->h_full, h_count & 1, &sm->abort_flag) && ok;
     ++h_count;
     tc_fence_after();
-#ifdef ARTAB_TIMELINE
-    if (jl == 1 && threadIdx.x == 64) g_tl[tl_slot & 31][blockIdx.x & 31][10] = clock64();
-#endif
     uint32_t r[2][16];
 #pragma unroll
     for (int c = 0; c < 2; ++c) tmem_ld16(t_row + kAccH + HPART * wg + 16 * c, r[c]);
@@ -618,16 +647,11 @@ struct Epilogue {
       split2(g0.x, g0.y, hi[i], lo[i]);
       split2(g1.x, g1.y, hi[i + 1], lo[i + 1]);
     }
-#ifdef ARTAB_TIMELINE
-    if (jl == 1 && threadIdx.x == 64) g_tl[tl_slot & 31][blockIdx.x & 31][11] = clock64();
-#endif
     if (jl >= 1) {  // the previous tile's second GEMM must have finished reading the operand buffer
       ok = mbar_wait(&sm->ah_free, free_count & 1, &sm->abort_flag) && ok;
       ++free_count;
     }
-#ifdef ARTAB_TIMELINE
-    if (jl == 1 && threadIdx.x == 64) g_tl[tl_slot & 31][blockIdx.x & 31][12] = clock64();
-#endif
+
     // this thread's 32 hidden columns sit in k-chunk wg / 2, 16-byte chunks 4 * (wg % 2) .. + 3 of the
     // 128-byte row; chunk c of row r lives at chunk position c ^ (r % 8)
     uint8_t* base_hi = sm->ah[0][wg >> 1] + row * 128;
@@ -656,12 +680,20 @@ struct Epilogue {
   // CTA's zone is free, wait for the peer's word, store the own partial into the PEER's zone,
   // release-arrive on the peer's barrier, acquire-wait on the own one, read the own zone.
   // a + b == b + a exactly, so both CTAs end up with the same bits.  Called after wait_acc().
-  // Remote arrivals are single transactions on the cluster network, so they are kept few: one per
-  // CTA for "zone free" (the accumulator wait every thread has passed is a CTA-wide event), one per
-  // warp for "partial delivered" (__syncwarp orders the warp's stores before lane 0's release).
-  __device__ void exchange_add(float* v, uint32_t peer) {
-    if (wg == 0 && row == 0) mbar_arrive_remote(map_to_rank(smem_u32(&sm->x_ready), peer));
-    ok = mbar_wait_cluster(&sm->x_ready, 0, &sm->abort_flag) && ok;
+  // Remote arrivals are single transactions on the cluster network, so they are kept few: "zone free"
+  // is ONE arrival, made by the tensor core itself (the second issuer commits its last MMAs of the MLP
+  // onto the PEER's barrier), "partial delivered" is one arrival per warp (__syncwarp orders the
+  // warp's stores before lane 0's release).  The exchange is split in two so that the caller can put
+  // independent work (reading the residual back, adding the bias) between sending and receiving.
+#ifdef ARTAB_TIMELINE
+#define XTL(id) do { if (threadIdx.x == 64) g_tl[tl_slot & 31][blockIdx.x & 31][id] = clock64(); } while (0)
+#else
+#define XTL(id) do { } while (0)
+#endif
+  __device__ void send_partial(uint32_t peer) {
+    XTL(10);
+    ok = mbar_wait_cluster(&sm->x_ready, 0, &sm->abort_flag) && ok;   // the peer's zone is idle
+    XTL(11);
     const uint32_t zone_peer = map_to_rank(smem_u32(&sm->ring[1][0][0]), peer);
     uint32_t r[16];
 #pragma unroll
@@ -676,10 +708,15 @@ struct Epilogue {
                      : "memory");
       }
     }
+    XTL(12);
     __syncwarp();
     if ((threadIdx.x & 31) == 0) mbar_arrive_remote(map_to_rank(smem_u32(&sm->x_full), peer));  // releases the warp's stores
+  }
+  __device__ void receive_add(float* v) {
     ok = mbar_wait_cluster(&sm->x_full, 0, &sm->abort_flag) && ok;
+    XTL(19);
     const float4* zone = reinterpret_cast<const float4*>(&sm->ring[1][0][0]);
+    uint32_t r[16];
 #pragma unroll
     for (int c = 0; c < NCH; ++c) {
       float4 t[4];
@@ -824,9 +861,10 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const DenseArgs a
         p.mlp_first(a.tc_wa, a.tc_head_lo & 1, NKC, nt, h_first, h_step);
       } else if (a.do_pre) {
         p.matrix(a.pre_w.tc_wf, NKC, lo_pre & 8, kSlab);
-        // this CTA's projections alternate between the two rings (the second ring is idle once the
-        // MLP is over), so the next projection's weights are resident before its MMAs can start
-        for (int t = t_begin; t < t_end; t += 2) p.matrix_range(a.pre_w.tc_wqkv, t * NKC, (t + 1) * NKC, lo_pre & 16, kSlab);
+        // this CTA's projections alternate between the two rings, the first one in the SECOND ring:
+        // that ring is idle once the MLP is over, so these weights are resident long before x1 is
+        // published, while this ring is still busy with the folded feature-attention matrix
+        for (int t = t_begin + 1; t < t_end; t += 2) p.matrix_range(a.pre_w.tc_wqkv, t * NKC, (t + 1) * NKC, lo_pre & 16, kSlab);
       }
     }
   } else if (warp == 19) {
@@ -840,7 +878,7 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const DenseArgs a
       if (a.do_head) {
         p.mlp_second(a.tc_wb, a.tc_head_lo & 2, 16 * 128, nt, h_first, h_step);
       } else if (a.do_pre) {
-        for (int t = t_begin + 1; t < t_end; t += 2) p.matrix_range(a.pre_w.tc_wqkv, t * NKC, (t + 1) * NKC, lo_pre & 16, kSlab);
+        for (int t = t_begin; t < t_end; t += 2) p.matrix_range(a.pre_w.tc_wqkv, t * NKC, (t + 1) * NKC, lo_pre & 16, kSlab);
       }
     }
   } else if (warp == 1) {
@@ -862,22 +900,44 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const DenseArgs a
         m.gemm_full_ts(kAccA, D, NKC, lo_pre & 8);
         umma_commit(&sm->acc_full);
         m.wait_epilogue();                               // A_x = x1
-        // second ring, continued where the second issuer left it (the MLP's second GEMM of this launch)
+#ifdef ARTAB_TIMELINE
+        g_tl[a.tl_slot & 31][blockIdx.x & 31][27] = clock64();
+#endif
+        // second ring, continued where the second issuer left it (the MLP's second GEMM of this launch).
+        // Both issuer states are used by name, never through a reference chosen at run time: that
+        // would push them out of registers into the thread's stack, whose first touch is a cold miss.
         Issuer mb{sm, tmem, 1, a.do_post ? n_mine * 2 * ((lo_post & 4) ? 2 : 1) : 0, 0, 0, 0, true};
         for (int t = t_begin; t < t_end; ++t) {
           if (t > t_begin) m.wait_epilogue();            // previous projection drained from ACC_A
-          Issuer& g = ((t - t_begin) & 1) ? mb : m;
-          g.ok = g.ok && m.ok;
-          g.gemm_full_ts(kAccA, D, NKC, lo_pre & 16);
+          if (((t - t_begin) & 1) == 0) {
+            mb.ok = mb.ok && m.ok;
+            mb.gemm_full_ts(kAccA, D, NKC, lo_pre & 16);
+#ifdef ARTAB_TIMELINE
+            if (t == t_begin) g_tl[a.tl_slot & 31][blockIdx.x & 31][28] = clock64();
+#endif
+          } else {
+            m.ok = m.ok && mb.ok;
+            m.gemm_full_ts(kAccA, D, NKC, lo_pre & 16);
+          }
           umma_commit(&sm->acc_full);
         }
       }
     }
   } else if (warp == 18) {
     // --------------------------------- MMA issuer B ---------------------------------
+    if (csize > 1 && a.do_post) {  // whole warp: this thread will arrive on the peer's barrier
+      cluster_wait();
+      cluster_waited = true;
+    }
     if (lane == 0) {
       Issuer m{sm, tmem, 1, 0, 0, 0, 0, true};
-      if (a.do_post) m.mlp_second(lo_post & 4, n_mine, D);
+      if (a.do_post) {
+        m.mlp_second(lo_post & 4, n_mine, D);
+        // this CTA's second GEMM is complete once these MMAs are: its second weight ring and hidden
+        // operand buffers are then free to receive the peer's partial sums, and the peer is told so
+        // by the tensor core itself
+        if (csize > 1) umma_commit_addr(map_to_rank(smem_u32(&sm->x_ready), crank ^ 1u));
+      }
       if (a.do_head) m.mlp_second(a.tc_head_lo & 2, h_mine, 16);
     }
   } else {
@@ -981,6 +1041,10 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const DenseArgs a
       load_lm(a.attn);
       e.publish_ax(v);
       TL(3);
+      if (csize > 1) {  // free here (the first GEMM runs): the peer's barriers are known to exist from now on
+        cluster_wait();
+        cluster_waited = true;
+      }
       load_lm(a.x1_in);                          // residual
       e.wait_acc();
       TL(4);
@@ -1000,19 +1064,20 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const DenseArgs a
           TL(7 + (jl < 5 ? jl : 5));
         }
       }
-      e.load_ax(v);
       e.wait_acc();
       e.drain_free();
       TL(13);
+      if (csize > 1) e.send_partial(crank ^ 1u);   // the own partial sums travel while the lines below run
+      e.load_ax(v);
 #pragma unroll
-      for (int i = 0; i < PART; ++i) v[i] += sm->vec[2][e.col0 + i];
-      if (csize > 1) {
-        cluster_wait();
-        cluster_waited = true;
-        e.exchange_add(v, crank ^ 1u);
-      } else {
-        e.add_acc(v);
+      for (int i = 0; i < PART; i += 4) {
+        const float4 b = *reinterpret_cast<const float4*>(&sm->vec[2][e.col0 + i]);
+        v[i] += b.x; v[i + 1] += b.y; v[i + 2] += b.z; v[i + 3] += b.w;
       }
+      if (csize > 1)
+        e.receive_add(v);
+      else
+        e.add_acc(v);
       TL(14);
       e.layer_norm(v, sm->vec[3], sm->vec[4]);   // v = x3
       if (a.x_out && crank == 0) store_row(a.x_out);
@@ -1098,10 +1163,9 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const DenseArgs a
       TL(17);
       e.add_acc(v);
       e.layer_norm(v, sm->vec[5], sm->vec[6]);     // v = x1
-      e.publish_ax(v);       // the Q projection's MMAs start on this ...
+      e.publish_ax(v);       // the Q projection's MMAs start on this
       TL(18);
       store_lm(a.x1_out);    // ... while the residual for the next launch drains to memory
-      TL(19);
       // q, k, v projections, one accumulator round each.  Destinations of this row's K / V are
       // resolved once (no per-element division): context cache rows during prefill, the private
       // buffer slot (in-place append) otherwise.
