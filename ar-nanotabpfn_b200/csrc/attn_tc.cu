@@ -188,12 +188,35 @@ struct TcParams {
   int drop_score_commits; // diagnostics only: the MMA thread never signals "scores ready", so the waits run out
 };
 
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t* r) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,"
+      "%30,%31,%32};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+        "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]),
+        "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]),
+        "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+
+// How far (in log2 units) a row's running reference may lag behind its true maximum before the
+// accumulated output is rescaled: exponentials then stay below 2^8, far inside bf16 / fp32 range.
+constexpr float kLazyMax = 8.0f;
+
 // Softmax of this thread's half (64 columns) of one 128 x 128 score tile row.  The two
 // softmax warpgroups own columns [0,64) and [64,128) of the same rows and exchange their row
 // maxima through shared memory.  MASKED: columns >= n_valid are -inf.
+//
+// O accumulates in tensor memory across the key tiles (the P.V MMAs run with the accumulate flag), so
+// no thread folds it tile by tile.  The exponentials are taken against a reference m that is only
+// raised when a tile's maximum exceeds it by more than kLazyMax; then O is rescaled in place (each
+// warpgroup its half of the 64 output columns: one tcgen05.ld / st round trip), which on ordinary
+// data happens on the first tiles only.  The result does not depend on when m is raised: the final
+// O / l and lse = m + log2(l) are exact in m.
 template <bool MASKED>
 __device__ __forceinline__ bool softmax_tile(Smem* sm, uint32_t t_row, int wg, int row, int parity, float sc,
-                                             int n_valid, float& m, float& l, float& alpha, bool first,
+                                             int n_valid, float& m, float& l, bool first,
                                              volatile int* abort_flag) {
   uint32_t r[32];
   float mx = -INFINITY;
@@ -211,9 +234,11 @@ __device__ __forceinline__ bool softmax_tile(Smem* sm, uint32_t t_row, int wg, i
   }
   sm->xmax[parity][wg][row] = mx;
   asm volatile("bar.sync 2, 256;" ::: "memory");  // the two softmax warpgroups only
-  mx = fmaxf(mx, sm->xmax[parity][wg ^ 1][row]);
-  const float m_new = fmaxf(m, mx * sc);  // column 0 of every tile is valid, so mx is finite
-  alpha = ex2_approx(m - m_new);          // m = -inf on the first tile gives 0
+  mx = fmaxf(mx, sm->xmax[parity][wg ^ 1][row]) * sc;  // column 0 of every tile is valid, so mx is finite
+  // both warpgroups see the same mx for the row and take the same decision
+  const bool raise = first || mx > m + kLazyMax;
+  const float alpha = raise ? ex2_approx(m - mx) : 1.0f;   // m = -inf on the first tile gives 0
+  if (raise) m = mx;
   bool ok = true;
   float sum = 0.f;
 #pragma unroll 1
@@ -227,8 +252,8 @@ __device__ __forceinline__ bool softmax_tile(Smem* sm, uint32_t t_row, int wg, i
     uint32_t pk[16];
 #pragma unroll
     for (int i = 0; i < 32; i += 2) {
-      float p0 = ex2_approx(fmaf(__uint_as_float(r[i]), sc, -m_new));
-      float p1 = ex2_approx(fmaf(__uint_as_float(r[i + 1]), sc, -m_new));
+      float p0 = ex2_approx(fmaf(__uint_as_float(r[i]), sc, -m));
+      float p1 = ex2_approx(fmaf(__uint_as_float(r[i + 1]), sc, -m));
       if (MASKED) {
         if (col0 + 32 * c + i >= n_valid) p0 = 0.f;
         if (col0 + 32 * c + i + 1 >= n_valid) p1 = 0.f;
@@ -237,16 +262,23 @@ __device__ __forceinline__ bool softmax_tile(Smem* sm, uint32_t t_row, int wg, i
       pk[i >> 1] = pack_bf16(p0, p1);
     }
     // This tile's scores were computed while the previous tile's P . V may still be running: P has
-    // one buffer, so it is rewritten only once that MMA has completed (the maxima and the first
-    // half of the exponentials above overlapped it).
+    // one buffer and O one accumulator, so both are touched only once that MMA has completed (the
+    // maxima and the first half of the exponentials above overlapped it).
     if (c == 0 && !first) {
       ok = mbar_wait(&sm->o_full, parity ^ 1, abort_flag);
       tc_fence_after();
+      if (__any_sync(0xffffffffu, raise)) {  // rare: rescale this warpgroup's half of the accumulated O
+        uint32_t o[32];
+        tmem_ld32(t_row + kColO + 32 * wg, o);
+        tmem_wait_ld();
+#pragma unroll
+        for (int d = 0; d < 32; ++d) o[d] = __float_as_uint(__uint_as_float(o[d]) * alpha);
+        tmem_st32(t_row + kColO + 32 * wg, o);
+      }
     }
     tmem_st16(t_row + kColP + 32 * wg + 16 * c, pk);
   }
   l = l * alpha + sum;
-  m = m_new;
   return ok;
 }
 
@@ -395,7 +427,7 @@ ctx_attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks) {
           const uint32_t v_addr = smem_u32(sm->v[st][ks >> 2]) + 32 * (ks & 3);
-          umma_ts(tmem + kColO, tmem + kColP + 8 * ks, make_desc(v_addr, 1024, kLayoutSw128), idesc_pv, ks);
+          umma_ts(tmem + kColO, tmem + kColP + 8 * ks, make_desc(v_addr, 1024, kLayoutSw128), idesc_pv, (j | ks) != 0);
         }
         umma_commit(&sm->o_full);
         umma_commit(&sm->kv_empty[st]);
@@ -405,10 +437,7 @@ ctx_attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     // --------------------------------- softmax ---------------------------------
     const uint32_t t_row = tmem + ((uint32_t)lane_base << 16);
     const float sc = p.scale_log2e;
-    float m = -INFINITY, l = 0.f, alpha = 0.f;
-    float o[DH];
-#pragma unroll
-    for (int d = 0; d < DH; ++d) o[d] = 0.f;
+    float m = -INFINITY, l = 0.f;
     uint32_t r[32];
     bool ok = true;
     // On an abort the loop still runs every iteration (waits return at once, results are void):
@@ -418,23 +447,9 @@ ctx_attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       tc_fence_after();
       const int n_valid = p.n_ctx - (tile_begin + j) * BN;
       if (n_valid >= BN)
-        ok = softmax_tile<false>(sm, t_row, wg, row, j & 1, sc, BN, m, l, alpha, j == 0, abort_flag) && ok;
+        ok = softmax_tile<false>(sm, t_row, wg, row, j & 1, sc, BN, m, l, j == 0, abort_flag) && ok;
       else
-        ok = softmax_tile<true>(sm, t_row, wg, row, j & 1, sc, n_valid, m, l, alpha, j == 0, abort_flag) && ok;
-      // warpgroup 0 folds the previous tile's O (its MMA completed before this tile's S) and
-      // rescales; the read must precede the arrival below, which lets the next P.V overwrite O
-      if (wg == 0 && j > 0) {
-        // (o_full of tile j - 1 was awaited inside softmax_tile)
-#pragma unroll 1
-        for (int hl = 0; hl < 2; ++hl) {  // hi and lo halves of V
-          tmem_ld32(t_row + kColO + 32 * hl, r);
-          tmem_wait_ld();
-#pragma unroll
-          for (int d = 0; d < DH; ++d) o[d] += __uint_as_float(r[d]);
-        }
-#pragma unroll
-        for (int d = 0; d < DH; ++d) o[d] *= alpha;
-      }
+        ok = softmax_tile<true>(sm, t_row, wg, row, j & 1, sc, n_valid, m, l, j == 0, abort_flag) && ok;
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(&sm->p_full);
@@ -446,13 +461,15 @@ ctx_attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       if (ok) ok = mbar_wait(&sm->o_full, (nt - 1) & 1, abort_flag);
       if (ok) {
         tc_fence_after();
-#pragma unroll 1
-        for (int hl = 0; hl < 2; ++hl) {
-          tmem_ld32(t_row + kColO + 32 * hl, r);
-          tmem_wait_ld();
+        float o[DH];
+        tmem_ld32(t_row + kColO, r);          // P . V_hi
+        tmem_wait_ld();
 #pragma unroll
-          for (int d = 0; d < DH; ++d) o[d] += __uint_as_float(r[d]);
-        }
+        for (int d = 0; d < DH; ++d) o[d] = __uint_as_float(r[d]);
+        tmem_ld32(t_row + kColO + 32, r);     // P . V_lo
+        tmem_wait_ld();
+#pragma unroll
+        for (int d = 0; d < DH; ++d) o[d] += __uint_as_float(r[d]);
         if (row_valid) {
           const float inv = 1.0f / l;
 #pragma unroll

@@ -50,7 +50,7 @@ NC, NT, STREAMS, SEED = syn.CONFIG3["n_ctx"], syn.CONFIG3["n_targets"], syn.CONF
 # DRAM bytes (read + write) of one 1024-row decode-step launch of the tensor-core dense chain: a constant
 # taken from one ncu capture of that kernel (dram__bytes_read.sum + dram__bytes_write.sum), not measured
 # in this run; the weight tiles dominate it
-DENSE_TC_DRAM_BYTES_PER_LAUNCH = 3.657e6
+DENSE_TC_DRAM_BYTES_PER_LAUNCH = 3.68e6
 CPU_SAMPLE = dict(streams=128, targets=16)  # bounded CPU sample of the same workload
 WORKLOAD_CONFIG = {"workload": "config3: 6L d192 h6 ff768, ctx 1024x20, 128 targets, 512 streams/GPU, "
                                "shared context KV, prefill included in every step",
