@@ -9,6 +9,7 @@ flex BlockMasks; ``ARTabPFN.forward`` takes them.
 """
 from __future__ import annotations
 
+import torch
 from torch import nn
 
 
@@ -23,10 +24,32 @@ class MultiheadAttention(nn.Module):
         self.v_proj = nn.Linear(d_model, d_model, bias=False)
         self.out_proj = nn.Linear(d_model, d_model, bias=False)
 
-    def forward(self, *args, **kwargs):
-        raise NotImplementedError(
-            "a stand-alone attention module call is outside this build: use ARTabPFN.forward "
-            "(inference only) or ARTabPFNPredictor")
+    @torch.no_grad()
+    def forward(self, q, k, v, block_mask):
+        """The reference's module call (ar_tabpfn/model/attention.py:45-61) for inference:
+        q [B,Sq,D], k / v [B,Skv,D] -> (out [B,Sq,D], (K, V) [B,H,Skv,Dh]).  ``block_mask`` is a
+        ``DenseMask`` (every query sees every key: the feature attention across column tokens) or a
+        ``RowMask`` (self-attention over rows laid out [context | buffer | other]).  The softmax
+        attention runs on this library's kernels; the four projections are plain library GEMMs.
+        No autograd graph is built."""
+        from . import triton_kernels as tk
+        B, Sq, D = q.shape
+        Skv = k.shape[1]
+        H, Dh = self.n_heads, self.head_dim
+        qh = self.q_proj(q).view(B, Sq, H, Dh).transpose(1, 2)
+        kh = self.k_proj(k).view(B, Skv, H, Dh).transpose(1, 2)
+        vh = self.v_proj(v).view(B, Skv, H, Dh).transpose(1, 2)
+        if isinstance(block_mask, RowMask):
+            if Sq != Skv or block_mask.num_rows != Sq:
+                raise ValueError("a RowMask describes self-attention over num_rows rows")
+            out = tk.row_attention(qh, kh, vh, block_mask.context_len, block_mask.buffer_len, block_mask.visible)
+        elif isinstance(block_mask, DenseMask):
+            out = tk.dense_attention(qh, kh, vh)
+        else:
+            raise TypeError("block_mask must be a DenseMask or a RowMask of this package (flex BlockMasks are not "
+                            "decoded)")
+        out = out.transpose(1, 2).reshape(B, Sq, D)
+        return self.out_proj(out), (kh, vh)
 
 
 class DenseMask:

@@ -94,8 +94,22 @@ class TwoStageTransformerLayer(nn.Module):
         self.norm2 = nn.LayerNorm(d_model)
         self.norm3 = nn.LayerNorm(d_model)
 
-    def forward(self, *args, **kwargs):
-        raise NotImplementedError("training forward is outside this build")
+    @torch.no_grad()
+    def forward(self, x: Tensor, mask_features, mask_rows):
+        """The reference's layer call (model.py:100-126) for inference, with ANY number of column
+        tokens: x [B,R,C,D] -> (x [B,R,C,D], (K, V) of the row attention [B*C,H,R,Dh]).  Feature
+        attention across the C tokens of a row under ``mask_features`` (a ``DenseMask``), row attention
+        over the R rows of every column under ``mask_rows`` (a ``RowMask``); both softmax attentions
+        run on this library's kernels, projections / LayerNorm / MLP are library calls.  The
+        predictor's hot path (one token per row) does not come through here."""
+        B, R, C, D = x.shape
+        x_feat = x.reshape(B * R, C, D)
+        attn_out, _ = self.attn_features(x_feat, x_feat, x_feat, mask_features)
+        x = self.norm1((attn_out + x_feat).reshape(B, R, C, D))
+        x_row = x.permute(0, 2, 1, 3).reshape(B * C, R, D)
+        attn_out, kv = self.attn_rows(x_row, x_row, x_row, mask_rows)
+        x = self.norm2((attn_out + x_row).reshape(B, C, R, D).permute(0, 2, 1, 3))
+        return self.norm3(x + self.ff(x)), kv
 
 
 class TwoStageTransformer(nn.Module):
@@ -105,8 +119,15 @@ class TwoStageTransformer(nn.Module):
         self.layers = nn.ModuleList([TwoStageTransformerLayer(d_model, n_heads, d_ff) for _ in range(n_layers)])
         self.norm = nn.LayerNorm(d_model)
 
-    def forward(self, *args, **kwargs):
-        raise NotImplementedError("training forward is outside this build")
+    @torch.no_grad()
+    def forward(self, x: Tensor, mask_features, mask_rows):
+        """x [B,R,C,D] through every layer and the final norm; returns (x, [(K, V) per layer]) like the
+        reference (model.py:139-147).  Inference only."""
+        kv_cache = []
+        for layer in self.layers:
+            x, kv = layer(x, mask_features, mask_rows)
+            kv_cache.append(kv)
+        return self.norm(x), kv_cache
 
 
 class _HeadWeights:

@@ -79,6 +79,48 @@ def _context_partials(qr: Tensor, k: Tensor, v: Tensor, Nc: int, Ncp: int, rows_
     return out, lse
 
 
+def dense_attention(q: Tensor, k: Tensor, v: Tensor) -> Tensor:
+    """Softmax attention of every query over all keys of its own group: q [G,H,Lq,Dh],
+    k / v [G,H,Lk,Dh] -> [G,H,Lq,Dh] (q dtype).  What the reference's MultiheadAttention computes
+    under create_dense_mask (ar_tabpfn/model/attention.py:45-61, 72-83), e.g. the feature attention
+    across the C column tokens of a row."""
+    G, H, Lq, Dh = q.shape
+    kp, vp, Nk, Nkp = pack_context(k.to(q.dtype), v.to(q.dtype))
+    o, _ = _context_partials(_rows(q), kp, vp, Nk, Nkp, Lq, 1)
+    return _unrows(o[0], G, Lq).to(q.dtype)
+
+
+def row_attention(q: Tensor, k: Tensor, v: Tensor, context_len: int, buffer_len: int, visible) -> Tensor:
+    """Self-attention over R rows laid out [context | buffer | other] under a row mask of the
+    create_row_mask family (ar_tabpfn/model/attention.py:86-175): q / k / v [G,H,R,Dh] -> [G,H,R,Dh].
+    Context rows see the context.  Non-context row j sees the context and the first ``visible[j]``
+    buffer rows: its context part and its buffer part are computed separately and merged by
+    log-sum-exp in registers (no mask tensor, no concatenated K/V)."""
+    G, H, R, Dh = q.shape
+    Nc, Nb = int(context_len), int(buffer_len)
+    Nr = R - Nc
+    if Nc <= 0:
+        raise ValueError("row attention needs at least one context row")
+    if len(visible) != Nr:
+        raise ValueError("one visible count per non-context row is needed")
+    lib = _lib.lib()
+    kp, vp, _, Ncp = pack_context(k[:, :, :Nc].to(q.dtype), v[:, :, :Nc].to(q.dtype))
+    out = torch.empty(G, H, R, Dh, device=q.device, dtype=q.dtype)
+    o, _ = _context_partials(_rows(q[:, :, :Nc]), kp, vp, Nc, Ncp, Nc, 1)
+    out[:, :, :Nc] = _unrows(o[0], G, Nc).to(q.dtype)
+    if Nr > 0:
+        qr = _rows(q[:, :, Nc:])
+        o, l = _context_partials(qr, kp, vp, Nc, Ncp, Nr, 1)
+        kv = _pack_buffer(k[:, :, Nc:Nc + Nb].to(q.dtype), v[:, :, Nc:Nc + Nb].to(q.dtype)) if Nb else None
+        vis = torch.tensor([int(x) for x in visible], dtype=torch.int32, device=q.device)
+        merged = torch.empty(G * Nr, H, Dh, device=q.device, dtype=torch.float32)
+        _lib.check(lib.artab_buffer_attention_merge_visible(
+            _lib.dtype_code(q.dtype), _lib.ptr(qr), _lib.ptr(kv), G, H, Dh, Nb, Nr, _lib.ptr(vis), Nb, _lib.ptr(o),
+            _lib.ptr(l), 1, G * Nr, _lib.ptr(merged), _lib.stream_ptr()))
+        out[:, :, Nc:] = _unrows(merged, G, Nr).to(q.dtype)
+    return out
+
+
 def _scaled(q: Tensor, scale: Optional[float]) -> Tensor:
     Dh = q.shape[-1]
     if scale is None or abs(scale - Dh ** -0.5) < 1e-12:

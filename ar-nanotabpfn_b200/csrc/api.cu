@@ -787,6 +787,38 @@ int artab_buffer_attention_merge_ragged(int dtype, const void* q, const void* kv
   return launch_buf_merge(b, (cudaStream_t)stream);
 }
 
+int artab_buffer_attention_merge_visible(int dtype, const void* q, const void* kv_buf, int n_streams, int n_heads,
+                                         int head_dim, int max_buf, int tokens_per_stream, const int32_t* visible,
+                                         int n_buf, const float* o_part, const float* lse_part, int n_splits,
+                                         int rows, float* out, void* stream) {
+  PlainLaunchScope plain;  // the caller's earlier launches are unknown: see common.cuh
+  ARTAB_REQUIRE(q && o_part && lse_part && out && visible && n_splits >= 1, ARTAB_EINVAL,
+                "buffer_attention_merge_visible: null pointer");
+  ARTAB_REQUIRE(kv_buf || n_buf == 0, ARTAB_EINVAL, "buffer_attention_merge_visible: kv_buf is null");
+  ARTAB_REQUIRE(tokens_per_stream >= 1 && n_buf >= 0 && n_buf <= max_buf && rows == n_streams * tokens_per_stream,
+                ARTAB_EINVAL, "buffer_attention_merge_visible: inconsistent sizes");
+  BufMergeArgs b;
+  memset(&b, 0, sizeof(b));
+  b.dtype = dtype;
+  b.q = q;
+  b.kv_buf = kv_buf;
+  b.n_heads = n_heads;
+  b.head_dim = head_dim;
+  b.max_buf = max_buf;
+  b.mode_tf = 2;
+  b.visible = visible;
+  b.tps = tokens_per_stream;
+  b.len0 = n_buf;  // upper bound of every visible count
+  b.n_items = (long)n_streams * n_heads * tokens_per_stream;
+  b.o_part = o_part;
+  b.lse_part = lse_part;
+  b.n_splits = n_splits;
+  b.rows = rows;
+  b.scale = 1.0f / sqrtf((float)head_dim);
+  b.out = out;
+  return launch_buf_merge(b, (cudaStream_t)stream);
+}
+
 int artab_kv_append(int dtype, void* kv_buf, const void* k_new, const void* v_new, int n_streams, int n_heads,
                     int head_dim, int max_buf, int pos, void* stream) {
   PlainLaunchScope plain;  // the caller's earlier launches are unknown: see common.cuh

@@ -267,6 +267,19 @@ ARTAB_API int artab_buffer_attention_merge(int dtype, const void* q, const void*
                                  const float* o_part, const float* lse_part, int n_splits, int rows,
                                  float* out, void* stream);
 
+/* The general prefix form: every stream carries `tokens_per_stream` query rows, and row j of a
+ * stream sees the first visible[j] of the stream's n_buf buffer rows (int32 device array
+ * [tokens_per_stream], values clamped to [0, n_buf]); merged in registers with the n_splits context
+ * partials like the other forms.  This is the buffer half of the reference's row attention under
+ * create_row_mask (ar_tabpfn/model/attention.py:86-175), where the visibility of the buffer rows is
+ * a prefix for every non-context row; the context half is artab_context_attention.
+ *   out [rows][H][Dh] fp32, rows = n_streams * tokens_per_stream. */
+ARTAB_API int artab_buffer_attention_merge_visible(int dtype, const void* q, const void* kv_buf, int n_streams,
+                                                   int n_heads, int head_dim, int max_buf, int tokens_per_stream,
+                                                   const int32_t* visible, int n_buf, const float* o_part,
+                                                   const float* lse_part, int n_splits, int rows, float* out,
+                                                   void* stream);
+
 /* The decode form of artab_buffer_attention_merge with RAGGED private buffers: stream b sees
  * its first lens[b] buffer rows (int32 device array [B], values clamped to [0, len_max];
  * NULL: len_max for every stream), the same for every head and for both queries of a stream.

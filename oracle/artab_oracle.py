@@ -515,6 +515,46 @@ class OraclePredictor:
         return head_logpdf(mean, std, logw, yt)
 
 
+def backbone_forward(sd: Dict[str, Tensor], n_heads: int, x: Tensor, n_ctx: int, n_buf: int, visible,
+                     prefix: str = ""):
+    """The backbone on inputs with C column tokens per row, x [B,R,C,D] -> [B,R,C,D]
+    (model.py:100-147 of the reference): per layer feature attention across the C tokens of a row
+    (dense), LayerNorm, row attention over the R rows of every column under a row mask of the
+    create_row_mask family (rows [context | buffer | other]; non-context row j sees the context and
+    the first visible[j] buffer rows; context rows see the context), LayerNorm, MLP, LayerNorm; the
+    final LayerNorm at the end.  Also returns the row-attention K, V [B*C,H,R,Dh] of every layer."""
+    B, R, C, D = x.shape
+    H, Dh = n_heads, D // n_heads
+    allowed = torch.zeros(R, R, dtype=torch.bool)
+    allowed[:, :n_ctx] = True
+    for j, v in enumerate(visible):
+        allowed[n_ctx + j, n_ctx:n_ctx + int(v)] = True
+
+    def mha(p, t, mask):
+        G, S, _ = t.shape
+        hd = lambda w: linear(t, sd[p + w]).view(G, S, H, Dh).transpose(1, 2)
+        q, k, v = hd("q_proj.weight"), hd("k_proj.weight"), hd("v_proj.weight")
+        o = masked_attention(q, k, v, mask)
+        return linear(o.transpose(1, 2).reshape(G, S, D), sd[p + "out_proj.weight"]), (k, v)
+
+    kvs = []
+    L = 0
+    while f"{prefix}layers.{L}.norm1.weight" in sd:
+        L += 1
+    for l in range(L):
+        p = f"{prefix}layers.{l}."
+        xf = x.reshape(B * R, C, D)
+        a, _ = mha(p + "attn_features.", xf, None)
+        x = layer_norm((a + xf).reshape(B, R, C, D), sd[p + "norm1.weight"], sd[p + "norm1.bias"])
+        xr = x.permute(0, 2, 1, 3).reshape(B * C, R, D)
+        a, kv = mha(p + "attn_rows.", xr, allowed)
+        kvs.append(kv)
+        x = layer_norm((a + xr).reshape(B, C, R, D).permute(0, 2, 1, 3), sd[p + "norm2.weight"], sd[p + "norm2.bias"])
+        ff = linear(gelu_erf(linear(x, sd[p + "ff.0.weight"], sd[p + "ff.0.bias"])), sd[p + "ff.2.weight"], sd[p + "ff.2.bias"])
+        x = layer_norm(x + ff, sd[p + "norm3.weight"], sd[p + "norm3.bias"])
+    return layer_norm(x, sd[prefix + "norm.weight"], sd[prefix + "norm.bias"]), kvs
+
+
 def row_mask_visible(n_buf: int, n_targets: int, attending_chunks: Optional[int] = None):
     """Visible-buffer counts of the non-context rows under create_row_mask
     (attention.py:86-175): buffer j sees buffers <= j; target t sees buffers

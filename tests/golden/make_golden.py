@@ -2,7 +2,7 @@
 
 Run once, in a container where the reference checkout is available:
 
-    python tests/golden/make_golden.py /path/to/reference [--forward-only | --ragged-only]
+    python tests/golden/make_golden.py /path/to/reference [--forward-only | --ragged-only | --columns-only]
 
 It imports the reference's ``ar_tabpfn.model`` package under the alias
 ``ref_ar_tabpfn`` (so it cannot collide with the shipped drop-in package of
@@ -229,6 +229,31 @@ def ragged_fixture(tk):
     return cases
 
 
+@torch.no_grad()
+def columns_fixture(ref, root):
+    """The reference's backbone (TwoStageTransformer) on inputs with SEVERAL column tokens per row,
+    x [B, R, C, D] with C > 1: feature attention across the C tokens of a row under
+    create_dense_mask(C), row attention over the R rows of every column under create_row_mask.
+    Stored: input, weights, the output after the final norm and the row-attention K / V of layer 0."""
+    attn = importlib.import_module("ref_ar_tabpfn.model.attention")
+    cases = []
+    for seed, (D, H, L, Dff, B, C, Nc, Nb, Nt) in enumerate([(64, 4, 2, 128, 2, 3, 20, 4, 8), (64, 2, 1, 128, 3, 5, 33, 2, 4),
+                                                              (32, 2, 1, 64, 1, 2, 7, 1, 3)]):
+        torch.manual_seed(100 + seed)
+        m = ref.TwoStageTransformer(D, H, L, Dff).eval()
+        for mod in m.modules():
+            if isinstance(mod, torch.nn.Linear):
+                torch.nn.init.xavier_uniform_(mod.weight)
+        R = Nc + Nb + Nt
+        x = torch.randn(B, R, C, D)
+        mf = attn.create_dense_mask(C, device="cpu")
+        mr = attn.create_row_mask(R, context_len=Nc, buffer_len=Nb, attending_chunks=1, device="cpu")
+        out, kv = m(x, mf, mr)
+        cases.append(dict(cfg=dict(d_model=D, n_heads=H, n_layers=L, d_ff=Dff), B=B, C=C, Nc=Nc, Nb=Nb, Nt=Nt,
+                          attending_chunks=1, x=x, state_dict=sd_of(m), out=out, k0=kv[0][0], v0=kv[0][1]))
+    return cases
+
+
 def compact(o):
     """Clone every tensor so that no view drags a larger storage into the file."""
     if isinstance(o, torch.Tensor):
@@ -249,6 +274,10 @@ def main():
     if "--ragged-only" in sys.argv[2:]:       # leaves the other fixtures as they are
         torch.save(compact(ragged_fixture(tk)), os.path.join(HERE, "ragged.pt"))
         print("ragged.pt", os.path.getsize(os.path.join(HERE, "ragged.pt")))
+        return
+    if "--columns-only" in sys.argv[2:]:      # leaves the other fixtures as they are
+        torch.save(compact(columns_fixture(ref, root)), os.path.join(HERE, "columns.pt"))
+        print("columns.pt", os.path.getsize(os.path.join(HERE, "columns.pt")))
         return
     if "--forward-only" in sys.argv[2:]:      # leaves the other fixtures as they are
         torch.save(compact(forward_fixture(ref, root)), os.path.join(HERE, "forward.pt"))
@@ -273,7 +302,8 @@ def main():
     torch.save(compact(h32), os.path.join(HERE, "dh32.pt"))
     torch.save(compact(forward_fixture(ref, root)), os.path.join(HERE, "forward.pt"))
     torch.save(compact(ragged_fixture(tk)), os.path.join(HERE, "ragged.pt"))
-    for f in ("ops.pt", "config1.pt", "tiny_distinct.pt", "dh32.pt", "forward.pt", "ragged.pt"):
+    torch.save(compact(columns_fixture(ref, root)), os.path.join(HERE, "columns.pt"))
+    for f in ("ops.pt", "config1.pt", "tiny_distinct.pt", "dh32.pt", "forward.pt", "ragged.pt", "columns.pt"):
         print(f, os.path.getsize(os.path.join(HERE, f)))
 
 

@@ -169,3 +169,14 @@ def test_ragged_buffer_attention_matches_reference():
         assert (out[c["lens"] == 0] == 0).all()          # nothing visible: zero output
         hyb = orc.hybrid_attention(c["q"], c["k_ctx"], c["v_ctx"], c["k_buf"], c["v_buf"], buf_mask=c["mask"])
         torch.testing.assert_close(hyb, c["hybrid"], atol=1e-6, rtol=1e-6)
+
+
+def test_backbone_with_column_tokens_matches_reference():
+    """C > 1 column tokens per row: the oracle's backbone against golden outputs of the reference's
+    TwoStageTransformer under create_dense_mask / create_row_mask."""
+    for c in load("columns.pt"):
+        vis = orc.row_mask_visible(c["Nb"], c["Nt"], c["attending_chunks"])
+        out, kvs = orc.backbone_forward(c["state_dict"], c["cfg"]["n_heads"], c["x"], c["Nc"], c["Nb"], vis)
+        torch.testing.assert_close(out, c["out"], atol=5e-6, rtol=1e-5)
+        torch.testing.assert_close(kvs[0][0], c["k0"], atol=2e-6, rtol=1e-5)
+        torch.testing.assert_close(kvs[0][1], c["v0"], atol=2e-6, rtol=1e-5)
