@@ -57,7 +57,8 @@ _SIGNATURES = {
     "artab_buffer_attention_merge": (_i, [_i, _p, _p, _i, _i, _i, _i, _i, _i, _i, _p, _p, _i, _i, _p, _p]),
     "artab_buffer_attention_merge_ragged": (_i, [_i, _p, _p, _i, _i, _i, _i, _i, _p, _i, _p, _p, _i, _i, _p, _p,
                                                 _p]),
-    "artab_buffer_attention_merge_visible": (_i, [_i, _p, _p, _i, _i, _i, _i, _i, _p, _i, _p, _p, _i, _i, _p, _p]),
+    "artab_buffer_attention_merge_visible": (_i, [_i, _p, _p, _i, _i, _i, _i, _i, _p, _i, _p, _p, _p, _i, _i, _p, _p,
+                                                  _p]),
     "artab_kv_append": (_i, [_i, _p, _p, _p, _i, _i, _i, _i, _i, _p]),
     "artab_embed": (_i, [C.POINTER(Model), _p, _p, _p, _i, _i, _i, _p, _p]),
     "artab_head_logpdf": (_i, [C.POINTER(Model), _p, _p, _i, _p, _p]),

@@ -115,8 +115,8 @@ def row_attention(q: Tensor, k: Tensor, v: Tensor, context_len: int, buffer_len:
         vis = torch.tensor([int(x) for x in visible], dtype=torch.int32, device=q.device)
         merged = torch.empty(G * Nr, H, Dh, device=q.device, dtype=torch.float32)
         _lib.check(lib.artab_buffer_attention_merge_visible(
-            _lib.dtype_code(q.dtype), _lib.ptr(qr), _lib.ptr(kv), G, H, Dh, Nb, Nr, _lib.ptr(vis), Nb, _lib.ptr(o),
-            _lib.ptr(l), 1, G * Nr, _lib.ptr(merged), _lib.stream_ptr()))
+            _lib.dtype_code(q.dtype), _lib.ptr(qr), _lib.ptr(kv), G, H, Dh, Nb, Nr, _lib.ptr(vis), Nb, None,
+            _lib.ptr(o), _lib.ptr(l), 1, G * Nr, _lib.ptr(merged), None, _lib.stream_ptr()))
         out[:, :, Nc:] = _unrows(merged, G, Nr).to(q.dtype)
     return out
 
@@ -170,18 +170,35 @@ def _pack_buffer(k_buf: Tensor, v_buf: Tensor) -> Tensor:
 
 
 def _stream_lengths(mask: Optional[Tensor], B: int, H: int, Lq: int, Nb: int, device) -> Optional[Tensor]:
-    """A buffer mask (True = visible, broadcastable to [B,H,Lq,Nb]) as per-stream lengths [B] int32.
-    The kernels take ragged buffers as one visible-prefix length per stream, which covers the masks
-    the reference itself uses on this path; any other pattern is refused."""
-    if mask is None:
-        return None
+    """A buffer mask (True = visible, broadcastable to [B,H,Lq,Nb]) as per-stream lengths [B] int32
+    when it is one visible prefix per stream (ragged buffers: what the reference itself uses on this
+    path, and the fast tensor-core form of the buffer pass); None for any other pattern, which
+    ``_buffer_merge_masked`` serves."""
     m = mask.to(device=device, dtype=torch.bool).expand(B, H, Lq, Nb)
     lens = m[:, 0, 0].sum(dim=-1)
     want = torch.arange(Nb, device=device)[None, None, None, :] < lens[:, None, None, None]
     if not torch.equal(m, want.expand(B, H, Lq, Nb)):
-        raise NotImplementedError("buffer masks must be one visible prefix per stream (the same for every head "
-                                  "and query); use hybrid_teacher_forcing_attention for the block-causal pattern")
+        return None
     return lens.to(torch.int32).contiguous()
+
+
+def _buffer_merge_masked(q: Tensor, kv: Tensor, mask: Tensor, partials, want_lse: bool):
+    """The general form: any boolean mask broadcastable to [B,H,Lq,Nb].  One work item per
+    (stream, head, query); the mask travels as one byte per (query row, head, key)."""
+    lib = _lib.lib()
+    B, H, Lq, Dh = q.shape
+    Nb = kv.shape[2]
+    qr = _rows(q)                                                   # [B*Lq, H, Dh]
+    o, l, splits = partials(qr, Lq)
+    m = mask.to(device=q.device, dtype=torch.bool).expand(B, H, Lq, Nb)
+    km = m.permute(0, 2, 1, 3).reshape(B * Lq, H, Nb).to(torch.uint8).contiguous()
+    vis = torch.full((Lq,), Nb, dtype=torch.int32, device=q.device)
+    merged = torch.empty(B * Lq, H, Dh, device=q.device, dtype=torch.float32)
+    lse = torch.empty(B * Lq, H, device=q.device, dtype=torch.float32) if want_lse else None
+    _lib.check(lib.artab_buffer_attention_merge_visible(
+        _lib.dtype_code(q.dtype), _lib.ptr(qr), _lib.ptr(kv), B, H, Dh, Nb, Lq, _lib.ptr(vis), Nb, _lib.ptr(km),
+        _lib.ptr(o), _lib.ptr(l), splits, B * Lq, _lib.ptr(merged), _lib.ptr(lse), _lib.stream_ptr()))
+    return _unrows(merged, B, Lq), (lse.view(B, Lq, H).permute(0, 2, 1) if want_lse else None)
 
 
 def _buffer_merge(q: Tensor, kv: Tensor, lens: Optional[Tensor], partials, want_lse: bool):
@@ -209,19 +226,23 @@ def _buffer_merge(q: Tensor, kv: Tensor, lens: Optional[Tensor], partials, want_
 def pytorch_buffer_attention(q: Tensor, k_buf: Tensor, v_buf: Tensor, mask: Optional[Tensor] = None,
                              scale: Optional[float] = None) -> Tuple[Tensor, Tensor]:
     """Attention of q [B,H,Lq,Dh] over each stream's private K/V [B,H,Nb,Dh] -> out (q dtype),
-    lse [B,H,Lq] fp32.  ``mask``: one visible prefix per stream (ragged buffers); a query that
+    lse [B,H,Lq] fp32.  ``mask``: any boolean tensor broadcastable to [B,H,Lq,Nb] (True = visible);
+    one visible prefix per stream (ragged buffers) takes the fast form of the pass.  A query that
     sees nothing gets out = 0 and lse = -inf, like the reference (triton_kernels.py:570-614).
     The name is the reference's; the work runs in the buffer-pass kernel."""
     B, H, Lq, Dh = q.shape
     Nb = k_buf.shape[2]
-    lens = _stream_lengths(mask, B, H, Lq, Nb, q.device)
+    lens = _stream_lengths(mask, B, H, Lq, Nb, q.device) if mask is not None else None
     kv = _pack_buffer(k_buf.to(q.dtype), v_buf.to(q.dtype))
 
     def no_context(qr, n):
         return (torch.zeros(1, B * n, H, Dh, device=q.device, dtype=torch.float32),
                 torch.full((1, B * n, H), float("-inf"), device=q.device, dtype=torch.float32), 1)
 
-    out, lse = _buffer_merge(_scaled(q, scale), kv, lens, no_context, want_lse=True)
+    if mask is not None and lens is None and Nb > 0:
+        out, lse = _buffer_merge_masked(_scaled(q, scale), kv, mask, no_context, want_lse=True)
+    else:
+        out, lse = _buffer_merge(_scaled(q, scale), kv, lens, no_context, want_lse=True)
     return out.to(q.dtype), lse
 
 
@@ -235,14 +256,14 @@ def pytorch_context_attention(q: Tensor, k_ctx: Tensor, v_ctx: Tensor,
 def hybrid_attention(q: Tensor, k_ctx: Tensor, v_ctx: Tensor, k_buf: Tensor, v_buf: Tensor,
                      buf_mask: Optional[Tensor] = None, use_triton: bool = True) -> Tensor:
     """Shared-context attention + private-buffer attention merged by log-sum-exp.  Every query
-    sees every buffer key of its stream, or with ``buf_mask`` the stream's visible prefix (ragged
-    buffer lengths).  Returns [B,H,Lq,Dh]."""
+    sees every buffer key of its stream, or with ``buf_mask`` (any boolean tensor broadcastable to
+    [B,H,Lq,Nb]) what the mask lets it see.  Returns [B,H,Lq,Dh]."""
     B, H, Lq, Dh = q.shape
     Nb = k_buf.shape[2]
     if Nb == 0:
         return triton_context_attention(q, k_ctx, v_ctx)[0]
     lib = _lib.lib()
-    lens = _stream_lengths(buf_mask, B, H, Lq, Nb, q.device)
+    lens = _stream_lengths(buf_mask, B, H, Lq, Nb, q.device) if buf_mask is not None else None
     k, v, Nc, Ncp = pack_context(k_ctx.to(q.dtype), v_ctx.to(q.dtype))
     kv = _pack_buffer(k_buf.to(q.dtype), v_buf.to(q.dtype))
 
@@ -251,6 +272,8 @@ def hybrid_attention(q: Tensor, k_ctx: Tensor, v_ctx: Tensor, k_buf: Tensor, v_b
         o, l = _context_partials(qr, k, v, Nc, Ncp, n, splits)
         return o, l, splits
 
+    if buf_mask is not None and lens is None:
+        return _buffer_merge_masked(q, kv, buf_mask, context, want_lse=False)[0].to(q.dtype)
     return _buffer_merge(q, kv, lens, context, want_lse=False)[0].to(q.dtype)
 
 

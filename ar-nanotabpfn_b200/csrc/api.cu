@@ -789,8 +789,9 @@ int artab_buffer_attention_merge_ragged(int dtype, const void* q, const void* kv
 
 int artab_buffer_attention_merge_visible(int dtype, const void* q, const void* kv_buf, int n_streams, int n_heads,
                                          int head_dim, int max_buf, int tokens_per_stream, const int32_t* visible,
-                                         int n_buf, const float* o_part, const float* lse_part, int n_splits,
-                                         int rows, float* out, void* stream) {
+                                         int n_buf, const uint8_t* key_mask, const float* o_part,
+                                         const float* lse_part, int n_splits, int rows, float* out, float* lse_out,
+                                         void* stream) {
   PlainLaunchScope plain;  // the caller's earlier launches are unknown: see common.cuh
   ARTAB_REQUIRE(q && o_part && lse_part && out && visible && n_splits >= 1, ARTAB_EINVAL,
                 "buffer_attention_merge_visible: null pointer");
@@ -808,6 +809,8 @@ int artab_buffer_attention_merge_visible(int dtype, const void* q, const void* k
   b.mode_tf = 2;
   b.visible = visible;
   b.tps = tokens_per_stream;
+  b.key_mask = key_mask;
+  b.lse_out = lse_out;
   b.len0 = n_buf;  // upper bound of every visible count
   b.n_items = (long)n_streams * n_heads * tokens_per_stream;
   b.o_part = o_part;

@@ -27,6 +27,8 @@ struct BufMergeArgs {
   int mode_tf, nt, n_new, len0;  // mode_tf: 0 decode step, 1 teacher forcing, 2 per-token visible prefix
   const int32_t* visible;  // mode 2: [tps] token j of a stream sees buffer keys [0, visible[j])
   int tps;                 // mode 2: tokens per stream
+  const uint8_t* key_mask; // mode 2, optional: [rows][H][max_buf] bytes, non-zero = the query sees that buffer key
+                           // (on top of the visible prefix): arbitrary boolean masks of the functional API
   const int32_t* lens;     // mode 0: [B] visible buffer rows of each stream, clamped to len0 (null: len0 for all)
   float* lse_out;          // optional [rows][H]: natural-log LSE of the merged attention (-inf: nothing visible)
   long n_items;

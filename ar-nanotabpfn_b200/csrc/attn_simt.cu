@@ -175,6 +175,7 @@ __global__ void __launch_bounds__(128, 6) buf_merge_kernel(const BufMergeArgs a)
   long b;
   int h, len;
   long row_t, row_b;
+  const uint8_t* mrow = nullptr;  // optional per-key visibility of this item's query (mode 2)
   if (a.mode_tf == 2) {
     // one query per item: token j of stream b sees the first visible[j] buffer rows
     const int j = (int)(item % a.tps);
@@ -184,6 +185,7 @@ __global__ void __launch_bounds__(128, 6) buf_merge_kernel(const BufMergeArgs a)
     len = min(max(__ldg(a.visible + j), 0), a.len0);  // len0: buffer rows written per stream
     row_t = b * a.tps + j;
     row_b = -1;
+    if (a.key_mask) mrow = a.key_mask + ((size_t)row_t * a.n_heads + h) * a.max_buf;
   } else if (a.mode_tf) {
     const int ips = a.nt + 1;
     const int i = (int)(item % ips);
@@ -261,7 +263,8 @@ __global__ void __launch_bounds__(128, 6) buf_merge_kernel(const BufMergeArgs a)
         s0 += __shfl_xor_sync(0xffffffffu, s0, o);
         s1 += __shfl_xor_sync(0xffffffffu, s1, o);
       }
-      const bool valid = key0 + c * KPI + grp < len;
+      bool valid = key0 + c * KPI + grp < len;
+      if (valid && mrow) valid = mrow[key0 + c * KPI + grp] != 0;
       sc0[c] = valid ? s0 : -INFINITY;
       sc1[c] = valid ? s1 : -INFINITY;
     }
@@ -272,7 +275,11 @@ __global__ void __launch_bounds__(128, 6) buf_merge_kernel(const BufMergeArgs a)
         mn0 = fmaxf(mn0, sc0[c]);
         mn1 = fmaxf(mn1, sc1[c]);
       }
-      const float a0 = fast_exp2(m[0] - mn0), a1 = fast_exp2(m[1] - mn1);
+      // a lane group whose keys are all masked so far keeps mn = -inf: nothing to rescale, and its
+      // exponentials below are taken against 0 instead (exp2(-inf - 0) = 0 for the masked keys)
+      const float a0 = mn0 == -INFINITY ? 1.0f : fast_exp2(m[0] - mn0);
+      const float a1 = mn1 == -INFINITY ? 1.0f : fast_exp2(m[1] - mn1);
+      const float r0 = mn0 == -INFINITY ? 0.0f : mn0, r1 = mn1 == -INFINITY ? 0.0f : mn1;
       l[0] *= a0;
       l[1] *= a1;
 #pragma unroll
@@ -285,7 +292,7 @@ __global__ void __launch_bounds__(128, 6) buf_merge_kernel(const BufMergeArgs a)
         if (key0 + c * KPI >= len) continue;
         float vf[VEC];
         Vec16<T>::unpack(vr[c], vf);
-        const float p0 = fast_exp2(sc0[c] - mn0), p1 = fast_exp2(sc1[c] - mn1);  // masked keys: exp2(-inf) = 0
+        const float p0 = fast_exp2(sc0[c] - r0), p1 = fast_exp2(sc1[c] - r1);  // masked keys: exp2(-inf) = 0
         l[0] += p0;
         l[1] += p1;
 #pragma unroll

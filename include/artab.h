@@ -273,12 +273,16 @@ ARTAB_API int artab_buffer_attention_merge(int dtype, const void* q, const void*
  * partials like the other forms.  This is the buffer half of the reference's row attention under
  * create_row_mask (ar_tabpfn/model/attention.py:86-175), where the visibility of the buffer rows is
  * a prefix for every non-context row; the context half is artab_context_attention.
- *   out [rows][H][Dh] fp32, rows = n_streams * tokens_per_stream. */
+ * key_mask (optional, may be NULL): [rows][H][max_buf] bytes, non-zero = this query sees that buffer
+ * key, applied on top of the prefix: with visible[j] = n_buf it expresses ANY boolean mask, which is
+ * what pytorch_buffer_attention / hybrid_attention accept (ar_tabpfn/model/triton_kernels.py:570-614).
+ *   out [rows][H][Dh] fp32, rows = n_streams * tokens_per_stream; lse_out optional [rows][H] fp32
+ *   (natural log of the merged attention, -inf where a query sees nothing). */
 ARTAB_API int artab_buffer_attention_merge_visible(int dtype, const void* q, const void* kv_buf, int n_streams,
                                                    int n_heads, int head_dim, int max_buf, int tokens_per_stream,
-                                                   const int32_t* visible, int n_buf, const float* o_part,
-                                                   const float* lse_part, int n_splits, int rows, float* out,
-                                                   void* stream);
+                                                   const int32_t* visible, int n_buf, const uint8_t* key_mask,
+                                                   const float* o_part, const float* lse_part, int n_splits,
+                                                   int rows, float* out, float* lse_out, void* stream);
 
 /* The decode form of artab_buffer_attention_merge with RAGGED private buffers: stream b sees
  * its first lens[b] buffer rows (int32 device array [B], values clamped to [0, len_max];
