@@ -248,8 +248,15 @@ __device__ __forceinline__ float gelu_fast(float x) {
 }
 
 
-// Optional in-kernel timeline (diagnostic builds only, -DARTAB_TIMELINE): the first epilogue thread of
-// every CTA stamps clock64() at the phase boundaries of the launch; slot = launch counter mod 32.
+// Optional in-kernel timeline (diagnostic builds only, -DARTAB_TIMELINE; read by
+// `microbench.py timeline`): the first epilogue thread of every CTA stamps clock64() at the phase
+// boundaries of the launch; slot = launch counter mod 32.  Marks: 0 roles split, 1 constants staged,
+// 2 predecessor complete, 3 attention rows published, 4 Wo accumulator ready, 25 LayerNorm 2 done,
+// 5 x2 published, 6 MLP starts, 7.. hidden tile done, 13 second GEMM complete, 10 / 11 / 12 / 19
+// exchange (enter, peer ready, stores issued, data arrived), 14 exchange done, 15 LayerNorm 3 done,
+// 16 x3 published, 17 fold accumulator ready, 18 x1 published, 27 issuer sees x1, 20 / 22 projection
+// accumulators ready, 21 / 23 staged projections stored, 24 head accumulator ready, 26 epilogue done;
+// 28 clock at kernel entry; 29 / 30 / 31 global timer (ns) at entry, predecessor complete, end.
 #ifdef ARTAB_TIMELINE
 __device__ long long g_tl[32][32][32];   // [launch slot][cta][mark]
 #define TL(id) do { if (tl_on) g_tl[a.tl_slot & 31][blockIdx.x & 31][id] = clock64(); } while (0)
@@ -387,7 +394,7 @@ struct Issuer {
   }
   // ACC[acc_col] = A_x . W^T with W streamed as `nkc` slabs of [n_out rows][64 k].
   // One out-of-line copy serves every call site (see gemm_full_ts_shared below).
-  __device__ void gemm_full_ts(uint32_t acc_col, int n_out, int nkc, bool has_lo, long long* stamp = nullptr);
+  __device__ void gemm_full_ts(uint32_t acc_col, int n_out, int nkc, bool has_lo);
   // ACC_H (128 columns) = A_x . W_tile^T; the tile arrives as nkc slabs of [128 rows][64 k] per part,
   // ordered hi part (all k-chunks) then lo part
   __device__ void gemm_tile_ts(int nkc, bool has_lo) {
@@ -468,7 +475,7 @@ struct Issuer {
 // site).  So there is ONE copy, entered with everything in registers; it returns the new ring count,
 // or -1 - count when a wait gave up.
 __device__ __noinline__ int gemm_full_ts_shared(Smem* sm, uint32_t tmem, int ring, int consumed, uint32_t acc_col,
-                                                int n_out, int nkc, int has_lo, long long* stamp) {
+                                                int n_out, int nkc, int has_lo) {
   const uint32_t idesc = make_idesc(n_out);
   const uint32_t acc = tmem + acc_col;
   uint32_t ahi = tmem + kAxHi, alo = tmem + kAxLo;
@@ -477,7 +484,6 @@ __device__ __noinline__ int gemm_full_ts_shared(Smem* sm, uint32_t tmem, int rin
     int buf = consumed % NSLOT;
     ok = ok && mbar_wait(&sm->w_full[ring][buf], (consumed / NSLOT) & 1, &sm->abort_flag);
     tc_fence_after();
-    if (stamp && kc == 0) stamp[0] = clock64();
     const uint64_t bd = make_desc(smem_u32(sm->ring[ring][buf]));
 #pragma unroll
     for (int ks = 0; ks < 4; ++ks) umma_ts(acc, ahi + ks * 8, desc_step(bd, 32 * ks), idesc, (kc | ks) != 0);
@@ -498,8 +504,8 @@ __device__ __noinline__ int gemm_full_ts_shared(Smem* sm, uint32_t tmem, int rin
   }
   return ok ? consumed : -1 - consumed;
 }
-__device__ __forceinline__ void Issuer::gemm_full_ts(uint32_t acc_col, int n_out, int nkc, bool has_lo, long long* stamp) {
-  const int r = gemm_full_ts_shared(sm, tmem, ring, consumed, acc_col, n_out, nkc, has_lo ? 1 : 0, stamp);
+__device__ __forceinline__ void Issuer::gemm_full_ts(uint32_t acc_col, int n_out, int nkc, bool has_lo) {
+  const int r = gemm_full_ts_shared(sm, tmem, ring, consumed, acc_col, n_out, nkc, has_lo ? 1 : 0);
   if (r < 0) {
     ok = false;
     consumed = -1 - r;
@@ -912,9 +918,6 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const DenseArgs a
           if (((t - t_begin) & 1) == 0) {
             mb.ok = mb.ok && m.ok;
             mb.gemm_full_ts(kAccA, D, NKC, lo_pre & 16);
-#ifdef ARTAB_TIMELINE
-            if (t == t_begin) g_tl[a.tl_slot & 31][blockIdx.x & 31][28] = clock64();
-#endif
           } else {
             m.ok = m.ok && mb.ok;
             m.gemm_full_ts(kAccA, D, NKC, lo_pre & 16);

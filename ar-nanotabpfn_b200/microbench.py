@@ -7,6 +7,7 @@
     python ar-nanotabpfn_b200/microbench.py chain   [--streams 512 --ctx 1024 --targets 8]
     python ar-nanotabpfn_b200/microbench.py config4 [--datasets 64 --ctx 2048 --targets 256]
     python ar-nanotabpfn_b200/microbench.py config5 [--streams 4096 --ctx 16384 --targets 256]
+    python ar-nanotabpfn_b200/microbench.py timeline           (needs a library built with -DARTAB_TIMELINE)
 
 ``ctx`` is the shared-context decode-attention micro-benchmark: bf16, head_dim 32,
 every stream carries ``lq`` queries against one shared context K/V ~ N(0,1); the
@@ -337,9 +338,61 @@ def bench_config5(a):
         dist.destroy_process_group()
 
 
+TIMELINE_MARKS = {0: "roles split", 1: "constants staged", 2: "predecessor complete", 3: "attention rows published",
+                  4: "Wo acc ready", 25: "LayerNorm 2", 5: "x2 published", 6: "MLP starts", 7: "hidden 0", 8: "hidden 1",
+                  9: "hidden 2", 13: "second GEMM complete", 10: "X enter", 11: "X peer ready", 12: "X stores issued",
+                  19: "X data arrived", 14: "exchange done", 15: "LayerNorm 3", 16: "x3 published", 17: "fold acc ready",
+                  18: "x1 published", 27: "issuer sees x1", 20: "proj 0 acc ready", 21: "proj 0 stored",
+                  22: "proj 1 acc ready", 23: "proj 1 stored", 24: "proj 2 / head acc ready", 26: "epilogue done"}
+
+
+def bench_timeline(a):
+    """Per-phase SM-cycle stamps of the tensor-core dense chain during a short config-3 sampling job.
+    Needs a diagnostic build of the library:
+        NVCC_APPEND_FLAGS=-DARTAB_TIMELINE python ar-nanotabpfn_b200/build.py --force
+    or one kept beside the product library and named by the environment variable ARTAB_TIMELINE_LIB.
+    Prints, for CTA 0 and 1 of every recorded launch slot (the last 32 dense launches), the offset of
+    every mark from the roles split, and the global-timer distances entry -> predecessor complete -> end."""
+    import ctypes as C
+    import numpy as np
+    import ar_tabpfn
+    import synthetic as syn
+    if os.environ.get("ARTAB_TIMELINE_LIB"):
+        _lib.LIB_PATH = os.environ["ARTAB_TIMELINE_LIB"]
+    lib = _lib.lib()
+    if not hasattr(lib, "artab_debug_timeline"):
+        raise SystemExit("this library was built without -DARTAB_TIMELINE")
+    dev = torch.device("cuda")
+    m = syn.config3_model().to(dev)
+    B, Nt = a.streams, a.targets
+    xc, yc, xt = (t.to(dev) for t in syn.config3_workload(B, Nt))
+    p = ar_tabpfn.ARTabPFNPredictor.from_trained_model(m, backend="triton_shared_context", precision="bf16")
+    var = p.draw_variates(Nt, B, dev)
+    for _ in range(2):
+        p.sample_sequence(xc, yc, xt, variates=var)
+    torch.cuda.synchronize()
+    buf = (C.c_longlong * (32 * 32 * 32))()
+    lib.artab_debug_timeline.restype = C.c_int
+    if lib.artab_debug_timeline(buf):
+        raise SystemExit("reading the timeline failed")
+    tl = np.ctypeslib.as_array(buf).reshape(32, 32, 32)
+    for slot in range(32):
+        for cta in (0, 1):
+            t = tl[slot, cta]
+            if t[0] == 0:
+                continue
+            marks = sorted(((int(t[i] - t[0]), TIMELINE_MARKS[i]) for i in TIMELINE_MARKS if t[i] >= t[0]),
+                           key=lambda z: z[0])
+            marks = [z for z in marks if z[0] < 10 ** 7]     # stale marks of an earlier launch in this slot
+            print(json.dumps({"slot": slot, "cta": cta, "entry_to_roles_cycles": int(t[0] - t[28]),
+                              "us_entry_to_predecessor_complete": (int(t[30]) - int(t[29])) / 1e3,
+                              "us_entry_to_end": (int(t[31]) - int(t[29])) / 1e3,
+                              "cycles_from_roles_split": {name: off for off, name in marks}}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("which", choices=["ctx", "config2", "buffer", "append", "chain", "config4", "config5"])
+    ap.add_argument("which", choices=["ctx", "config2", "buffer", "append", "chain", "config4", "config5", "timeline"])
     ap.add_argument("--datasets", type=int, default=64)
     ap.add_argument("--targets", type=int, default=None)
     ap.add_argument("--streams", type=int, default=None)
@@ -356,12 +409,12 @@ def main():
     a = ap.parse_args()
     defaults = {"ctx": dict(streams=1024, ctx=4096), "config2": dict(streams=1024, ctx=4096), "buffer": dict(streams=1024), "append": dict(streams=4096),
                 "chain": dict(streams=512, ctx=1024, targets=8), "config4": dict(ctx=2048, targets=256),
-                "config5": dict(streams=4096, ctx=16384, targets=256)}[a.which]
+                "config5": dict(streams=4096, ctx=16384, targets=256), "timeline": dict(streams=512, targets=9)}[a.which]
     for k, v in defaults.items():
         if getattr(a, k) is None:
             setattr(a, k, v)
     {"ctx": bench_ctx, "config2": bench_config2, "buffer": bench_buffer, "append": bench_append, "chain": bench_chain,
-     "config4": bench_config4, "config5": bench_config5}[a.which](a)
+     "config4": bench_config4, "config5": bench_config5, "timeline": bench_timeline}[a.which](a)
 
 
 if __name__ == "__main__":
