@@ -376,6 +376,17 @@ int decode_common(const artab_model* m, artab_state* st, int n_new, const DenseA
 
 using namespace artab;
 
+#ifdef ARTAB_TIMELINE
+// diagnostic builds: the stamp log shared by all kernels (see common.cuh) and its reader
+namespace artab {
+StampLog* stamp_log_buffer() {
+  static StampLog* buf = nullptr;
+  if (!buf && cudaMalloc(&buf, sizeof(StampLog)) == cudaSuccess) cudaMemset(buf, 0, sizeof(StampLog));
+  return buf;
+}
+}  // namespace artab
+#endif
+
 extern "C" {
 
 int artab_plan_splits(int dtype, int rows, int rows_per_group, int n_groups, int n_heads, int n_ctx) {
@@ -398,6 +409,22 @@ int artab_debug_set(int key, long long value) {
       return ARTAB_EINVAL;
   }
 }
+
+#ifdef ARTAB_TIMELINE
+// copies up to max_records (kernel * 10000 + event * 1000 + CTA (999: the last of a large grid), nanoseconds)
+// pairs, empties the log and returns how many were copied
+ARTAB_API long long artab_debug_stamps(long long* host_dst, long long max_records) {
+  artab::StampLog* buf = artab::stamp_log_buffer();
+  if (!buf || cudaDeviceSynchronize() != cudaSuccess) return -1;
+  unsigned long long n = 0;
+  if (cudaMemcpy(&n, &buf->n, sizeof n, cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+  if (n > (1ULL << 16)) n = 1ULL << 16;
+  if ((long long)n > max_records) n = (unsigned long long)max_records;
+  if (n && cudaMemcpy(host_dst, buf->rec, n * 2 * sizeof(long long), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+  cudaMemset(&buf->n, 0, sizeof n);
+  return (long long)n;
+}
+#endif
 
 void artab_set_dependent_launch(int on) { g_dependent_launch.store(on != 0, std::memory_order_relaxed); }
 

@@ -294,6 +294,7 @@ ctx_attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   const int rows_in_group = p.n_groups == 1 ? p.rows : p.rows_per_group;
   const long group_row0 = p.n_groups == 1 ? 0 : (long)g * p.rows_per_group;
   const int m0 = blockIdx.x * BM;
+  if (threadIdx.x == 0) ARTAB_STAMP(2, 0);
 
   const int tiles = (p.n_ctx + BN - 1) / BN;
   const int tps = (tiles + p.n_splits - 1) / p.n_splits;
@@ -348,6 +349,7 @@ ctx_attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   if (warp != 0) {  // the producer waits after its early K/V prefetch
     dep_wait();
     dep_trigger();
+    if (threadIdx.x == 32) ARTAB_STAMP(2, 1);
   }
 
   if (warp == 0) {
@@ -491,6 +493,7 @@ ctx_attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
   }
   if (threadIdx.x == 0 && sm->ctl.abort_flag && p.status) atomicExch(p.status, 1);
+  if (threadIdx.x == 0) ARTAB_STAMP(2, 2);
 }
 
 // ---------------------------------- host side ----------------------------------
@@ -586,7 +589,7 @@ int launch_ctx_attn_tc(const CtxAttnArgs& a, cudaStream_t s) {
   static_assert(sizeof(Smem) + 1024 <= 100 * 1024, "shared-memory plan exceeds the request");
   static SmemConfig configured;
   {
-    const cudaError_t e = configured.ensure(ctx_attn_tc_kernel, smem);
+    const cudaError_t e = configured.ensure(ctx_attn_tc_kernel, smem, true);
     ARTAB_REQUIRE(e == cudaSuccess, ARTAB_ELAUNCH, "ctx_attn_tc_kernel: shared memory refused: %s",
                   cudaGetErrorString(e));
   }
@@ -609,6 +612,7 @@ int launch_ctx_attn_tc(const CtxAttnArgs& a, cudaStream_t s) {
   const int rows_in_group = a.n_groups == 1 ? a.rows : a.rows_per_group;
   dim3 grid((rows_in_group + BM - 1) / BM, a.n_heads, a.n_groups * a.n_splits);
   prof_begin(PROF_CTX, s);
+  ARTAB_STAMP_ATTACH();
   const cudaError_t le = launch_dependent(ctx_attn_tc_kernel, grid, dim3(kThreads), smem, s, tq, tk, tv, p);
   prof_end(s);
   ARTAB_REQUIRE(le == cudaSuccess, ARTAB_ELAUNCH, "ctx_attn_tc_kernel: %s", cudaGetErrorString(le));

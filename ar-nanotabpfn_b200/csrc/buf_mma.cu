@@ -69,6 +69,7 @@ __global__ void __launch_bounds__(WPB * 32, 6) buf_mma_kernel(const BufMergeArgs
   // tiles) while this kernel is still walking the private buffers.  Its wait still covers everything
   // older, because this grid only completes after its own wait below.
   dep_trigger();
+  if (threadIdx.x == 0) ARTAB_STAMP(3, 0);
   const long item = (long)blockIdx.x * WPB + warp;
   if (item >= a.n_items) return;  // warp-uniform; the kernel has no CTA-wide barrier
   const int g = lane >> 2;   // fragment row: query index (rows 0, 1) / key inside an 8-key tile
@@ -200,39 +201,59 @@ __global__ void __launch_bounds__(WPB * 32, 6) buf_mma_kernel(const BufMergeArgs
 
   // The pass above read only what kernels older than the preceding one wrote (q and the buffer
   // rows); the context partials come from the preceding kernel.
+  if (threadIdx.x == 0) ARTAB_STAMP(3, 3);
   dep_wait();
+  if (threadIdx.x == 0) ARTAB_STAMP(3, 1);
 
   if (g >= 2 || rows2[g & 1] < 0) return;
   const long r = rows2[g];
   const float lse_b = l > 0.f ? (m + log2f(l)) * kLn2 : -INFINITY;  // natural log, like the partials
-  float top = lse_b;
-  for (int sp = 0; sp < a.n_splits; ++sp)
-    top = fmaxf(top, __ldg(a.lse_part + ((size_t)sp * a.rows + r) * a.n_heads + h));
-  float wsum = 0.f, out[8];
-#pragma unroll
-  for (int i = 0; i < 8; ++i) out[i] = 0.f;
-  if (l > 0.f) {
-    const float wb = expf(lse_b - top);
-    wsum = wb;
-    const float inv = wb / l;
+  // Log-sum-exp merge with the context partials.  A dependent global load costs about a microsecond
+  // here, so the partials are fetched four at a time with every load (LSEs and outputs) issued before
+  // anything is computed, and folded in with a running reference `top` (rescaled when a chunk raises it).
+  float top = lse_b, wsum = l > 0.f ? 1.0f : 0.f, out[8];
+  {
+    const float inv = l > 0.f ? 1.0f / l : 0.f;
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       out[2 * j] = o[j][0] * inv;
       out[2 * j + 1] = o[j][1] * inv;
     }
   }
-  for (int sp = 0; sp < a.n_splits; ++sp) {
-    const size_t ro = ((size_t)sp * a.rows + r) * a.n_heads + h;
-    const float ls = __ldg(a.lse_part + ro);
-    if (ls == -INFINITY) continue;
-    const float ws = expf(ls - top);
-    wsum += ws;
-    const float* op = a.o_part + ro * DH + t4 * 2;
+  for (int sp0 = 0; sp0 < a.n_splits; sp0 += 4) {
+    float ls[4];
+    float2 ov[4][4];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const float2 v = *reinterpret_cast<const float2*>(op + 8 * j);
-      out[2 * j] = fmaf(ws, v.x, out[2 * j]);
-      out[2 * j + 1] = fmaf(ws, v.y, out[2 * j + 1]);
+    for (int i = 0; i < 4; ++i) {
+      const int sp = min(sp0 + i, a.n_splits - 1);   // clamped: the loads never depend on a branch
+      const size_t ro = ((size_t)sp * a.rows + r) * a.n_heads + h;
+      ls[i] = __ldcg(a.lse_part + ro);
+      const float* op = a.o_part + ro * DH + t4 * 2;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) ov[i][j] = __ldcg(reinterpret_cast<const float2*>(op + 8 * j));
+    }
+    float cmax = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      if (sp0 + i >= a.n_splits) ls[i] = -INFINITY;
+      cmax = fmaxf(cmax, ls[i]);
+    }
+    if (cmax == -INFINITY) continue;
+    const float ntop = fmaxf(top, cmax);
+    const float rs = top == -INFINITY ? 0.f : expf(top - ntop);
+    top = ntop;
+    wsum *= rs;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) out[j] *= rs;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float ws = ls[i] == -INFINITY ? 0.f : expf(ls[i] - top);
+      wsum += ws;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        out[2 * j] = fmaf(ws, ov[i][j].x, out[2 * j]);
+        out[2 * j + 1] = fmaf(ws, ov[i][j].y, out[2 * j + 1]);
+      }
     }
   }
   if (a.lse_out && t4 == 0) a.lse_out[(size_t)r * a.n_heads + h] = wsum > 0.f ? top + logf(wsum) : -INFINITY;
@@ -244,6 +265,7 @@ __global__ void __launch_bounds__(WPB * 32, 6) buf_mma_kernel(const BufMergeArgs
     float* dst = a.out + (a.out_lane_major ? lane_major_index(r, col, a.n_heads * DH) : (size_t)r * a.n_heads * DH + col);
     *reinterpret_cast<float2*>(dst) = make_float2(out[2 * j] * inv, out[2 * j + 1] * inv);
   }
+  if (threadIdx.x == 0) ARTAB_STAMP(3, 2);
 }
 
 }  // namespace
@@ -255,6 +277,7 @@ int launch_buf_merge_mma(const BufMergeArgs& a, cudaStream_t s) {
   ARTAB_REQUIRE(buf_mma_supported(a.dtype, a.head_dim), ARTAB_EINVAL, "buffer attention (mma): bf16, head_dim 32 only");
   const unsigned grid = (unsigned)((a.n_items + WPB - 1) / WPB);
   prof_begin(PROF_BUF, s);
+  ARTAB_STAMP_ATTACH();
   const cudaError_t le = launch_dependent(buf_mma_kernel, dim3(grid), dim3(WPB * 32), 0, s, a);
   prof_end(s);
   ARTAB_REQUIRE(le == cudaSuccess, ARTAB_ELAUNCH, "buf_mma_kernel: %s", cudaGetErrorString(le));

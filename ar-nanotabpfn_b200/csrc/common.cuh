@@ -46,6 +46,49 @@ void prof_end(cudaStream_t s);
 __device__ __forceinline__ void dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void dep_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
+#ifdef ARTAB_TIMELINE
+// Diagnostic builds only: a log of global-timer stamps shared by every kernel of the library, read
+// with artab_debug_stamps.  Every CTA of a grid of up to
+// ARTAB_STAMP_ALL CTAs, else the first and the last CTA, records (kernel, event, CTA, ns).
+// Kernels: 0 embed, 1 tensor-core dense chain, 2 context contraction, 3 buffer pass (tensor-core
+// fragments), 4 buffer pass (scalar); events: 0 entry, 1 predecessor complete, 2 end, 3 kernel-specific
+// (buffer pass: private keys done, before the wait; dense chain: last instruction).
+#ifndef ARTAB_STAMP_ALL
+#define ARTAB_STAMP_ALL 32   // grids up to this many CTAs record every CTA
+#endif
+struct StampLog {
+  unsigned long long n;
+  long long rec[1 << 16][2];
+};
+StampLog* stamp_log_buffer();       // one device buffer per process, allocated on first use
+static __device__ StampLog* g_stamp_log;   // one copy per translation unit, attached before its launches
+static inline void stamp_log_attach() {
+  static bool done = false;
+  if (done) return;
+  StampLog* p = stamp_log_buffer();
+  cudaMemcpyToSymbol(g_stamp_log, &p, sizeof p);
+  done = true;
+}
+__device__ __forceinline__ void stamp(int kernel, int event) {
+  const unsigned nb = gridDim.x * gridDim.y * gridDim.z;
+  const unsigned b = (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
+  StampLog* log = g_stamp_log;
+  if (!log || (nb > ARTAB_STAMP_ALL && b != 0 && b != nb - 1)) return;
+  long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  const unsigned long long i = atomicAdd(&log->n, 1ULL);
+  if (i < (1ULL << 16)) {
+    log->rec[i][0] = kernel * 10000 + event * 1000 + (nb > ARTAB_STAMP_ALL ? (b ? 999 : 0) : (int)b);
+    log->rec[i][1] = t;
+  }
+}
+#define ARTAB_STAMP(kernel, event) stamp(kernel, event)
+#define ARTAB_STAMP_ATTACH() stamp_log_attach()
+#else
+#define ARTAB_STAMP(kernel, event) do { } while (0)
+#define ARTAB_STAMP_ATTACH() do { } while (0)
+#endif
+
 bool dependent_launch_enabled();
 // diagnostics set through artab_debug_set: limit of the bounded waits (0: the built-in second or so) and
 // the switch that makes the context kernel's waits run out (see artab.h)
@@ -65,15 +108,19 @@ struct PlainLaunchScope {
 constexpr int kMaxDevices = 64;
 struct SmemConfig {
   size_t bytes[kMaxDevices] = {};
+  // several_per_sm: the kernel is meant to have more than one CTA resident per SM, so it also asks
+  // for the largest shared-memory carve-out (the default heuristic may pick one that fits a single CTA)
   template <typename K>
-  cudaError_t ensure(K kernel, size_t smem) {
+  cudaError_t ensure(K kernel, size_t smem, bool several_per_sm = false) {
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return e;
-    if (dev < 0 || dev >= kMaxDevices) return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (smem <= bytes[dev]) return cudaSuccess;
+    const bool tracked = dev >= 0 && dev < kMaxDevices;
+    if (tracked && smem <= bytes[dev]) return cudaSuccess;
     e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e == cudaSuccess) bytes[dev] = smem;
+    if (e == cudaSuccess && several_per_sm)
+      e = cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxShared);
+    if (e == cudaSuccess && tracked) bytes[dev] = smem;
     return e;
   }
 };

@@ -443,8 +443,10 @@ __global__ void __launch_bounds__(288) dense_chain_kernel(const DenseArgs a) {
 __global__ void __launch_bounds__(128) embed_kernel(const EmbedArgs a) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long row = (long)blockIdx.x * (blockDim.x >> 5) + warp;
+  if (threadIdx.x == 0) ARTAB_STAMP(0, 0);
   dep_wait();
   dep_trigger();
+  if (threadIdx.x == 0) ARTAB_STAMP(0, 1);
   if (row >= a.rows) return;
   const float* xr;
   float yv = 0.f;
@@ -519,6 +521,7 @@ int launch_embed(const EmbedArgs& a, cudaStream_t s) {
   if (a.rows <= 0) return ARTAB_OK;
   const int wpb = 4;
   prof_begin(PROF_EMBED, s);
+  ARTAB_STAMP_ATTACH();
   const cudaError_t le = launch_dependent(embed_kernel, dim3((unsigned)((a.rows + wpb - 1) / wpb)), dim3(wpb * 32), 0, s, a);
   prof_end(s);
   ARTAB_REQUIRE(le == cudaSuccess, ARTAB_ELAUNCH, "embed_kernel: %s", cudaGetErrorString(le));

@@ -262,9 +262,11 @@ __device__ long long g_tl[32][32][32];   // [launch slot][cta][mark]
 #define TL(id) do { if (tl_on) g_tl[a.tl_slot & 31][blockIdx.x & 31][id] = clock64(); } while (0)
 __device__ __forceinline__ long long gtimer() { long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
 #define TLG(id) do { if (tl_on) g_tl[a.tl_slot & 31][blockIdx.x & 31][id] = gtimer(); } while (0)
+#define TLS(event) do { if (tl_on) ARTAB_STAMP(1, event); } while (0)
 #else
 #define TL(id) do { } while (0)
 #define TLG(id) do { } while (0)
+#define TLS(event) do { } while (0)
 #endif
 
 // The same for two neighbouring columns at once, on packed pairs (same operations, same rounding as
@@ -801,10 +803,44 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const DenseArgs a
   if (threadIdx.x == 64) {
     g_tl[a.tl_slot & 31][blockIdx.x & 31][29] = gtimer();
     g_tl[a.tl_slot & 31][blockIdx.x & 31][28] = clock64();
+    ARTAB_STAMP(1, 0);
   }
 #endif
   constexpr int NKC = D / 64;
   constexpr uint32_t kSlab = D * 128;
+
+  // The epilogue threads fetch the per-column constants (LayerNorm vectors, biases: model constants,
+  // nothing the preceding kernel wrote) before anything else, into registers: the loads are in flight
+  // while the barriers are set up and tensor memory is allocated, and are stored to shared memory
+  // once the roles have split.  All loads are issued before the first store (read-only path: the
+  // compiler may not assume that the shared-memory stores leave the global vectors alone, and would
+  // otherwise wait for every load in turn).
+  constexpr int kBiasPerThread = (1024 + kEpi - 1) / kEpi;
+  float cv[7], cb[kBiasPerThread];
+  {
+    const int i = (int)threadIdx.x - 64;
+    const bool epi = i >= 0 && i < kEpi;
+    const bool col = epi && i < D;
+#pragma unroll
+    for (int k = 0; k < 7; ++k) cv[k] = 0.f;
+    if (col && a.do_post) {
+      cv[0] = __ldg(a.post_w.ln2_g + i);
+      cv[1] = __ldg(a.post_w.ln2_b + i);
+      cv[2] = __ldg(a.post_w.b2 + i);
+      cv[3] = __ldg(a.post_w.ln3_g + i);
+      cv[4] = __ldg(a.post_w.ln3_b + i);
+    }
+    if (col && a.do_final) {
+      cv[5] = __ldg(a.lnf_g + i);
+      cv[6] = __ldg(a.lnf_b + i);
+    } else if (col && a.do_pre) {
+      cv[5] = __ldg(a.pre_w.ln1_g + i);
+      cv[6] = __ldg(a.pre_w.ln1_b + i);
+    }
+#pragma unroll
+    for (int k = 0; k < kBiasPerThread; ++k)
+      cb[k] = (epi && a.do_post && i + k * kEpi < a.Dff) ? __ldg(a.post_w.b1 + i + k * kEpi) : 0.f;
+  }
   const int nt = a.Dff / HT;
   // A CTA pair (cluster of 2) may share one row tile: both walk the whole chain, but each takes
   // every other hidden tile of the layer's MLP (partial sums exchanged once) and a part of the
@@ -814,22 +850,25 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const DenseArgs a
   const int t_begin = (csize == 2 && crank == 1) ? 2 : 0;   // projections (0 q, 1 k, 2 v) of this CTA
   const int t_end = (csize == 2 && crank == 0) ? 2 : 3;
 
-  if (threadIdx.x == 0) {
-    for (int r = 0; r < 2; ++r)
-      for (int i = 0; i < NSLOT; ++i) {
-        mbar_init(&sm->w_full[r][i], 1);
-        mbar_init(&sm->w_empty[r][i], 1);
-      }
-    mbar_init(&sm->ep_done, kEpi);
-    mbar_init(&sm->acc_full, 1);
-    mbar_init(&sm->h_full, 1);
-    mbar_init(&sm->acch_free, kEpi);
-    mbar_init(&sm->ah_ready, kEpi);
-    mbar_init(&sm->ah_free, 1);
-    mbar_init(&sm->x_full, kEpi / 32);   // one remote arrival per epilogue warp
-    mbar_init(&sm->x_ready, 1);          // one remote arrival per CTA
-    mbar_init(&sm->x_done, kEpi);
-    sm->abort_flag = 0;
+  // barrier set-up spread over the first warp (one barrier per lane instead of one thread doing all)
+  if (warp == 0) {
+    if (lane < 2 * NSLOT) {
+      mbar_init(&sm->w_full[lane / NSLOT][lane % NSLOT], 1);
+      mbar_init(&sm->w_empty[lane / NSLOT][lane % NSLOT], 1);
+    }
+    switch (lane) {
+      case 8: mbar_init(&sm->ep_done, kEpi); break;
+      case 9: mbar_init(&sm->acc_full, 1); break;
+      case 10: mbar_init(&sm->h_full, 1); break;
+      case 11: mbar_init(&sm->acch_free, kEpi); break;
+      case 12: mbar_init(&sm->ah_ready, kEpi); break;
+      case 13: mbar_init(&sm->ah_free, 1); break;
+      case 14: mbar_init(&sm->x_full, kEpi / 32); break;   // one remote arrival per epilogue warp
+      case 15: mbar_init(&sm->x_ready, 1); break;          // one remote arrival per CTA
+      case 16: mbar_init(&sm->x_done, kEpi); break;
+      case 17: sm->abort_flag = 0; break;
+      default: break;
+    }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
@@ -995,42 +1034,18 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const DenseArgs a
         *reinterpret_cast<float4*>(dst + goff + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
     };
 
-    // Small per-column vectors -> shared memory (read by every epilogue thread, many times).  All
-    // loads are issued before the first store (read-only path: the compiler may not assume that the
-    // shared-memory stores leave the global vectors alone, and would otherwise wait for every load in
-    // turn); their latency then hides under the first GEMM.
+    // Small per-column vectors -> shared memory (read by every epilogue thread, many times): the values
+    // were fetched at the top of the kernel, so their latency is behind us by now.
     {
       const int i = threadIdx.x - 64;
-      float t[7];
-      float bh[(1024 + kEpi - 1) / kEpi];
-      const bool col = i < D;
+      if (i < D) {
 #pragma unroll
-      for (int k = 0; k < 7; ++k) t[k] = 0.f;
-      if (col && a.do_post) {
-        t[0] = __ldg(a.post_w.ln2_g + i);
-        t[1] = __ldg(a.post_w.ln2_b + i);
-        t[2] = __ldg(a.post_w.b2 + i);
-        t[3] = __ldg(a.post_w.ln3_g + i);
-        t[4] = __ldg(a.post_w.ln3_b + i);
-      }
-      if (col && a.do_final) {
-        t[5] = __ldg(a.lnf_g + i);
-        t[6] = __ldg(a.lnf_b + i);
-      } else if (col && a.do_pre) {
-        t[5] = __ldg(a.pre_w.ln1_g + i);
-        t[6] = __ldg(a.pre_w.ln1_b + i);
-      }
-#pragma unroll
-      for (int k = 0; k < (1024 + kEpi - 1) / kEpi; ++k)
-        bh[k] = (a.do_post && i + k * kEpi < a.Dff) ? __ldg(a.post_w.b1 + i + k * kEpi) : 0.f;
-      if (col) {
-#pragma unroll
-        for (int k = 0; k < 7; ++k) sm->vec[k][i] = t[k];
+        for (int k = 0; k < 7; ++k) sm->vec[k][i] = cv[k];
       }
       if (a.do_post) {
 #pragma unroll
-        for (int k = 0; k < (1024 + kEpi - 1) / kEpi; ++k)
-          if (i + k * kEpi < a.Dff) sm->bias_h[i + k * kEpi] = bh[k];
+        for (int k = 0; k < kBiasPerThread; ++k)
+          if (i + k * kEpi < a.Dff) sm->bias_h[i + k * kEpi] = cb[k];
       }
     }
     // Everything above (and the weight producers' first tiles) needed nothing from the preceding
@@ -1040,6 +1055,7 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const DenseArgs a
     dep_trigger();
     TL(2);
     TLG(30);
+    TLS(1);
     if (a.do_post) {
       load_lm(a.attn);
       e.publish_ax(v);
@@ -1298,6 +1314,7 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const DenseArgs a
     if (!e.ok && threadIdx.x == 64 && a.status) atomicExch(a.status, 3);
     TL(26);
     TLG(31);
+    TLS(2);
   }
 
   tc_fence_before();
@@ -1310,6 +1327,7 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const DenseArgs a
     if (!cluster_waited) cluster_wait();
     cluster_sync_all();  // neither CTA leaves while the other could still address its shared memory
   }
+  if (threadIdx.x == 64) ARTAB_STAMP(1, 3);
 }
 
 }  // namespace
@@ -1341,6 +1359,7 @@ int launch_dense_tc(const DenseArgs& a, cudaStream_t s) {
 #ifdef ARTAB_TIMELINE
   static int tl_next = 0;
   const_cast<DenseArgs&>(a).tl_slot = tl_next++ & 31;
+  ARTAB_STAMP_ATTACH();
 #endif
   prof_begin(PROF_DENSE, s);
   switch (a.D) {

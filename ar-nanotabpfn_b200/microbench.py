@@ -368,9 +368,26 @@ def bench_timeline(a):
     xc, yc, xt = (t.to(dev) for t in syn.config3_workload(B, Nt))
     p = ar_tabpfn.ARTabPFNPredictor.from_trained_model(m, backend="triton_shared_context", precision="bf16")
     var = p.draw_variates(Nt, B, dev)
-    for _ in range(2):
+    stamps = None
+    if hasattr(lib, "artab_debug_stamps"):
+        lib.artab_debug_stamps.restype = C.c_longlong
+        lib.artab_debug_stamps.argtypes = [C.c_void_p, C.c_longlong]
+        stamps = (C.c_longlong * (2 << 16))()
+    for it in range(2):
+        if stamps is not None:
+            lib.artab_debug_stamps(stamps, 1 << 16)      # empties the log: only the last job is kept
         p.sample_sequence(xc, yc, xt, variates=var)
     torch.cuda.synchronize()
+    if stamps is not None:
+        # per kernel, every CTA of a small grid, else the first and the last (999): (kernel, event, CTA, microseconds
+        # since the first record);
+        # kernels 0 embed, 1 dense chain, 2 context contraction, 3 / 4 buffer pass; events 0 entry,
+        # 1 predecessor complete, 2 end
+        n = lib.artab_debug_stamps(stamps, 1 << 16)
+        rec = sorted((stamps[2 * i + 1], stamps[2 * i]) for i in range(max(n, 0)))
+        t0 = rec[0][0] if rec else 0
+        print(json.dumps({"stamps": [[c // 10000, c // 1000 % 10, c % 1000, round((t - t0) / 1e3, 3)] for t, c in rec]}),
+              flush=True)
     buf = (C.c_longlong * (32 * 32 * 32))()
     lib.artab_debug_timeline.restype = C.c_int
     if lib.artab_debug_timeline(buf):
