@@ -350,15 +350,13 @@ def bench_timeline(a):
     """Per-phase SM-cycle stamps of the tensor-core dense chain during a short config-3 sampling job.
     Needs a diagnostic build of the library:
         NVCC_APPEND_FLAGS=-DARTAB_TIMELINE python ar-nanotabpfn_b200/build.py --force
-    or one kept beside the product library and named by the environment variable ARTAB_TIMELINE_LIB.
+    or one kept beside the product library and named by the environment variable ARTAB_MICROBENCH_LIB.
     Prints, for CTA 0 and 1 of every recorded launch slot (the last 32 dense launches), the offset of
     every mark from the roles split, and the global-timer distances entry -> predecessor complete -> end."""
     import ctypes as C
     import numpy as np
     import ar_tabpfn
     import synthetic as syn
-    if os.environ.get("ARTAB_TIMELINE_LIB"):
-        _lib.LIB_PATH = os.environ["ARTAB_TIMELINE_LIB"]
     lib = _lib.lib()
     if not hasattr(lib, "artab_debug_timeline"):
         raise SystemExit("this library was built without -DARTAB_TIMELINE")
@@ -408,6 +406,8 @@ def bench_timeline(a):
 
 
 def main():
+    if os.environ.get("ARTAB_MICROBENCH_LIB"):   # another build of the library (diagnostic flags, a variant under test)
+        _lib.LIB_PATH = os.environ["ARTAB_MICROBENCH_LIB"]
     ap = argparse.ArgumentParser()
     ap.add_argument("which", choices=["ctx", "config2", "buffer", "append", "chain", "config4", "config5", "timeline"])
     ap.add_argument("--datasets", type=int, default=64)
