@@ -97,6 +97,34 @@ def test_hybrid_bf16_vs_fp32_torch(tk, shape):
     torch.testing.assert_close(lse_c, want_l, atol=2e-3, rtol=2e-3)
 
 
+@pytest.mark.parametrize("jump", [20.0, 150.0, 400.0])
+def test_context_attention_scores_jump_between_key_tiles(tk, jump):
+    """Later key tiles of the tensor-core kernel are exponentiated against the reference found so far,
+    without looking at their maximum first.  Here a handful of keys far down the context score `jump`
+    (natural-log units) above everything before them: a moderate jump must raise the reference for the
+    following tiles, a large one overflows the exponentials of its tile and must send it through the
+    exact two-pass form.  n_splits=1 keeps all five key tiles in one CTA, in order."""
+    B, H, Lq, Nc, Dh = 40, 2, 2, 600, 32
+    g = torch.Generator().manual_seed(11)
+    q = torch.randn(B, H, Lq, Dh, generator=g)
+    k = 0.3 * torch.randn(H, Nc, Dh, generator=g)
+    v = torch.randn(H, Nc, Dh, generator=g)
+    # rows 0..9 of every head get a key in the third tile that is aligned with them; rows of the second
+    # half of the batch another one in the fifth tile, twice as far up
+    for h in range(H):
+        u = q[3, h, 0] / q[3, h, 0].norm()
+        k[h, 300] = u * jump * Dh ** 0.5 / q[3, h, 0].norm()
+        w = q[30, h, 1] / q[30, h, 1].norm()
+        k[h, 590] = w * 2 * jump * Dh ** 0.5 / q[30, h, 1].norm()
+    q, k, v = q.bfloat16().cuda(), k.bfloat16().cuda(), v.bfloat16().cuda()
+    want, want_l = ref_attention(q, k.unsqueeze(0).expand(B, -1, -1, -1), v.unsqueeze(0).expand(B, -1, -1, -1))
+    for splits in (1, 2):
+        out, lse = tk.triton_context_attention(q, k, v, n_splits=splits)
+        assert torch.isfinite(out).all() and torch.isfinite(lse).all()
+        assert (out.float() - want).abs().max() / want.abs().max() < 1e-2
+        torch.testing.assert_close(lse, want_l, atol=2e-3, rtol=2e-3)
+
+
 @pytest.mark.parametrize("shape", [(3, 2, 37, 100, 32), (2, 6, 128, 260, 32), (2, 2, 9, 50, 16)])
 def test_teacher_forcing_bf16_vs_fp32_torch(tk, shape):
     """bf16 mode, block-causal buffer visibility (buffer query i sees buffer keys <= i, target query i
