@@ -870,21 +870,16 @@ __global__ void __launch_bounds__(kThreads, 1) dense_tc_kernel(const DenseArgs a
       default: break;
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    if (lane == 0) ARTAB_STAMP(1, 4);
   }
   if (warp == 1) {
-    if (lane == 0) ARTAB_STAMP(1, 5);
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm->tmem_base)),
                  "r"(kTmemCols)
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-    if (lane == 0) ARTAB_STAMP(1, 6);
   }
-  if (threadIdx.x == 64) ARTAB_STAMP(1, 7);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  if (threadIdx.x == 64) ARTAB_STAMP(1, 8);
   // The peer's barriers must exist before anyone arrives on them.  Every thread arrives here; the
   // epilogue threads wait just before the MLP exchange (the first remote access of a launch), all
   // other threads, and the epilogue threads of a launch without an exchange, at the end.
