@@ -97,6 +97,23 @@ def test_hybrid_bf16_vs_fp32_torch(tk, shape):
     torch.testing.assert_close(lse_c, want_l, atol=2e-3, rtol=2e-3)
 
 
+@pytest.mark.parametrize("splits", [4, 5, 8, 9])
+def test_context_attention_many_splits_bf16(tk, splits):
+    """More key splits than the merge fetches at once (it takes the partials four at a time and keeps
+    a running reference across the chunks), with one split whose scores dominate the others."""
+    B, H, Lq, Nc, Dh = 70, 6, 2, 1100, 32   # nine key tiles
+    g = torch.Generator().manual_seed(21)
+    q = torch.randn(B, H, Lq, Dh, generator=g)
+    k = torch.randn(H, Nc, Dh, generator=g)
+    v = torch.randn(H, Nc, Dh, generator=g)
+    k[:, 900:910] *= 6.0   # a late split carries nearly all the weight of many rows
+    q, k, v = q.bfloat16().cuda(), k.bfloat16().cuda(), v.bfloat16().cuda()
+    want, want_l = ref_attention(q, k.unsqueeze(0).expand(B, -1, -1, -1), v.unsqueeze(0).expand(B, -1, -1, -1))
+    out, lse = tk.triton_context_attention(q, k, v, n_splits=splits)
+    assert (out.float() - want).abs().max() / want.abs().max() < 1e-2
+    torch.testing.assert_close(lse, want_l, atol=2e-3, rtol=2e-3)
+
+
 @pytest.mark.parametrize("jump", [20.0, 150.0, 400.0])
 def test_context_attention_scores_jump_between_key_tiles(tk, jump):
     """Later key tiles of the tensor-core kernel are exponentiated against the reference found so far,
