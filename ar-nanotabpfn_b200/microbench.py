@@ -288,9 +288,19 @@ def bench_config4(a):
 
     ms = _event_time(fn, a.iters, a.warmup)
     ld = out["ld"]
+    # one more call with an event pair around every launch (they serialise the launches): where the time goes
+    lib = _lib.lib()
+    _lib.profile_read()
+    lib.artab_profile_enable(1)
+    fn()
+    torch.cuda.synchronize()
+    prof = _lib.profile_read()
+    lib.artab_profile_enable(0)
+    shares = {k: {"ms": round(v[0], 3), "launches": v[1]} for k, v in prof.items() if v[1]}
     print(json.dumps({"bench": "config4", "datasets": B, "ctx": Nc, "targets": Nt, "precision": a.dtype, "ms": ms,
                       "targets_per_s": B * Nt / (ms * 1e-3), "mean_logdens": float(ld.mean()),
-                      "finite": bool(torch.isfinite(ld).all()), "status": int(pred._bufs["status"].item())}),
+                      "finite": bool(torch.isfinite(ld).all()), "status": int(pred._bufs["status"].item()),
+                      "kernel_ms_serialised": shares}),
           flush=True)
 
 
