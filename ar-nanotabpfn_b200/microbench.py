@@ -337,12 +337,22 @@ def bench_config5(a):
     ms = torch.tensor([_event_time(fn, a.iters, a.warmup)], device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    # one more call with an event pair around every launch (they serialise the launches): where the time goes
+    lib = _lib.lib()
+    _lib.profile_read()
+    lib.artab_profile_enable(1)
+    fn()
+    torch.cuda.synchronize()
+    prof = _lib.profile_read()
+    lib.artab_profile_enable(0)
     if rank == 0:
         ys, ld = out["ys"], pred.last_logdens
         print(json.dumps({"bench": "config5", "n_gpus": world, "streams": a.streams, "ctx": Nc, "targets": Nt,
                           "precision": a.dtype, "ms": float(ms), "targets_per_s": a.streams * Nt / (float(ms) * 1e-3),
                           "scaling": "strong", "finite": bool(torch.isfinite(ys).all() and torch.isfinite(ld).all()),
-                          "mean_logdens": float(ld.mean()), "status": int(pred._bufs["status"].item())}), flush=True)
+                          "mean_logdens": float(ld.mean()), "status": int(pred._bufs["status"].item()),
+                          "kernel_ms_serialised": {k: {"ms": round(v[0], 3), "launches": v[1]}
+                                                   for k, v in prof.items() if v[1]}}), flush=True)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
