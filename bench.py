@@ -262,13 +262,14 @@ def run_scaleout(dev, world, rank, precision, steps=2, warmup=1):
         out = sharded_call(run_shard, full, variates=(expo, normal))
     sync()
     evs = []
-    for _ in range(steps):
-        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        s.record()
-        out = sharded_call(run_shard, full, variates=(expo, normal))
-        e.record()
-        evs.append((s, e))
-    sync()
+    with ClockSampler(dev.index if dev.index is not None else 0) as clk:   # this rank's GPU, during the timed calls
+        for _ in range(steps):
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            out = sharded_call(run_shard, full, variates=(expo, normal))
+            e.record()
+            evs.append((s, e))
+        sync()
     ms = torch.tensor([sum(s.elapsed_time(e) for s, e in evs) / steps], device=dev, dtype=torch.float64)
     # the context prefill alone (it is repeated on every rank and does not shrink with N)
     lo, hi = shard_bounds(B, world, rank)
@@ -289,7 +290,7 @@ def run_scaleout(dev, world, rank, precision, steps=2, warmup=1):
             "scaling": "strong", "steps": steps, "warmup": warmup, "ms_per_step": float(ms.item()),
             "targets_per_s": B * Nt / (float(ms.item()) * 1e-3), "prefill_ms": float(pre.item()),
             "finite": bool(torch.isfinite(ys).all() and torch.isfinite(ld).all()),
-            "device_status": int(pred._bufs["status"].item())}
+            "device_status": int(pred._bufs["status"].item()), "clocks": clk.result}
 
 
 def main():
